@@ -1,0 +1,134 @@
+/*
+ * C ABI of libmlkit_b200: sm_100a kernels for mlkit's packed-inference path.
+ *
+ * Every pointer is a DEVICE pointer owned by the caller unless a comment says
+ * otherwise.  Nothing here allocates device memory.  Every entry point queues
+ * its work on `stream` (a cudaStream_t passed as void*) and returns without
+ * synchronising.  Return value: 0 on success, a negative MKB_E_* code on a
+ * rejected call (nothing was launched); mkb_last_error() then describes the
+ * reason for the calling thread.
+ *
+ * Citations name files of the reference project (mlkit) whose interface or
+ * arithmetic an entry point stands in for.
+ */
+#ifndef MLKIT_B200_H
+#define MLKIT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of activations, scales/offsets and dense outputs */
+enum { MKB_F16 = 0, MKB_BF16 = 1, MKB_F32 = 2 };
+
+/* error codes */
+enum {
+  MKB_OK = 0,
+  MKB_E_ARGUMENT = -1,    /* null pointer, non-positive size, unknown dtype */
+  MKB_E_UNSUPPORTED = -2, /* shape / layout outside what the kernels cover */
+  MKB_E_ALIGNMENT = -3,   /* pointer or stride alignment the fast path needs */
+  MKB_E_CUDA = -4         /* the CUDA runtime refused the launch */
+};
+
+/* kernel choice for mkb_gemv_ex */
+enum {
+  MKB_GEMV_AUTO = 0,   /* fastest kernel that covers the arguments */
+  MKB_GEMV_SCALAR = 1, /* word-at-a-time fp32 kernel: every layout the reference's fused kernel accepts */
+  MKB_GEMV_TILED = 2   /* 16-row x 128-code register-tiled kernel (fp16 activations) */
+};
+
+int mkb_version(void);
+const char* mkb_last_error(void);
+
+/*
+ * Packed matvec for one to eight activation rows:
+ *   y[m,n] = sum_k x[m,k] * (lut[code[n,k]] * scales[n,k/group] (+ zeros[n,k/group])) (+ bias[n])
+ * accumulated in fp32 and stored in the activation dtype.
+ *
+ * Replaces the reference's Triton launch `packed_matrix_vector`
+ * (src/mlkit/kernels/packed_linear.py:107-173) as issued by
+ * `PackedLinear._launch_directly` (src/mlkit/inference/packed_linear.py:181-245)
+ * and `matrix_vector` (src/mlkit/kernels/packed_linear.py:181-226).
+ *
+ * packed: the little-endian code stream of src/mlkit/quantization/operations/bit_packing.py:13-29;
+ *         row n starts at packed + n*packed_row_stride and holds K*bits/8 bytes.
+ * scales/zeros/bias: element type scale_dtype / scale_dtype / x_dtype; zeros and bias may be null.
+ * lut: fp32 code values, lut_len <= 2^bits entries.
+ * integer_grid / grid_minimum: the caller's promise that lut[c] == grid_minimum + c exactly for
+ *         every code, with an integer grid_minimum (the counterpart of the reference's
+ *         uniform_grid / grid_minimum / grid_step launch constants,
+ *         src/mlkit/inference/packed_linear.py:90-97); pass 0 when unsure, the table is used then.
+ * Constraints (src/mlkit/kernels/packed_linear.py:63-79): 1 <= bits <= 8, K and group are
+ * multiples of the codes in one packing word, 1 <= M <= 8.
+ */
+int mkb_gemv(const void* x, const uint8_t* packed, const void* scales, const float* lut,
+             const void* zeros, const void* bias, void* y,
+             int M, int N, int K, int group, int bits, int lut_len,
+             int x_dtype, int scale_dtype,
+             int64_t packed_row_stride, int64_t scale_row_stride,
+             int integer_grid, float grid_minimum, void* stream);
+
+/* Same, with an explicit kernel choice (MKB_GEMV_*); returns MKB_E_UNSUPPORTED when the chosen
+ * kernel does not cover the arguments. */
+int mkb_gemv_ex(const void* x, const uint8_t* packed, const void* scales, const float* lut,
+                const void* zeros, const void* bias, void* y,
+                int M, int N, int K, int group, int bits, int lut_len,
+                int x_dtype, int scale_dtype,
+                int64_t packed_row_stride, int64_t scale_row_stride,
+                int integer_grid, float grid_minimum, int kernel, void* stream);
+
+/*
+ * Unpack and dequantise a packed weight:
+ *   codes_out[n,k] = code (uint8), w_out[n,k] = lut[code] * scale (+ zero) rounded once to out_dtype.
+ * Either output may be null.  The multiply and the add are separate IEEE binary32 operations,
+ * so the result equals the reference reconstruction bit for bit.
+ *
+ * Replaces `decode` / `decode_rows` (src/mlkit/kernels/packed_linear.py:229-313), the tensor route
+ * `unpack` + `decode_scaled` that `PackedLinear.weight` takes for layouts without whole words
+ * (src/mlkit/inference/packed_linear.py:110-143; src/mlkit/quantization/codecs/scaled.py:53-61) and
+ * `unpack` itself (src/mlkit/quantization/operations/bit_packing.py:80-99).
+ *
+ * The stream is read as one flat run of N*K codes (rows need not start on a byte); scales and zeros
+ * are [N, ceil(K/group)] with row stride scale_row_stride.  bits in 1..8.
+ */
+int mkb_dequant(const uint8_t* packed, const void* scales, const float* lut, const void* zeros,
+                void* w_out, uint8_t* codes_out,
+                int64_t N, int64_t K, int group, int bits, int lut_len,
+                int scale_dtype, int out_dtype, int64_t scale_row_stride, void* stream);
+
+/*
+ * Decode selected rows of a packed weight (embedding lookup through a packed output head):
+ *   out[i,:] = dequantised row rows[i], i < count, in out_dtype.
+ * Replaces `PackedEmbedding.forward` (src/mlkit/inference/packed_linear.py:274-287).
+ * Rows must hold whole bytes (K*bits % 8 == 0).
+ */
+int mkb_dequant_rows(const uint8_t* packed, const void* scales, const float* lut, const void* zeros,
+                     const int64_t* rows, void* out,
+                     int64_t count, int64_t N, int64_t K, int group, int bits, int lut_len,
+                     int scale_dtype, int out_dtype, int64_t scale_row_stride, void* stream);
+
+/*
+ * Structured orthogonal transform of activation rows, fused:
+ *   y[m,:] = (B kron H_pow2)(x[m,:] * signs), W = factor * pow2,
+ * H the Sylvester-ordered Walsh-Hadamard butterflies in ascending stride in fp32, scaled by
+ * fp32(1)/fp32(sqrt(pow2)); B (row-major [factor,factor] fp32, may be null when factor == 1) mixes
+ * the `factor` blocks:  y[f',p] = sum_f B[f',f] * h[f,p].  With inverse != 0 the transposed
+ * basis is applied and the signs multiply the result instead of the input.
+ * x and y have element type dtype and may alias; signs (int8 +1/-1) may be null.
+ *
+ * Replaces `hadamard_pass`/`transform` (src/mlkit/kernels/hadamard.py:21-136) and the tensor
+ * route around it, `structured_transform` / `randomized_transform`
+ * (src/mlkit/quantization/operations/orthogonal_transforms.py:101-118), as invoked by the
+ * rotation pre-hook (src/mlkit/conversion/model_transforms.py:189-196).
+ * pow2 is a power of two; W*4 bytes (+ factor^2*4) must fit shared memory (W <= 49152).
+ */
+int mkb_hadamard(const void* x, const int8_t* signs, const float* basis, void* y,
+                 int64_t M, int W, int factor, int pow2, int dtype, int inverse, int normalize,
+                 void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MLKIT_B200_H */

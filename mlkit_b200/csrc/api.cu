@@ -1,0 +1,95 @@
+// C ABI entry points that are not tied to one kernel file: error text, device cache, matvec dispatch.
+#include <cstdarg>
+#include <cstdio>
+
+#include "mkb_common.cuh"
+
+namespace mkb {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* format, ...) {
+  va_list arguments;
+  va_start(arguments, format);
+  vsnprintf(g_error, sizeof(g_error), format, arguments);
+  va_end(arguments);
+}
+
+int cuda_fail(cudaError_t status, const char* what) {
+  set_error("%s: %s", what, cudaGetErrorString(status));
+  return MKB_E_CUDA;
+}
+
+const DeviceInfo& device_info() {
+  static DeviceInfo cache[64];
+  static bool known[64];
+  int device = 0;
+  cudaGetDevice(&device);
+  if (device < 0 || device >= 64) device = 0;
+  if (!known[device]) {
+    DeviceInfo info{148, 232448};
+    cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, device);
+    cudaDeviceGetAttribute(&info.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+    cache[device] = info;
+    known[device] = true;
+  }
+  return cache[device];
+}
+
+int gemv_scalar_supported(int K, int group, int bits);
+int launch_gemv_scalar(const void* x, const uint8_t* packed, const void* scales, const float* lut,
+                       const void* zeros, const void* bias, void* y, int M, int N, int K, int group,
+                       int bits, int lut_len, int x_dtype, int scale_dtype, int64_t packed_row_stride,
+                       int64_t scale_row_stride, cudaStream_t stream);
+int gemv_tiled_supported(int M, int K, int group, int bits, int x_dtype, int scale_dtype,
+                         const void* x, const uint8_t* packed, int64_t packed_row_stride);
+int launch_gemv_tiled(const void* x, const uint8_t* packed, const void* scales, const float* lut,
+                      const void* zeros, const void* bias, void* y, int M, int N, int K, int group,
+                      int bits, int lut_len, int64_t packed_row_stride, int64_t scale_row_stride,
+                      int integer_grid, float grid_minimum, cudaStream_t stream);
+
+}  // namespace mkb
+
+extern "C" int mkb_version(void) { return 100; }
+
+extern "C" const char* mkb_last_error(void) { return mkb::g_error; }
+
+extern "C" int mkb_gemv_ex(const void* x, const uint8_t* packed, const void* scales, const float* lut,
+                           const void* zeros, const void* bias, void* y, int M, int N, int K, int group,
+                           int bits, int lut_len, int x_dtype, int scale_dtype,
+                           int64_t packed_row_stride, int64_t scale_row_stride, int integer_grid,
+                           float grid_minimum, int kernel, void* stream) {
+  using namespace mkb;
+  MKB_REQUIRE(M >= 1 && M <= 8, MKB_E_UNSUPPORTED, "gemv: M=%d outside 1..8", M);
+  MKB_REQUIRE(N >= 0 && K >= 0, MKB_E_ARGUMENT, "gemv: negative shape");
+  MKB_REQUIRE(bits >= 1 && bits <= 8, MKB_E_UNSUPPORTED, "gemv: bits=%d outside 1..8", bits);
+  MKB_REQUIRE(group >= 1, MKB_E_ARGUMENT, "gemv: group must be positive");
+  MKB_REQUIRE(x_dtype >= MKB_F16 && x_dtype <= MKB_F32 && scale_dtype >= MKB_F16 && scale_dtype <= MKB_F32,
+              MKB_E_ARGUMENT, "gemv: unknown dtype");
+  MKB_REQUIRE(lut_len >= 1 && lut_len <= (1 << bits), MKB_E_ARGUMENT,
+              "gemv: lut_len=%d does not fit %d-bit codes", lut_len, bits);
+  MKB_REQUIRE(kernel >= MKB_GEMV_AUTO && kernel <= MKB_GEMV_TILED, MKB_E_ARGUMENT, "gemv: unknown kernel choice");
+  if (N == 0) return MKB_OK;
+  MKB_REQUIRE(x && packed && scales && lut && y, MKB_E_ARGUMENT, "gemv: null pointer");
+  MKB_REQUIRE(gemv_scalar_supported(K, group, bits), MKB_E_UNSUPPORTED,
+              "gemv: K=%d or group=%d splits a packing word of %d-bit codes", K, group, bits);
+  MKB_REQUIRE(K > 0, MKB_E_UNSUPPORTED, "gemv: empty reduction");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool tiled_ok = gemv_tiled_supported(M, K, group, bits, x_dtype, scale_dtype, x, packed, packed_row_stride);
+  if (kernel == MKB_GEMV_TILED)
+    MKB_REQUIRE(tiled_ok, MKB_E_UNSUPPORTED, "gemv: the tiled kernel does not cover these arguments");
+  if (kernel == MKB_GEMV_TILED || (kernel == MKB_GEMV_AUTO && tiled_ok))
+    return launch_gemv_tiled(x, packed, scales, lut, zeros, bias, y, M, N, K, group, bits, lut_len,
+                             packed_row_stride, scale_row_stride, integer_grid, grid_minimum, s);
+  return launch_gemv_scalar(x, packed, scales, lut, zeros, bias, y, M, N, K, group, bits, lut_len, x_dtype,
+                            scale_dtype, packed_row_stride, scale_row_stride, s);
+}
+
+extern "C" int mkb_gemv(const void* x, const uint8_t* packed, const void* scales, const float* lut,
+                        const void* zeros, const void* bias, void* y, int M, int N, int K, int group,
+                        int bits, int lut_len, int x_dtype, int scale_dtype, int64_t packed_row_stride,
+                        int64_t scale_row_stride, int integer_grid, float grid_minimum, void* stream) {
+  return mkb_gemv_ex(x, packed, scales, lut, zeros, bias, y, M, N, K, group, bits, lut_len, x_dtype,
+                     scale_dtype, packed_row_stride, scale_row_stride, integer_grid, grid_minimum,
+                     MKB_GEMV_AUTO, stream);
+}

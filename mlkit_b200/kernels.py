@@ -1,0 +1,158 @@
+"""Tensor-level wrappers of the C ABI: they take CUDA tensors, pass raw pointers and the current stream.
+
+Counterpart of the reference's launch wrappers in ``src/mlkit/kernels/packed_linear.py:181-313``,
+``src/mlkit/kernels/hadamard.py:108-136`` and ``src/mlkit/kernels/launching.py:33-52``: work is queued
+on the current CUDA stream of the tensor's device, nothing is synchronised and, apart from the
+output tensor the caller passes in, nothing is allocated.
+"""
+
+import torch
+from torch import Tensor
+
+from mlkit_b200 import _native
+
+DTYPE_TAGS = {torch.float16: _native.F16, torch.bfloat16: _native.BF16, torch.float32: _native.F32}
+KERNEL_CHOICES = {"auto": _native.GEMV_AUTO, "scalar": _native.GEMV_SCALAR, "tiled": _native.GEMV_TILED}
+
+
+def _tag(dtype: torch.dtype, what: str) -> int:
+    try:
+        return DTYPE_TAGS[dtype]
+    except KeyError:
+        raise ValueError(f"{what} dtype {dtype} is not supported (fp16, bf16, fp32)") from None
+
+
+def _pointer(tensor: Tensor | None) -> int | None:
+    return None if tensor is None else tensor.data_ptr()
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _require_cuda(*tensors: Tensor | None) -> torch.device:
+    device = None
+    for tensor in tensors:
+        if tensor is None:
+            continue
+        if not tensor.is_cuda:
+            raise ValueError("mlkit_b200 kernels require CUDA tensors")
+        if device is not None and tensor.device != device:
+            raise ValueError("all tensors of one call must live on one device")
+        device = tensor.device
+    assert device is not None
+    return device
+
+
+def integer_grid_of(values: Tensor) -> tuple[bool, float]:
+    """Whether ``values[c] == values[0] + c`` exactly with an integer ``values[0]``; and ``values[0]``."""
+    table = values.detach().float().cpu()
+    if table.numel() == 0:
+        return False, 0.0
+    low = float(table[0])
+    exact = low == int(low) and abs(low) <= 512 and bool(
+        torch.equal(table, low + torch.arange(table.numel(), dtype=torch.float32)))
+    return exact, low
+
+
+def packed_matvec(x: Tensor, packed: Tensor, scales: Tensor, values: Tensor, zeros: Tensor | None,
+                  bias: Tensor | None, out: Tensor, *, group: int, bits: int, integer_grid: bool = False,
+                  grid_minimum: float = 0.0, kernel: str = "auto", packed_row_stride: int | None = None,
+                  scale_row_stride: int | None = None) -> Tensor:
+    """``out[m, n] = sum_k x[m, k] * (values[code[n, k]] * scales[n, k // group] (+ zeros)) (+ bias[n])``.
+
+    ``x`` is ``[M, K]`` contiguous with ``M <= 8``; ``out`` is ``[M, N]`` in the dtype of ``x``.
+    """
+    device = _require_cuda(x, packed, scales, values, zeros, bias, out)
+    rows, width = x.shape
+    outputs = out.shape[-1]
+    if not (x.is_contiguous() and out.is_contiguous()):
+        raise ValueError("packed_matvec needs contiguous activations and output")
+    if out.dtype != x.dtype or out.shape[0] != rows:
+        raise ValueError("output must match the activations in dtype and rows")
+    if zeros is not None and zeros.dtype != scales.dtype:
+        raise ValueError("offsets must share the dtype of the scales")
+    if bias is not None and bias.dtype != x.dtype:
+        bias = bias.to(x.dtype)
+    if packed_row_stride is None:
+        packed_row_stride = width * bits // 8
+    if scale_row_stride is None:
+        scale_row_stride = scales.stride(0) if scales.dim() == 2 else -(-width // group)
+    with torch.cuda.device(device):
+        status = _native.library().mkb_gemv_ex(
+            x.data_ptr(), packed.data_ptr(), scales.data_ptr(), values.data_ptr(), _pointer(zeros),
+            _pointer(bias), out.data_ptr(), rows, outputs, width, group, bits, values.numel(),
+            _tag(x.dtype, "activation"), _tag(scales.dtype, "scale"), packed_row_stride,
+            scale_row_stride, int(integer_grid), float(grid_minimum), KERNEL_CHOICES[kernel],
+            _stream(device))
+    _native.check(status, "packed_matvec")
+    return out
+
+
+def dequantize(packed: Tensor, scales: Tensor | None, values: Tensor | None, zeros: Tensor | None, *,
+               shape: tuple[int, int], group: int, bits: int, dtype: torch.dtype | None = torch.float16,
+               codes: bool = False) -> tuple[Tensor | None, Tensor | None]:
+    """Bit-exact reconstruction of a packed weight; returns ``(weight or None, codes or None)``."""
+    device = _require_cuda(packed, scales, values, zeros)
+    rows, width = shape
+    weight = None if dtype is None else torch.empty(shape, device=device, dtype=dtype)
+    unpacked = torch.empty(shape, device=device, dtype=torch.uint8) if codes else None
+    if weight is None and unpacked is None:
+        raise ValueError("dequantize needs at least one output")
+    if weight is not None and (scales is None or values is None):
+        raise ValueError("a dense weight needs scales and values")
+    if rows * width == 0:
+        return weight, unpacked
+    if scales is not None and not scales.is_contiguous():
+        raise ValueError("scales must be contiguous")
+    stride = 0 if scales is None else (scales.stride(0) if scales.dim() == 2 else -(-width // group))
+    with torch.cuda.device(device):
+        status = _native.library().mkb_dequant(
+            packed.data_ptr(), _pointer(scales), _pointer(values), _pointer(zeros), _pointer(weight),
+            _pointer(unpacked), rows, width, group, bits, 0 if values is None else values.numel(),
+            _native.F32 if scales is None else _tag(scales.dtype, "scale"),
+            _native.F16 if dtype is None else _tag(dtype, "output"), stride, _stream(device))
+    _native.check(status, "dequantize")
+    return weight, unpacked
+
+
+def dequantize_rows(packed: Tensor, scales: Tensor, values: Tensor, zeros: Tensor | None, rows: Tensor, *,
+                    shape: tuple[int, int], group: int, bits: int, dtype: torch.dtype) -> Tensor:
+    """Reconstruct the listed rows only: ``out[i] = weight[rows[i]]``."""
+    device = _require_cuda(packed, scales, values, zeros, rows)
+    total, width = shape
+    rows = rows.reshape(-1).to(torch.int64).contiguous()
+    out = torch.empty((rows.numel(), width), device=device, dtype=dtype)
+    if rows.numel() == 0:
+        return out
+    with torch.cuda.device(device):
+        status = _native.library().mkb_dequant_rows(
+            packed.data_ptr(), scales.data_ptr(), values.data_ptr(), _pointer(zeros), rows.data_ptr(),
+            out.data_ptr(), rows.numel(), total, width, group, bits, values.numel(),
+            _tag(scales.dtype, "scale"), _tag(dtype, "output"), scales.stride(0), _stream(device))
+    _native.check(status, "dequantize_rows")
+    return out
+
+
+def structured_transform(x: Tensor, *, factor: int, power: int, basis: Tensor | None = None,
+                         signs: Tensor | None = None, inverse: bool = False, normalize: bool = True,
+                         out: Tensor | None = None) -> Tensor:
+    """``(basis kron H_power)(x * signs)`` over the last axis, one fused launch; dtype preserved."""
+    device = _require_cuda(x, basis, signs, out)
+    width = x.shape[-1]
+    if factor * power != width:
+        raise ValueError("factor * power must equal the transform width")
+    source = x if x.is_contiguous() else x.contiguous()
+    if out is None:
+        out = torch.empty_like(source)
+    if signs is not None and (signs.dtype != torch.int8 or signs.numel() != width):
+        raise ValueError("signs must be an int8 vector of the transform width")
+    if basis is not None and (basis.dtype != torch.float32 or not basis.is_contiguous()):
+        raise ValueError("basis must be a contiguous fp32 matrix")
+    rows = source.numel() // width if width else 0
+    with torch.cuda.device(device):
+        status = _native.library().mkb_hadamard(
+            source.data_ptr(), _pointer(signs), _pointer(basis), out.data_ptr(), rows, width, factor,
+            power, _tag(x.dtype, "activation"), int(inverse), int(normalize), _stream(device))
+    _native.check(status, "structured_transform")
+    return out
