@@ -1,0 +1,342 @@
+"""Packed execution of quantised linear layers: ``PackedLinear``, ``PackedEmbedding``, ``optimize``.
+
+Drop-in counterparts of ``src/mlkit/inference/packed_linear.py`` (``PackedLinear`` ``:41-245``,
+``PackedEmbedding`` ``:248-287``, ``packed_compatible`` ``:290-304``), ``layout_for`` /
+``PackedLayout`` (``src/mlkit/kernels/packed_linear.py:43-79``), ``optimize``
+(``src/mlkit/inference/optimization.py:11-100``) and ``benchmark``
+(``src/mlkit/inference/benchmarking.py:17-71``).  Buffer names, attributes, dispatch rule (at most
+eight input rows take the fused matvec, more rows reconstruct the dense weight and use a matrix
+product) and error behaviour follow the reference; every device computation goes through
+``libmlkit_b200`` and there is no Triton and no CPU path.
+"""
+
+import copy
+import math
+import statistics
+import time
+from collections.abc import Callable
+from dataclasses import asdict, dataclass
+from typing import Any
+
+import torch
+import torch.nn.functional as functional
+from torch import Tensor, nn
+
+from mlkit_b200 import kernels
+from mlkit_b200.models import Model, QModel
+from mlkit_b200.quantization import Q, pack
+
+SCALE_STORAGE_DTYPES = {"fp16": torch.float16, "bf16": torch.bfloat16}
+MAXIMUM_FUSED_ROWS = 8
+MAXIMUM_CODE_BITS = 8
+MAXIMUM_TILE_CODES = 128
+MINIMUM_TILE_CODES = 16
+
+
+@dataclass(frozen=True)
+class PackedLayout:
+    """Word structure of a packed stream: the fewest whole bytes that hold whole codes."""
+
+    bits: int
+    bytes_per_word: int
+    codes_per_word: int
+    tile_words: int
+
+    @property
+    def tile_codes(self) -> int:
+        return self.tile_words * self.codes_per_word
+
+    def row_bytes(self, input_width: int) -> int:
+        return input_width // self.codes_per_word * self.bytes_per_word
+
+    def tiles_per_row(self, input_width: int) -> int:
+        return -(-input_width // self.tile_codes)
+
+
+def layout_for(bits: int, input_width: int, group: int) -> PackedLayout | None:
+    """The layout a layer can run the fused matvec with, or ``None`` when a row or a scale group
+    would split a packing word (such layers keep packed storage but always reconstruct)."""
+    if not 1 <= bits <= MAXIMUM_CODE_BITS:
+        return None
+    shared = math.gcd(bits, 8)
+    bytes_per_word, codes_per_word = bits // shared, 8 // shared
+    if input_width % codes_per_word or group % codes_per_word:
+        return None
+    words = group // codes_per_word
+    tile_words = min(MAXIMUM_TILE_CODES // codes_per_word, words & -words)
+    if tile_words * codes_per_word < MINIMUM_TILE_CODES:
+        return None
+    return PackedLayout(bits, bytes_per_word, codes_per_word, tile_words)
+
+
+def packed_compatible(quantized: Q) -> bool:
+    """A complete scalar codec of at most eight bits, original column order, group-aligned refits."""
+    if quantized.codec not in {"scaled", "feedback"}:
+        return False
+    group = quantized.params["group"]
+    bits = quantized.metadata.get("code_bits")
+    return (isinstance(bits, int) and 1 <= bits <= MAXIMUM_CODE_BITS and quantized.codes is not None
+            and quantized.params["values"].numel() <= 2**bits and quantized.params.get("offset", 0) == 0
+            and quantized.params.get("permutation") is None and quantized.params.get("refit", group) % group == 0)
+
+
+def preserve_input_processing(original: nn.Module, replacement: nn.Module) -> None:
+    """Carry online input transforms (pre-hooks and their ``_mlkit_*`` buffers) to the substitute."""
+    replacement._forward_pre_hooks = original._forward_pre_hooks.copy()
+    replacement._forward_pre_hooks_with_kwargs = original._forward_pre_hooks_with_kwargs.copy()
+    for name, value in original.named_buffers(recurse=False):
+        if name.startswith("_mlkit_"):
+            replacement.register_buffer(name, value.detach().clone())
+
+
+@torch.library.custom_op("mlkit_b200::packed_matvec", mutates_args=())
+def _packed_matvec_op(x: Tensor, packed: Tensor, scales: Tensor, values: Tensor, zeros: Tensor | None,
+                      bias: Tensor | None, outputs: int, group: int, bits: int, integer_grid: bool,
+                      grid_minimum: float) -> Tensor:
+    out = x.new_empty((x.shape[0], outputs))
+    kernels.packed_matvec(x, packed, scales, values, zeros, bias, out, group=group, bits=bits,
+                          integer_grid=integer_grid, grid_minimum=grid_minimum)
+    return out
+
+
+@_packed_matvec_op.register_fake
+def _(x, packed, scales, values, zeros, bias, outputs, group, bits, integer_grid, grid_minimum):
+    return x.new_empty((x.shape[0], outputs))
+
+
+class PackedLinear(nn.Module):
+    """Scalar-grid codes of one to eight bits executed from their packed stream.
+
+    Up to ``maximum_fused_rows`` input rows go through the packed matvec kernel.  More rows
+    reconstruct the dense weight (bit-exact dequantisation kernel) and use a matrix product.
+    """
+
+    packed: Tensor
+    scales: Tensor
+    values: Tensor
+    zeros: Tensor | None
+    bias: Tensor | None
+    _dense_weight: Tensor | None
+
+    def __init__(self, original: nn.Linear, quantized: Q, *, cache_dense: bool = False) -> None:
+        super().__init__()
+        if not packed_compatible(quantized):
+            raise ValueError(
+                "PackedLinear requires a complete scalar-grid codec of at most eight bits in "
+                "its original column order with refit boundaries aligned to scale groups")
+        device = original.weight.device
+        if device.type != "cuda":
+            raise ValueError("PackedLinear requires CUDA weights")
+        self.in_features, self.out_features = original.in_features, original.out_features
+        self.group = int(quantized.params["group"])
+        self.code_bits = int(quantized.metadata["code_bits"])
+        self.storage_dtype = original.weight.dtype
+        self.cache_dense = cache_dense
+        scales = quantized.params["scales"]
+        scale_dtype = SCALE_STORAGE_DTYPES.get(str(quantized.metadata.get("scale_fmt")), scales.dtype)
+        zero = quantized.params.get("zero")
+        self.register_buffer("packed", pack(quantized.codes, self.code_bits).to(device))
+        self.register_buffer("scales", scales.to(device=device, dtype=scale_dtype).contiguous())
+        self.register_buffer("values", quantized.params["values"].to(device=device, dtype=torch.float32).contiguous())
+        self.register_buffer("zeros", None if zero is None else zero.to(device=device, dtype=scale_dtype).contiguous())
+        self.register_buffer("bias", None if original.bias is None else original.bias.detach().clone())
+        self.register_buffer("_dense_weight", None, persistent=False)
+        levels = quantized.params["values"].detach().cpu().float()
+        steps = levels.diff()
+        self.uniform_grid = bool(len(steps) and torch.allclose(steps, steps[0].expand_as(steps)))
+        self.grid_minimum = float(levels[0])
+        self.grid_step = float(steps[0]) if len(steps) else 1.0
+        # the arithmetic decode is only taken when the table is an integer ramp, bit for bit
+        self.integer_grid, _ = kernels.integer_grid_of(levels)
+        self.layout = layout_for(self.code_bits, self.in_features, self.group)
+        self.maximum_fused_rows = 0 if self.layout is None else MAXIMUM_FUSED_ROWS
+        preserve_input_processing(original, self)
+
+    def _apply(self, fn: Callable[[Tensor], Tensor], recurse: bool = True) -> "PackedLinear":
+        self._dense_weight = None
+        return super()._apply(fn, recurse)
+
+    @property
+    def weight(self) -> Tensor:
+        """The dense reconstruction in the storage dtype: fp32 multiply (and add), one rounding."""
+        if self._dense_weight is not None:
+            return self._dense_weight
+        dense, _ = kernels.dequantize(self.packed, self.scales, self.values, self.zeros,
+                                      shape=(self.out_features, self.in_features), group=self.group,
+                                      bits=self.code_bits, dtype=self.storage_dtype)
+        if self.cache_dense:
+            self._dense_weight = dense
+        return dense
+
+    def forward(self, inputs: Tensor) -> Tensor:
+        width = self.in_features
+        if inputs.shape[-1] != width:
+            raise ValueError("input width does not match the packed linear")
+        if not inputs.is_cuda:
+            raise ValueError("packed inference requires CUDA inputs")
+        rows = inputs.numel() // width
+        if rows > self.maximum_fused_rows or rows == 0:
+            return functional.linear(inputs, self.weight.to(inputs.dtype), self.bias)
+        if inputs.requires_grad and torch.is_grad_enabled():
+            raise RuntimeError("packed CUDA inference does not support autograd")
+        flat = inputs.reshape(rows, width)
+        if not flat.is_contiguous():
+            flat = flat.contiguous()
+        bias = self.bias
+        if bias is not None and bias.dtype != inputs.dtype:
+            bias = bias.to(inputs.dtype)
+        if torch.compiler.is_compiling():
+            out = _packed_matvec_op(flat, self.packed, self.scales, self.values, self.zeros, bias,
+                                    self.out_features, self.group, self.code_bits, self.integer_grid,
+                                    self.grid_minimum)
+        else:
+            out = inputs.new_empty((rows, self.out_features))
+            kernels.packed_matvec(flat, self.packed, self.scales, self.values, self.zeros, bias, out,
+                                  group=self.group, bits=self.code_bits, integer_grid=self.integer_grid,
+                                  grid_minimum=self.grid_minimum)
+        return out.view(inputs.shape[:-1] + (self.out_features,))
+
+    def extra_repr(self) -> str:
+        return (f"in_features={self.in_features}, out_features={self.out_features}, bits={self.code_bits}, "
+                f"group={self.group}, fused={'yes' if self.layout is not None else 'no'}")
+
+
+class PackedEmbedding(nn.Module):
+    """Token embedding read from the packed codes of a tied output projection; only the requested
+    rows are decoded.  The projection is referenced, not registered: the model owns it as its head."""
+
+    def __init__(self, projection: PackedLinear, original: nn.Embedding) -> None:
+        super().__init__()
+        if projection.layout is None:
+            raise ValueError("a packed embedding requires rows that hold whole packing words")
+        self._projection = (projection,)
+        self.num_embeddings, self.embedding_dim = projection.out_features, projection.in_features
+        self.padding_idx = original.padding_idx
+
+    @property
+    def projection(self) -> PackedLinear:
+        return self._projection[0]
+
+    @property
+    def weight(self) -> Tensor:
+        return self.projection.weight
+
+    def forward(self, indices: Tensor) -> Tensor:
+        head = self.projection
+        rows = kernels.dequantize_rows(head.packed, head.scales, head.values, head.zeros, indices.reshape(-1),
+                                       shape=(self.num_embeddings, self.embedding_dim), group=head.group,
+                                       bits=head.code_bits, dtype=head.storage_dtype)
+        return rows.view(*indices.shape, self.embedding_dim)
+
+
+def optimize(model: Model | nn.Module, backend: str = "auto", *, compile: bool = False,
+             mode: str = "reduce-overhead", cache_dense: bool = False, inplace: bool = False) -> Model:
+    """Choose dense or packed execution; packed swaps every compatible ``nn.Linear`` of a ``QModel``
+    for a ``PackedLinear`` and a tied embedding for a ``PackedEmbedding``."""
+    if backend not in {"auto", "dense", "packed"}:
+        raise ValueError("backend must be auto, dense, or packed")
+    wrapped = model if isinstance(model, Model) else Model(model)
+    if isinstance(wrapped, QModel):
+        _ = wrapped.model_bpw
+    if backend == "auto":
+        backend = "packed" if isinstance(wrapped, QModel) else "dense"
+    if backend == "packed":
+        if not isinstance(wrapped, QModel):
+            raise ValueError("packed inference requires a QModel with codec state")
+        substitutes: dict[str, nn.Module] = {}
+        for name, quantized in wrapped.quantized.items():
+            target = wrapped.module.get_submodule(name)
+            if isinstance(target, nn.Linear) and packed_compatible(quantized):
+                substitutes[name] = PackedLinear(target, quantized, cache_dense=cache_dense)
+        count = len(substitutes)
+        for parameter_name, layer_name in wrapped.tied_weights.items():
+            owner_name = parameter_name.rpartition(".")[0]
+            owner = wrapped.module.get_submodule(owner_name)
+            head = substitutes.get(layer_name)
+            if isinstance(owner, nn.Embedding) and isinstance(head, PackedLinear) and head.layout is not None:
+                substitutes[owner_name] = PackedEmbedding(head, owner)
+        if inplace:
+            for name, substitute in substitutes.items():
+                if name:
+                    wrapped.module.set_submodule(name, substitute)
+                else:
+                    wrapped.module = substitute
+                    wrapped.architecture.model = substitute
+            converted = wrapped
+        else:
+            memo = {id(wrapped.module.get_submodule(name)): substitute for name, substitute in substitutes.items()}
+            converted = copy.deepcopy(wrapped, memo)
+            for module in converted.module.modules():
+                if isinstance(module, PackedLinear):
+                    module._forward_pre_hooks = copy.deepcopy(module._forward_pre_hooks, memo)
+        converted.execution_backend = f"packed:{count}"
+    else:
+        converted = wrapped if inplace else copy.deepcopy(wrapped)
+        converted.execution_backend = "dense"
+    if not inplace or backend == "packed":
+        for attribute in ("_compiled_call", "_compiled_call_impl", "_last_compile_config", "_cache"):
+            if attribute in converted.module.__dict__:
+                delattr(converted.module, attribute)
+    if compile:
+        configuration = getattr(converted.module, "generation_config", None)
+        if configuration is not None and hasattr(converted.module, "get_compiled_call"):
+            from transformers import CompileConfig
+
+            configuration = copy.deepcopy(configuration)
+            configuration.cache_implementation = "static"
+            configuration.compile_config = CompileConfig(mode=mode)
+            converted.module.generation_config = configuration
+        else:
+            converted.module.compile(mode=mode)
+        converted.execution_backend += "+compiled"
+    return converted
+
+
+@dataclass
+class BenchmarkResult:
+    median_ms: float
+    minimum_ms: float
+    percentile_95_ms: float
+    repetitions: int
+    device: str
+    peak_memory_bytes: int | None
+
+    def to_dict(self) -> dict[str, Any]:
+        return asdict(self)
+
+
+def benchmark(operation: Callable[[], Any], *, warmup: int = 10, repetitions: int = 50,
+              inference_mode: bool = True) -> BenchmarkResult:
+    """Wall-clock samples with a device synchronisation on both sides of every call."""
+    if warmup < 0 or repetitions < 1:
+        raise ValueError("warmup must be nonnegative and repetitions must be positive")
+    device = torch.device("cuda", torch.cuda.current_device())
+    samples = []
+    with torch.inference_mode(inference_mode):
+        for _ in range(warmup):
+            operation()
+        torch.cuda.synchronize(device)
+        torch.cuda.reset_peak_memory_stats(device)
+        for _ in range(repetitions):
+            torch.cuda.synchronize(device)
+            start = time.perf_counter()
+            operation()
+            torch.cuda.synchronize(device)
+            samples.append((time.perf_counter() - start) * 1000)
+    ordered = sorted(samples)
+    return BenchmarkResult(statistics.median(samples), ordered[0],
+                           ordered[min(len(ordered) - 1, int(len(ordered) * 0.95))], repetitions, str(device),
+                           torch.cuda.max_memory_allocated(device))
+
+
+def benchmark_model(model: Model | nn.Module, batch: Any, **options: Any) -> BenchmarkResult:
+    wrapped = model if isinstance(model, Model) else Model(model)
+
+    def run() -> Any:
+        if isinstance(batch, dict):
+            return wrapped(**batch)
+        if isinstance(batch, (tuple, list)):
+            return wrapped(*batch)
+        return wrapped(batch)
+
+    return benchmark(run, **options)

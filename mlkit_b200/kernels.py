@@ -51,7 +51,7 @@ def integer_grid_of(values: Tensor) -> tuple[bool, float]:
         return False, 0.0
     low = float(table[0])
     exact = low == int(low) and abs(low) <= 512 and bool(
-        torch.equal(table, low + torch.arange(table.numel(), dtype=torch.float32)))
+        torch.equal(table, low + torch.arange(table.numel(), dtype=torch.float32, device="cpu")))
     return exact, low
 
 

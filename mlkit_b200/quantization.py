@@ -258,11 +258,11 @@ class _GridFactory:
         if not 2 <= bits <= 16:
             raise ValueError("signed integer grids support 2 through 16 bits")
         low, high = -(2 ** (bits - 1)), 2 ** (bits - 1) - 1
-        levels = torch.arange(low, high + 1, dtype=torch.float32)
+        levels = torch.arange(low, high + 1, dtype=torch.float32, device="cpu")
         return Grid(lambda x: x.round().clamp(low, high), bits, values=levels, name=f"int{bits}", integer=True)
 
     def values(self, values: Any, *, bits: builtins.int | None = None, name: str = "values") -> Grid:
-        levels = torch.as_tensor(values, dtype=torch.float32).flatten().sort().values
+        levels = torch.as_tensor(values, dtype=torch.float32).detach().cpu().flatten().sort().values
         if not levels.numel() or not torch.isfinite(levels).all():
             raise ValueError("a scalar codebook must contain finite values")
         width = max(1, math.ceil(math.log2(levels.numel()))) if bits is None else bits
@@ -350,7 +350,8 @@ class Ctx:
 
 
 def _fp32_reciprocal(value: float) -> float:
-    return float(torch.tensor(1.0, dtype=torch.float32) / torch.tensor(value, dtype=torch.float32))
+    one = torch.tensor(1.0, dtype=torch.float32, device="cpu")
+    return float(one / torch.tensor(value, dtype=torch.float32, device="cpu"))
 
 
 def _group_range(weight: Tensor, group: int) -> tuple[Tensor, Tensor]:

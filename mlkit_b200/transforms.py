@@ -25,9 +25,9 @@ def _is_prime(value: int) -> bool:
 
 def _jacobsthal(field: int) -> Tensor:
     """chi(i - j) over GF(field): 0 on the diagonal, +1 for squares, -1 otherwise."""
-    index = torch.arange(field)
+    index = torch.arange(field, device="cpu")
     difference = (index[:, None] - index[None, :]) % field
-    square = torch.zeros(field)
+    square = torch.zeros(field, device="cpu")
     square[(index[1:] ** 2) % field] = 1
     return torch.where(difference == 0, 0.0, 2 * square[difference] - 1)
 
@@ -36,16 +36,16 @@ def _jacobsthal(field: int) -> Tensor:
 def paley_matrix(order: int) -> Tensor:
     """Orthonormal Hadamard matrix from a prime-field Paley design (construction I or II)."""
     if _is_prime(order - 1) and (order - 1) % 4 == 3:
-        matrix = torch.ones(order, order)
+        matrix = torch.ones(order, order, device="cpu")
         matrix[1:, 0] = -1
-        matrix[1:, 1:] = _jacobsthal(order - 1) + torch.eye(order - 1)
+        matrix[1:, 1:] = _jacobsthal(order - 1) + torch.eye(order - 1, device="cpu")
         return matrix / math.sqrt(order)
     field = order // 2 - 1
     if order % 2 == 0 and _is_prime(field) and field % 4 == 1:
-        conference = torch.ones(field + 1, field + 1)
+        conference = torch.ones(field + 1, field + 1, device="cpu")
         conference[0, 0] = 0
         conference[1:, 1:] = _jacobsthal(field)
-        eye = torch.eye(field + 1)
+        eye = torch.eye(field + 1, device="cpu")
         top = torch.cat((conference + eye, conference - eye), dim=1)
         bottom = torch.cat((conference - eye, -conference - eye), dim=1)
         return torch.cat((top, bottom), dim=0) / math.sqrt(order)
@@ -74,7 +74,7 @@ def transform_factor(width: int) -> tuple[int, int, Tensor | None]:
             return odd * multiplier, power // multiplier, paley_matrix(odd * multiplier)
         except ValueError:
             continue
-    index = torch.arange(odd, dtype=torch.float64)
+    index = torch.arange(odd, dtype=torch.float64, device="cpu")
     matrix = torch.cos(math.pi / odd * (index[None, :] + 0.5) * index[:, None])
     matrix[0] *= 1 / math.sqrt(odd)
     matrix[1:] *= math.sqrt(2 / odd)
