@@ -1,0 +1,356 @@
+"""Benchmark of the packed INT4-g128 matvec path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One process per GPU (for N > 1 launch under ``python -m torch.distributed.run``).  Rank 0 prints one
+JSON line.
+
+N = 1: the workload is the seven block linears of a Llama-3-8B-shaped decoder block (q, k, v, o,
+gate, up, down; INT4, group 128, fp16 scales; weights N(0, 0.02) from a seed, RTN-quantised on the
+device by this package's own ``mk.int(4, group=128)``), with 1, 2, 4 and 8 activation rows.  A step is
+one pass of the packed matvec over ``BLOCKS`` distinct blocks x 7 linears x 4 row counts.  The blocks
+together hold ~0.9 GB of packed weights, so no weight is served from L2 twice in a row.
+
+N > 1: the 70B-shaped tensor-parallel decode step of ``mlkit_b200.tp`` (see ``decode_workload``).
+
+``value`` is algorithmic GB/s with every input resident in HBM; ``e2e`` is the same pass through the
+public module call (``PackedLinear.forward``) with activations coming from pinned host memory and
+results returned to it inside the timed region.  ``--impl reference`` times the reference's CPU route
+(unpack, reconstruct, ``F.linear``) through ``oracle/cpu_path.py`` on the host cores.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+LLAMA8B = {"q": (4096, 4096), "k": (1024, 4096), "v": (1024, 4096), "o": (4096, 4096),
+           "gate": (14336, 4096), "up": (14336, 4096), "down": (4096, 14336)}
+ROW_COUNTS = (1, 2, 4, 8)
+BLOCKS = 8
+BITS, GROUP = 4, 128
+METRIC = "packed_int4_g128_gemv_hbm_gbps"
+
+
+def gemv_bytes(out_rows: int, width: int, rows_in: int) -> int:
+    """Algorithmic bytes of one INT4-g128 matvec: codes + fp16 scales + activations + outputs + table."""
+    return out_rows * width * BITS // 8 + out_rows * (width // GROUP) * 2 + rows_in * width * 2 + rows_in * out_rows * 2 + 64
+
+
+def pass_bytes(blocks: int) -> int:
+    return blocks * sum(gemv_bytes(n, k, m) for (n, k) in LLAMA8B.values() for m in ROW_COUNTS)
+
+
+def peaks() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int) -> None:
+        self.device_index = device_index
+        self.process = None
+
+    def __enter__(self) -> "ClockSampler":
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.process = None
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.summary = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.process is None:
+            return
+        time.sleep(0.25)
+        self.process.terminate()
+        try:
+            out, _ = self.process.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+            out, _ = self.process.communicate()
+        clocks, reasons, maximum = [], set(), None
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            fields = [f.strip() for f in line.split(",")]
+            if len(fields) < 9:
+                continue
+            try:
+                clocks.append(float(fields[1]))
+                maximum = float(fields[2])
+            except ValueError:
+                continue
+            for name, field in zip(names, fields[5:9]):
+                if field.lower().startswith("active"):
+                    reasons.add(name)
+        if clocks:
+            self.summary = {"sm_mhz": statistics.median(clocks), "sm_max_mhz": maximum, "reasons": sorted(reasons),
+                            "samples": len(clocks)}
+
+
+def build_blocks(device: torch.device, blocks: int):
+    """``blocks`` decoder blocks of seven ``PackedLinear`` layers, RTN-quantised on the device."""
+    import mlkit_b200 as mk
+    from torch import nn
+
+    generator = torch.Generator(device=device).manual_seed(1234)
+    fmt = mk.int(BITS, group=GROUP)
+    result = []
+    for _ in range(blocks):
+        layers = {}
+        for name, (out_rows, width) in LLAMA8B.items():
+            weight = (torch.randn(out_rows, width, generator=generator, device=device) * 0.02).half()
+            linear = nn.Linear(width, out_rows, bias=False, device=device, dtype=torch.float16)
+            with torch.no_grad():
+                linear.weight.copy_(weight)
+            q = fmt(weight.float(), mk.Ctx(name, device=device))
+            layers[name] = mk.PackedLinear(linear, q)
+            del linear, weight, q
+        result.append(layers)
+    torch.cuda.empty_cache()
+    return result
+
+
+def run_pass_resident(blocks, inputs, outputs) -> int:
+    """One step with everything in HBM: bound launches on preallocated outputs.  Returns launches."""
+    launches = 0
+    for rows in ROW_COUNTS:
+        for layers in blocks:
+            for name, layer in layers.items():
+                layer._plan(torch.float16)(inputs[rows][layer.in_features], outputs[rows][layer.out_features])
+                launches += 1
+    return launches
+
+
+def capture_pass(blocks, inputs, outputs) -> tuple[torch.cuda.CUDAGraph, int]:
+    """The resident step as one CUDA graph (decode loops are launch-bound; the reference itself relies
+    on graph capture through ``torch.compile(mode="reduce-overhead")`` for generation)."""
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        run_pass_resident(blocks, inputs, outputs)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            launches = run_pass_resident(blocks, inputs, outputs)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    return graph, launches
+
+
+def run_pass_e2e(blocks, host_inputs, host_outputs, device) -> tuple[int, int]:
+    """One step through ``PackedLinear.forward`` with host-resident activations and results."""
+    h2d = d2h = 0
+    for rows in ROW_COUNTS:
+        for layers in blocks:
+            for name, layer in layers.items():
+                x_host = host_inputs[rows][layer.in_features]
+                x = x_host.to(device, non_blocking=True)
+                y = layer(x)
+                host_outputs[rows][layer.out_features].copy_(y, non_blocking=True)
+                h2d += x_host.numel() * 2
+                d2h += y.numel() * 2
+    return h2d, d2h
+
+
+def per_layer_table(blocks, inputs, outputs, peak: float) -> dict:
+    """Average launch duration per layer shape and row count (CUDA events around the launches of all
+    blocks, which keeps every weight cold in L2), as algorithmic GB/s and roofline fraction."""
+    table = {}
+    for name, (out_rows, width) in LLAMA8B.items():
+        if name in ("v", "up"):
+            continue
+        for rows in ROW_COUNTS:
+            def launch_all():
+                for layers in blocks:
+                    layers[name]._plan(torch.float16)(inputs[rows][width], outputs[rows][out_rows])
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                launch_all()
+                torch.cuda.synchronize()
+                with torch.cuda.graph(graph, stream=side):
+                    launch_all()
+            torch.cuda.current_stream().wait_stream(side)
+            graph.replay()
+            torch.cuda.synchronize()
+            best = None
+            for _ in range(5):
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record()
+                graph.replay()
+                stop.record()
+                torch.cuda.synchronize()
+                elapsed = start.elapsed_time(stop) / len(blocks)
+                best = elapsed if best is None else min(best, elapsed)
+            gbps = gemv_bytes(out_rows, width, rows) / best / 1e6
+            table[f"{name}_{width}x{out_rows}_M{rows}"] = {"us": round(best * 1e3, 3), "gbps": round(gbps, 1),
+                                                           "frac": round(gbps / peak, 4)}
+    return table
+
+
+def cpu_reference_layers(blocks: int = 1):
+    """Host copies of the block linears for the CPU route (random codes: arithmetic cost is value-blind)."""
+    generator = torch.Generator().manual_seed(99)
+    layers = []
+    for _ in range(blocks):
+        for name, (out_rows, width) in LLAMA8B.items():
+            layers.append({
+                "packed": torch.randint(0, 256, (out_rows * width * BITS // 8,), dtype=torch.uint8, generator=generator),
+                "scales": (torch.rand(out_rows, width // GROUP, generator=generator) * 0.01 + 0.001).half(),
+                "values": torch.arange(-8, 8, dtype=torch.float32), "group": GROUP, "bits": BITS,
+                "shape": (out_rows, width),
+            })
+    return layers
+
+
+def time_cpu_route(repetitions: int, warmup: int):
+    """Seconds per pass of unpack + reconstruct + F.linear over one block's seven linears, M = 1."""
+    from oracle import cpu_path
+
+    layers = cpu_reference_layers(1)
+    seconds, threads = cpu_path.time_reconstruct_plus_matmul(layers, rows_in=1, repetitions=repetitions, warmup=warmup)
+    bytes_per_pass = sum(gemv_bytes(n, k, 1) for (n, k) in LLAMA8B.values())
+    return seconds, threads, bytes_per_pass
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=10)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = parser.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        seconds, threads, bytes_per_pass = time_cpu_route(max(1, args.steps), max(0, args.warmup))
+        value = bytes_per_pass / seconds / 1e9
+        print(json.dumps({
+            "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "llama3-8b block linears int4 g128 (q,k,v,o,gate,up,down), M=1, CPU reconstruct+matmul"},
+            "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
+                             "sample": "one decoder block (7 linears, 109 MB packed), M=1, per step"},
+            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+        from mlkit_b200 import tp_bench
+
+        tp_bench.run(args, rank, world, device, peaks())
+        dist.destroy_process_group()
+        return
+
+    peak, peak_kind = peaks()
+    blocks = build_blocks(device, BLOCKS)
+    generator = torch.Generator(device=device).manual_seed(7)
+    widths = sorted({k for (_, k) in LLAMA8B.values()})
+    outs = sorted({n for (n, _) in LLAMA8B.values()})
+    inputs = {m: {k: torch.randn(m, k, generator=generator, device=device).half() for k in widths} for m in ROW_COUNTS}
+    outputs = {m: {n: torch.empty(m, n, device=device, dtype=torch.float16) for n in outs} for m in ROW_COUNTS}
+    host_inputs = {m: {k: inputs[m][k].cpu().pin_memory() for k in widths} for m in ROW_COUNTS}
+    host_outputs = {m: {n: torch.empty(m, n, dtype=torch.float16).pin_memory() for n in outs} for m in ROW_COUNTS}
+
+    # ---- resident-input timing: W warm-up steps, then exactly K steps between two events ----
+    graph, launches_per_step = capture_pass(blocks, inputs, outputs)
+    for _ in range(max(3, args.warmup)):
+        graph.replay()
+    torch.cuda.synchronize()
+    with ClockSampler(local_rank) as sampler:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(args.steps):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        resident_ms = start.elapsed_time(stop) / args.steps
+        launches = launches_per_step * args.steps
+        # the same step launched eagerly (host launch path included)
+        start.record()
+        for _ in range(args.steps):
+            run_pass_resident(blocks, inputs, outputs)
+        stop.record()
+        torch.cuda.synchronize()
+        eager_ms = start.elapsed_time(stop) / args.steps
+        # ---- end-to-end timing through the module call with host activations ----
+        with torch.inference_mode():
+            for _ in range(max(3, args.warmup)):
+                run_pass_e2e(blocks, host_inputs, host_outputs, device)
+            torch.cuda.synchronize()
+            start.record()
+            for _ in range(args.steps):
+                h2d, d2h = run_pass_e2e(blocks, host_inputs, host_outputs, device)
+            stop.record()
+            torch.cuda.synchronize()
+            e2e_ms = start.elapsed_time(stop) / args.steps
+        table = per_layer_table(blocks, inputs, outputs, peak)
+    step_bytes = pass_bytes(BLOCKS)
+    value = step_bytes / resident_ms / 1e6
+    gate = [table[f"gate_4096x14336_M{m}"] for m in ROW_COUNTS]
+    gate_bytes = statistics.mean(gemv_bytes(14336, 4096, m) for m in ROW_COUNTS)
+    gate_us = statistics.mean(entry["us"] for entry in gate)
+    achieved = gate_bytes / gate_us / 1e3
+
+    cpu_seconds, cpu_threads, cpu_bytes = time_cpu_route(repetitions=3, warmup=1)
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": resident_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"llama3-8b block linears int4 g128 (q,k,v,o,gate,up,down) x M in {list(ROW_COUNTS)} x {BLOCKS} distinct blocks",
+                   "l2": f"inputs larger than L2: {BLOCKS} blocks = {BLOCKS * 113} MB of packed weights cycled",
+                   "pct_of_8tbs": round(value / 8000 * 100, 2), "launch": "one CUDA graph per step",
+                   "eager_ms_per_step": round(eager_ms, 4)},
+        "e2e": {"value": step_bytes / e2e_ms / 1e6, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "clocks": sampler.summary,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind,
+                     "kernel": "gemv_tiled_kernel<4, raw> on gate/up 4096->14336, mean over M in {1,2,4,8}",
+                     "bytes_per_launch": gate_bytes, "us_per_launch": gate_us},
+        "per_layer": table,
+        "cpu_baseline": {"value": cpu_bytes / cpu_seconds / 1e9, "unit": "GB/s", "cores": cpu_threads, "kind": "port",
+                         "sample": "one decoder block (7 linears, 109 MB packed), M=1, median of 3 passes"},
+    }
+    traffic_file = ROOT / "profiles" / "gemv_tiled_gate_traffic.json"
+    if traffic_file.exists():
+        line["roofline"]["traffic"] = json.loads(traffic_file.read_text()).get("dram_bytes_per_launch")
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

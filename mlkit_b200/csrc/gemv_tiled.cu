@@ -549,7 +549,9 @@ int occupancy_for(Kernel kernel, size_t smem, int& ctas_per_sm) {
   std::lock_guard<std::mutex> guard(lock);
   auto found = cache.find(key);
   if (found != cache.end()) { ctas_per_sm = found->second; return MKB_OK; }
-  cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  // opt in to the device maximum once: a later, smaller request must not lower the limit again
+  cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            device_info().max_smem_optin);
   if (status != cudaSuccess) return cuda_fail(status, "gemv_tiled: shared memory opt-in");
   int blocks = 0;
   status = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, kThreadsT, smem);

@@ -150,11 +150,30 @@ class PackedLinear(nn.Module):
         self.integer_grid, _ = kernels.integer_grid_of(levels)
         self.layout = layout_for(self.code_bits, self.in_features, self.group)
         self.maximum_fused_rows = 0 if self.layout is None else MAXIMUM_FUSED_ROWS
+        self._plans: dict[torch.dtype, kernels.MatvecPlan] = {}
         preserve_input_processing(original, self)
 
     def _apply(self, fn: Callable[[Tensor], Tensor], recurse: bool = True) -> "PackedLinear":
         self._dense_weight = None
+        self._plans = {}  # bound device pointers are stale once buffers move or change dtype
         return super()._apply(fn, recurse)
+
+    def __deepcopy__(self, memo: dict) -> "PackedLinear":
+        """Copy everything but the bound launch plans, which point into this instance's buffers."""
+        duplicate = self.__class__.__new__(self.__class__)
+        memo[id(self)] = duplicate
+        for key, value in self.__dict__.items():
+            duplicate.__dict__[key] = {} if key == "_plans" else copy.deepcopy(value, memo)
+        return duplicate
+
+    def _plan(self, dtype: torch.dtype) -> "kernels.MatvecPlan":
+        plan = self._plans.get(dtype)
+        if plan is None:
+            plan = self._plans[dtype] = kernels.MatvecPlan(
+                self.packed, self.scales, self.values, self.zeros, self.bias, outputs=self.out_features,
+                width=self.in_features, group=self.group, bits=self.code_bits, dtype=dtype,
+                integer_grid=self.integer_grid, grid_minimum=self.grid_minimum)
+        return plan
 
     @property
     def weight(self) -> Tensor:
@@ -182,18 +201,17 @@ class PackedLinear(nn.Module):
         flat = inputs.reshape(rows, width)
         if not flat.is_contiguous():
             flat = flat.contiguous()
-        bias = self.bias
-        if bias is not None and bias.dtype != inputs.dtype:
-            bias = bias.to(inputs.dtype)
         if torch.compiler.is_compiling():
+            bias = self.bias
+            if bias is not None and bias.dtype != inputs.dtype:
+                bias = bias.to(inputs.dtype)
             out = _packed_matvec_op(flat, self.packed, self.scales, self.values, self.zeros, bias,
                                     self.out_features, self.group, self.code_bits, self.integer_grid,
                                     self.grid_minimum)
         else:
-            out = inputs.new_empty((rows, self.out_features))
-            kernels.packed_matvec(flat, self.packed, self.scales, self.values, self.zeros, bias, out,
-                                  group=self.group, bits=self.code_bits, integer_grid=self.integer_grid,
-                                  grid_minimum=self.grid_minimum)
+            if inputs.dtype not in kernels.DTYPE_TAGS:
+                raise ValueError(f"activation dtype {inputs.dtype} is not supported (fp16, bf16, fp32)")
+            out = self._plan(inputs.dtype)(flat, inputs.new_empty((rows, self.out_features)))
         return out.view(inputs.shape[:-1] + (self.out_features,))
 
     def extra_repr(self) -> str:

@@ -89,6 +89,47 @@ def packed_matvec(x: Tensor, packed: Tensor, scales: Tensor, values: Tensor, zer
     return out
 
 
+class MatvecPlan:
+    """The constant arguments of one layer's matvec, bound once.
+
+    The per-call work is what the reference's direct launcher leaves
+    (``src/mlkit/inference/packed_linear.py:181-245``): pass the activation and output pointers,
+    the row count and the current stream.  The plan holds raw device pointers, so it must be rebuilt
+    whenever the layer's buffers move (``PackedLinear._apply`` drops it).
+    """
+
+    __slots__ = ("function", "head", "tail", "outputs", "width", "dtype", "device", "device_index", "keep")
+
+    def __init__(self, packed: Tensor, scales: Tensor, values: Tensor, zeros: Tensor | None, bias: Tensor | None,
+                 *, outputs: int, width: int, group: int, bits: int, dtype: torch.dtype, integer_grid: bool,
+                 grid_minimum: float) -> None:
+        device = _require_cuda(packed, scales, values, zeros, bias)
+        if zeros is not None and zeros.dtype != scales.dtype:
+            raise ValueError("offsets must share the dtype of the scales")
+        if bias is not None and bias.dtype != dtype:
+            bias = bias.to(dtype)
+        self.function = _native.library().mkb_gemv
+        self.head = (packed.data_ptr(), scales.data_ptr(), values.data_ptr(), _pointer(zeros), _pointer(bias))
+        self.tail = (outputs, width, group, bits, values.numel(), _tag(dtype, "activation"),
+                     _tag(scales.dtype, "scale"), width * bits // 8,
+                     scales.stride(0) if scales.dim() == 2 else -(-width // group), int(integer_grid),
+                     float(grid_minimum))
+        self.outputs, self.width, self.dtype, self.device = outputs, width, dtype, device
+        self.device_index = device.index
+        self.keep = (packed, scales, values, zeros, bias)  # the pointers above stay valid while these live
+
+    def __call__(self, x: Tensor, out: Tensor) -> Tensor:
+        """``x`` [M, width] and ``out`` [M, outputs]: contiguous, on the plan's device, dtype of the plan."""
+        if torch.cuda.current_device() != self.device_index:
+            with torch.cuda.device(self.device):
+                return self(x, out)
+        status = self.function(x.data_ptr(), *self.head, out.data_ptr(), x.shape[0], *self.tail,
+                               torch.cuda.current_stream().cuda_stream)
+        if status:
+            _native.check(status, "packed_matvec")
+        return out
+
+
 def dequantize(packed: Tensor, scales: Tensor | None, values: Tensor | None, zeros: Tensor | None, *,
                shape: tuple[int, int], group: int, bits: int, dtype: torch.dtype | None = torch.float16,
                codes: bool = False) -> tuple[Tensor | None, Tensor | None]:
