@@ -346,6 +346,20 @@ def main() -> None:
         "cpu_baseline": {"value": cpu_bytes / cpu_seconds / 1e9, "unit": "GB/s", "cores": cpu_threads, "kind": "port",
                          "sample": "one decoder block (7 linears, 109 MB packed), M=1, median of 3 passes"},
     }
+    # the 70B-shaped decode step on this one GPU (the N > 1 runs shard the same model)
+    del blocks, graph
+    torch.cuda.empty_cache()
+    from mlkit_b200 import tp_bench
+
+    decode = tp_bench.measure(0, 1, device, steps=max(5, args.steps), warmup=3)
+    line["decode"] = {
+        "workload": f"llama3-70b-shaped int4 g128 decode, tp1, ctx {tp_bench.CONTEXT}, one CUDA graph per step",
+        "tokens_per_s": {f"batch{b}": r["tokens_per_s"] for b, r in decode["batches"].items()},
+        "e2e_tokens_per_s": {f"batch{b}": r["e2e_tokens_per_s"] for b, r in decode["batches"].items()},
+        "ms_per_step": {f"batch{b}": r["ms_per_step"] for b, r in decode["batches"].items()},
+        "per_gpu_roofline_frac": {f"batch{b}": r["per_gpu_gbps"] / peak for b, r in decode["batches"].items()},
+        "launches_per_step": decode["launches_per_step"],
+    }
     traffic_file = ROOT / "profiles" / "gemv_tiled_gate_traffic.json"
     if traffic_file.exists():
         line["roofline"]["traffic"] = json.loads(traffic_file.read_text()).get("dram_bytes_per_launch")

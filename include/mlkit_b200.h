@@ -128,6 +128,29 @@ int mkb_hadamard(const void* x, const int8_t* signs, const float* basis, void* y
                  int64_t M, int W, int factor, int pow2, int dtype, int inverse, int normalize,
                  void* stream);
 
+/*
+ * Operators between the packed matvecs of a Llama-style decode step (fp16 storage, fp32 arithmetic).
+ * They have no counterpart in the reference, which leaves the decoder block to the `transformers`
+ * modules and their compilation (src/mlkit/inference/optimization.py:86-99); here each is one launch so
+ * that the tensor-parallel decode step of this library is a short, graph-capturable chain.
+ *
+ * mkb_add_rmsnorm: residual[m,:] += delta[m,:] (delta may be null), normed = rms_norm(residual) * weight.
+ * mkb_rope_append: qkv[m] = [q_heads | kv_heads | kv_heads] x head_dim; rotates q and k in place
+ *     (rotate-half pairing, angle positions[m] * theta^(-2i/head_dim)) and stores k, v at
+ *     cache[m, kv_head, positions[m], :]; caches are [M, kv_heads, capacity, head_dim].
+ * mkb_attention_decode: out[m, head, :] = softmax(q . K[0..positions[m]] * scale) V, grouped-query,
+ *     head_dim 128.
+ * mkb_silu_mul: out[m, i] = silu(gate_up[m, i]) * gate_up[m, I + i].
+ */
+int mkb_add_rmsnorm(void* residual, const void* delta, const void* weight, void* normed,
+                    int M, int H, float eps, void* stream);
+int mkb_rope_append(void* qkv, const int* positions, void* k_cache, void* v_cache,
+                    int M, int q_heads, int kv_heads, int head_dim, int capacity, float theta, void* stream);
+int mkb_attention_decode(const void* qkv, const int* positions, const void* k_cache, const void* v_cache,
+                         void* out, int M, int q_heads, int kv_heads, int head_dim, int capacity,
+                         float scale, void* stream);
+int mkb_silu_mul(const void* gate_up, void* out, int M, int I, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -21,6 +21,10 @@ SIGNATURES = {
     "mkb_dequant": (c_int, [c_void_p] * 6 + [c_int64, c_int64] + [c_int] * 5 + [c_int64, c_void_p]),
     "mkb_dequant_rows": (c_int, [c_void_p] * 6 + [c_int64] * 3 + [c_int] * 5 + [c_int64, c_void_p]),
     "mkb_hadamard": (c_int, [c_void_p] * 4 + [c_int64] + [c_int] * 6 + [c_void_p]),
+    "mkb_add_rmsnorm": (c_int, [c_void_p] * 4 + [c_int, c_int, c_float, c_void_p]),
+    "mkb_rope_append": (c_int, [c_void_p] * 4 + [c_int] * 5 + [c_float, c_void_p]),
+    "mkb_attention_decode": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_float, c_void_p]),
+    "mkb_silu_mul": (c_int, [c_void_p] * 2 + [c_int, c_int, c_void_p]),
 }
 
 _library = None

@@ -1,0 +1,215 @@
+// The small operators between the packed matvecs of a Llama-style decode step, one launch each:
+// residual add + RMS norm, rotary embedding + KV-cache append, single-token attention over the cache
+// (grouped-query), SiLU(gate) * up.  fp16 storage, fp32 arithmetic.  They exist so that a decode step
+// is a short chain of launches that a CUDA graph replays; none of them is bandwidth critical.
+#include "mkb_common.cuh"
+
+namespace mkb {
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int offset = 16; offset; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int offset = 16; offset; offset >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+  return v;
+}
+
+// residual[m,:] += delta[m,:] (when delta != null); normed[m,:] = residual[m,:] * rsqrt(mean(sq) + eps) * weight
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(__half* __restrict__ residual, const __half* __restrict__ delta,
+                                                          const __half* __restrict__ weight, __half* __restrict__ normed,
+                                                          int H, float eps) {
+  extern __shared__ float row_s[];  // [H]
+  __shared__ float part_s[8];
+  const int64_t base = int64_t(blockIdx.x) * H;
+  float sq = 0.f;
+  for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
+    float2 v = __half22float2(*reinterpret_cast<const __half2*>(residual + base + i));
+    if (delta != nullptr) {
+      const float2 d = __half22float2(*reinterpret_cast<const __half2*>(delta + base + i));
+      // the sum is stored back in fp16: the running residual of the model is an fp16 tensor
+      const __half2 summed = __floats2half2_rn(v.x + d.x, v.y + d.y);
+      *reinterpret_cast<__half2*>(residual + base + i) = summed;
+      v = __half22float2(summed);
+    }
+    row_s[i] = v.x;
+    row_s[i + 1] = v.y;
+    sq += v.x * v.x + v.y * v.y;
+  }
+  sq = warp_sum(sq);
+  if ((threadIdx.x & 31) == 0) part_s[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  float total = 0.f;
+  for (int w = 0; w < (blockDim.x >> 5); ++w) total += part_s[w];
+  const float inv = rsqrtf(total / float(H) + eps);
+  for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
+    const float2 w = __half22float2(*reinterpret_cast<const __half2*>(weight + i));
+    // same rounding points as the usual fp16 module: the normalised value is rounded, then scaled
+    const __half2 unit = __floats2half2_rn(row_s[i] * inv, row_s[i + 1] * inv);
+    const float2 u = __half22float2(unit);
+    *reinterpret_cast<__half2*>(normed + base + i) = __floats2half2_rn(u.x * w.x, u.y * w.y);
+  }
+}
+
+// qkv[m] = [q heads | k heads | v heads], head_dim D (even).  Rotates q and k in place (pairs (i, i + D/2),
+// angle position * theta^(-2i/D)) and writes k, v into the caches at `positions[m]`.
+__global__ void rope_append_kernel(__half* __restrict__ qkv, const int* __restrict__ positions,
+                                   __half* __restrict__ k_cache, __half* __restrict__ v_cache, int q_heads,
+                                   int kv_heads, int D, int capacity, float theta) {
+  const int m = blockIdx.x, head = blockIdx.y;  // head over q_heads + kv_heads (+ kv_heads for v)
+  const int position = positions[m];
+  const int row = (q_heads + 2 * kv_heads) * D;
+  __half* vec = qkv + int64_t(m) * row + int64_t(head) * D;
+  const int half_dim = D / 2;
+  if (head < q_heads + kv_heads) {
+    for (int i = threadIdx.x; i < half_dim; i += blockDim.x) {
+      const float freq = powf(theta, -2.f * float(i) / float(D));
+      float s, c;
+      sincosf(float(position) * freq, &s, &c);
+      const float a = __half2float(vec[i]), b = __half2float(vec[i + half_dim]);
+      vec[i] = __float2half_rn(a * c - b * s);
+      vec[i + half_dim] = __float2half_rn(b * c + a * s);
+    }
+  }
+  if (head >= q_heads) {
+    __syncthreads();
+    const bool is_v = head >= q_heads + kv_heads;
+    const int kv = head - q_heads - (is_v ? kv_heads : 0);
+    __half* cache = (is_v ? v_cache : k_cache) + ((int64_t(m) * kv_heads + kv) * capacity + position) * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) cache[i] = vec[i];
+  }
+}
+
+// One CTA per (sequence m, query head).  Warps split the cached positions, keep an online softmax
+// each, and merge in shared memory.  D == 128: a lane owns four dimensions.
+__global__ void __launch_bounds__(128) attention_decode_kernel(const __half* __restrict__ qkv, const int* __restrict__ positions,
+                                                               const __half* __restrict__ k_cache,
+                                                               const __half* __restrict__ v_cache, __half* __restrict__ out,
+                                                               int q_heads, int kv_heads, int capacity, float scale) {
+  constexpr int D = 128;
+  const int m = blockIdx.x, head = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int length = positions[m] + 1;  // the new token was appended already
+  const int kv = head / (q_heads / kv_heads);
+  const int row = (q_heads + 2 * kv_heads) * D;
+  const __half* q = qkv + int64_t(m) * row + int64_t(head) * D + lane * 4;
+  const float2 q01 = __half22float2(*reinterpret_cast<const __half2*>(q));
+  const float2 q23 = __half22float2(*reinterpret_cast<const __half2*>(q + 2));
+  const __half* keys = k_cache + (int64_t(m) * kv_heads + kv) * capacity * D + lane * 4;
+  const __half* values = v_cache + (int64_t(m) * kv_heads + kv) * capacity * D + lane * 4;
+  float running_max = -INFINITY, running_sum = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int p = warp; p < length; p += 4) {
+    const uint2 kraw = *reinterpret_cast<const uint2*>(keys + int64_t(p) * D);
+    const float2 k01 = __half22float2(*reinterpret_cast<const __half2*>(&kraw.x));
+    const float2 k23 = __half22float2(*reinterpret_cast<const __half2*>(&kraw.y));
+    const float score = warp_sum(q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y) * scale;
+    const float new_max = fmaxf(running_max, score);
+    const float rescale = __expf(running_max - new_max), weight = __expf(score - new_max);
+    const uint2 vraw = *reinterpret_cast<const uint2*>(values + int64_t(p) * D);
+    const float2 v01 = __half22float2(*reinterpret_cast<const __half2*>(&vraw.x));
+    const float2 v23 = __half22float2(*reinterpret_cast<const __half2*>(&vraw.y));
+    acc[0] = acc[0] * rescale + weight * v01.x;
+    acc[1] = acc[1] * rescale + weight * v01.y;
+    acc[2] = acc[2] * rescale + weight * v23.x;
+    acc[3] = acc[3] * rescale + weight * v23.y;
+    running_sum = running_sum * rescale + weight;
+    running_max = new_max;
+  }
+  __shared__ float max_s[4], sum_s[4], acc_s[4][D];
+  if (lane == 0) { max_s[warp] = running_max; sum_s[warp] = running_sum; }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc_s[warp][lane * 4 + i] = acc[i];
+  __syncthreads();
+  if (threadIdx.x < D) {
+    float top = -INFINITY;
+    for (int w = 0; w < 4; ++w) top = fmaxf(top, max_s[w]);
+    float total = 0.f, value = 0.f;
+    for (int w = 0; w < 4; ++w) {
+      if (max_s[w] == -INFINITY) continue;  // a warp that saw no position
+      const float factor = __expf(max_s[w] - top);
+      total += sum_s[w] * factor;
+      value += acc_s[w][threadIdx.x] * factor;
+    }
+    out[(int64_t(m) * q_heads + head) * D + threadIdx.x] = __float2half_rn(value / total);
+  }
+}
+
+// out[m, i] = silu(gate_up[m, i]) * gate_up[m, I + i]
+__global__ void silu_mul_kernel(const __half* __restrict__ gate_up, __half* __restrict__ out, int64_t rows, int I) {
+  const int64_t index = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) * 2;
+  if (index >= rows * I) return;
+  const int64_t m = index / I, i = index - m * I;
+  const float2 g = __half22float2(*reinterpret_cast<const __half2*>(gate_up + m * 2 * I + i));
+  const float2 u = __half22float2(*reinterpret_cast<const __half2*>(gate_up + m * 2 * I + I + i));
+  const float a = g.x / (1.f + __expf(-g.x)), b = g.y / (1.f + __expf(-g.y));
+  // the activation is rounded to fp16 before the product, as separate fp16 module ops would do
+  const float2 act = __half22float2(__floats2half2_rn(a, b));
+  *reinterpret_cast<__half2*>(out + m * I + i) = __floats2half2_rn(act.x * u.x, act.y * u.y);
+}
+
+}  // namespace
+}  // namespace mkb
+
+extern "C" int mkb_add_rmsnorm(void* residual, const void* delta, const void* weight, void* normed, int M, int H,
+                               float eps, void* stream) {
+  using namespace mkb;
+  MKB_REQUIRE(M >= 0 && H > 0 && H % 2 == 0, MKB_E_ARGUMENT, "add_rmsnorm: bad shape");
+  MKB_REQUIRE(H * 4 <= 160 * 1024, MKB_E_UNSUPPORTED, "add_rmsnorm: hidden size %d too large", H);
+  if (M == 0) return MKB_OK;
+  MKB_REQUIRE(residual && weight && normed, MKB_E_ARGUMENT, "add_rmsnorm: null pointer");
+  const size_t smem = size_t(H) * 4;
+  static bool opted = false;
+  if (smem > 48 * 1024 && !opted) {
+    cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    opted = true;
+  }
+  add_rmsnorm_kernel<<<M, 256, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__half*>(residual), static_cast<const __half*>(delta), static_cast<const __half*>(weight),
+      static_cast<__half*>(normed), H, eps);
+  MKB_LAUNCH_CHECK("add_rmsnorm launch");
+  return MKB_OK;
+}
+
+extern "C" int mkb_rope_append(void* qkv, const int* positions, void* k_cache, void* v_cache, int M, int q_heads,
+                               int kv_heads, int head_dim, int capacity, float theta, void* stream) {
+  using namespace mkb;
+  MKB_REQUIRE(M >= 0 && q_heads > 0 && kv_heads > 0 && head_dim > 0 && head_dim % 2 == 0 && capacity > 0,
+              MKB_E_ARGUMENT, "rope_append: bad shape");
+  if (M == 0) return MKB_OK;
+  MKB_REQUIRE(qkv && positions && k_cache && v_cache, MKB_E_ARGUMENT, "rope_append: null pointer");
+  rope_append_kernel<<<dim3(M, q_heads + 2 * kv_heads), 64, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__half*>(qkv), positions, static_cast<__half*>(k_cache), static_cast<__half*>(v_cache), q_heads,
+      kv_heads, head_dim, capacity, theta);
+  MKB_LAUNCH_CHECK("rope_append launch");
+  return MKB_OK;
+}
+
+extern "C" int mkb_attention_decode(const void* qkv, const int* positions, const void* k_cache, const void* v_cache,
+                                    void* out, int M, int q_heads, int kv_heads, int head_dim, int capacity,
+                                    float scale, void* stream) {
+  using namespace mkb;
+  MKB_REQUIRE(head_dim == 128, MKB_E_UNSUPPORTED, "attention_decode: head_dim %d (128 supported)", head_dim);
+  MKB_REQUIRE(M >= 0 && q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && capacity > 0, MKB_E_ARGUMENT,
+              "attention_decode: bad shape");
+  if (M == 0) return MKB_OK;
+  MKB_REQUIRE(qkv && positions && k_cache && v_cache && out, MKB_E_ARGUMENT, "attention_decode: null pointer");
+  attention_decode_kernel<<<dim3(M, q_heads), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(qkv), positions, static_cast<const __half*>(k_cache),
+      static_cast<const __half*>(v_cache), static_cast<__half*>(out), q_heads, kv_heads, capacity, scale);
+  MKB_LAUNCH_CHECK("attention_decode launch");
+  return MKB_OK;
+}
+
+extern "C" int mkb_silu_mul(const void* gate_up, void* out, int M, int I, void* stream) {
+  using namespace mkb;
+  MKB_REQUIRE(M >= 0 && I > 0 && I % 2 == 0, MKB_E_ARGUMENT, "silu_mul: bad shape");
+  if (M == 0) return MKB_OK;
+  MKB_REQUIRE(gate_up && out, MKB_E_ARGUMENT, "silu_mul: null pointer");
+  const int64_t pairs = int64_t(M) * I / 2;
+  silu_mul_kernel<<<unsigned((pairs + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(gate_up), static_cast<__half*>(out), M, I);
+  MKB_LAUNCH_CHECK("silu_mul launch");
+  return MKB_OK;
+}

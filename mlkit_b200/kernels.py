@@ -197,3 +197,39 @@ def structured_transform(x: Tensor, *, factor: int, power: int, basis: Tensor | 
             power, _tag(x.dtype, "activation"), int(inverse), int(normalize), _stream(device))
     _native.check(status, "structured_transform")
     return out
+
+
+# ---- operators between the matvecs of a decode step (fp16, contiguous, caller-provided outputs) ----
+
+def add_rmsnorm(residual: Tensor, delta: Tensor | None, weight: Tensor, normed: Tensor, eps: float) -> None:
+    """``residual += delta`` (in place, when given) and ``normed = rms_norm(residual) * weight``."""
+    rows, hidden = residual.shape
+    status = _native.library().mkb_add_rmsnorm(residual.data_ptr(), _pointer(delta), weight.data_ptr(),
+                                               normed.data_ptr(), rows, hidden, eps, _stream(residual.device))
+    _native.check(status, "add_rmsnorm")
+
+
+def rope_append(qkv: Tensor, positions: Tensor, k_cache: Tensor, v_cache: Tensor, *, q_heads: int, kv_heads: int,
+                head_dim: int, theta: float) -> None:
+    """Rotary embedding of the q and k heads of ``qkv`` in place, then k and v into the caches."""
+    status = _native.library().mkb_rope_append(qkv.data_ptr(), positions.data_ptr(), k_cache.data_ptr(),
+                                               v_cache.data_ptr(), qkv.shape[0], q_heads, kv_heads, head_dim,
+                                               k_cache.shape[2], theta, _stream(qkv.device))
+    _native.check(status, "rope_append")
+
+
+def attention_decode(qkv: Tensor, positions: Tensor, k_cache: Tensor, v_cache: Tensor, out: Tensor, *,
+                     q_heads: int, kv_heads: int, head_dim: int) -> None:
+    """Single-token grouped-query attention over the cached positions ``0..positions[m]``."""
+    status = _native.library().mkb_attention_decode(qkv.data_ptr(), positions.data_ptr(), k_cache.data_ptr(),
+                                                    v_cache.data_ptr(), out.data_ptr(), qkv.shape[0], q_heads,
+                                                    kv_heads, head_dim, k_cache.shape[2], head_dim ** -0.5,
+                                                    _stream(qkv.device))
+    _native.check(status, "attention_decode")
+
+
+def silu_mul(gate_up: Tensor, out: Tensor) -> None:
+    """``out = silu(gate_up[:, :I]) * gate_up[:, I:]``."""
+    status = _native.library().mkb_silu_mul(gate_up.data_ptr(), out.data_ptr(), gate_up.shape[0], out.shape[1],
+                                            _stream(gate_up.device))
+    _native.check(status, "silu_mul")

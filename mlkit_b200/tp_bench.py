@@ -1,0 +1,158 @@
+"""Timing of the 70B-shaped tensor-parallel decode step (the multi-GPU workload of ``bench.py``).
+
+Random-initialised Llama-3-70B shape (80 layers, hidden 8192, 64 query / 8 key-value heads, MLP 28672,
+vocabulary 128256 with an fp16 head); every block linear INT4 with group 128; a 512-token synthetic
+context in the KV cache; 1 to 8 sequences decoding one token each.  Total work is fixed as ranks are
+added (strong scaling): each rank streams 1/N of the packed weights per step.
+"""
+
+import json
+import statistics
+
+import torch
+import torch.distributed as dist
+
+from mlkit_b200 import tp
+
+CONTEXT = 512
+BATCHES = (1, 8)
+
+
+def step_bytes_per_rank(model: tp.TensorParallelDecoder, batch: int) -> int:
+    """Bytes one rank must read per step: its packed weights and head share, and the cached context."""
+    c = model.config
+    cache = 2 * batch * (c.kv_heads // model.world) * CONTEXT * c.head_dim * 2 * len(model.blocks)
+    return model.weight_bytes + cache
+
+
+def time_steps(captured: tp.CapturedStep, steps: int, warmup: int, world: int, host_io: bool) -> float:
+    """Milliseconds per decode step (max over ranks), CUDA events around ``steps`` graph replays."""
+    model = captured.model
+    batch = captured.tokens.shape[0]
+    host_tokens = torch.randint(0, model.config.vocab, (batch,), dtype=torch.int64).pin_memory()
+    host_positions = torch.full((batch,), CONTEXT, dtype=torch.int32).pin_memory()
+    host_next = torch.empty(batch, dtype=torch.int64).pin_memory()
+    captured.tokens.copy_(host_tokens)
+    captured.positions.copy_(host_positions)
+
+    def one_step() -> None:
+        if host_io:
+            captured.tokens.copy_(host_tokens, non_blocking=True)
+            captured.positions.copy_(host_positions, non_blocking=True)
+        logits = captured.replay()
+        if host_io:
+            host_next.copy_(logits.argmax(-1), non_blocking=True)
+
+    for _ in range(max(3, warmup)):
+        one_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        one_step()
+    stop.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    elapsed = torch.tensor([start.elapsed_time(stop) / steps], device=model.device)
+    if world > 1:
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    return float(elapsed)
+
+
+def dominant_kernel(model: tp.TensorParallelDecoder, batch: int) -> tuple[float, int]:
+    """Average duration (us) and algorithmic bytes of the gate|up matvec launch of this rank, timed over
+    the distinct weights of all layers (cold in L2) inside one CUDA graph."""
+    width, rows = model.config.hidden, model.blocks[0]["gate_up"].out_rows
+    x = torch.randn(batch, width, device=model.device).half()
+    out = torch.empty(batch, rows, device=model.device, dtype=torch.float16)
+    graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for block in model.blocks:
+            block["gate_up"](x, out)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for block in model.blocks:
+                block["gate_up"](x, out)
+    torch.cuda.current_stream().wait_stream(side)
+    graph.replay()
+    torch.cuda.synchronize()
+    samples = []
+    for _ in range(5):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        samples.append(start.elapsed_time(stop) * 1e3 / len(model.blocks))
+    shard = model.blocks[0]["gate_up"]
+    return min(samples), shard.nbytes + batch * width * 2 + batch * rows * 2 + 64
+
+
+def measure(rank: int, world: int, device: torch.device, steps: int, warmup: int, layers: int | None = None) -> dict:
+    """Build the synthetic model on this rank and time decode for every batch in ``BATCHES``."""
+    group = dist.group.WORLD if world > 1 else None
+    model = tp.TensorParallelDecoder.synthetic(tp.LLAMA3_70B, rank=rank, world=world, device=device, seed=1,
+                                               layers=layers, max_batch=max(BATCHES), capacity=CONTEXT + 64,
+                                               group=group)
+    model.fill_cache(CONTEXT)
+    results = {"batches": {}, "launches_per_step": len(model.blocks) * 9 + 3,
+               "collectives_per_step": 0 if world == 1 else 2 * len(model.blocks) + 1}
+    for batch in BATCHES:
+        captured = model.capture(batch)
+        resident = time_steps(captured, steps, warmup, world, host_io=False)
+        e2e = time_steps(captured, steps, warmup, world, host_io=True)
+        bytes_rank = step_bytes_per_rank(model, batch)
+        results["batches"][batch] = {
+            "ms_per_step": resident, "tokens_per_s": batch / resident * 1e3, "e2e_ms_per_step": e2e,
+            "e2e_tokens_per_s": batch / e2e * 1e3, "bytes_per_rank": bytes_rank,
+            "per_gpu_gbps": bytes_rank / resident / 1e6, "aggregate_gbps": world * bytes_rank / resident / 1e6,
+        }
+        del captured
+    kernel_us, kernel_bytes = dominant_kernel(model, 1)
+    results["kernel"] = {"us": kernel_us, "bytes": kernel_bytes,
+                         "shape": f"{model.config.hidden}->{model.blocks[0]['gate_up'].out_rows}"}
+    del model
+    torch.cuda.empty_cache()
+    return results
+
+
+def run(args, rank: int, world: int, device: torch.device, peak_info: tuple[float, str]) -> None:
+    """The N > 1 arm of ``bench.py``: rank 0 prints the JSON line."""
+    from bench import METRIC, ClockSampler
+
+    peak, peak_kind = peak_info
+    with ClockSampler(device.index) as sampler:
+        results = measure(rank, world, device, args.steps, args.warmup)
+    if rank != 0:
+        return
+    one, eight = results["batches"][1], results["batches"][8]
+    achieved = results["kernel"]["bytes"] / results["kernel"]["us"] / 1e3
+    print(json.dumps({
+        "metric": METRIC, "value": one["aggregate_gbps"], "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": one["ms_per_step"], "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"llama3-70b-shaped int4 g128 tensor-parallel decode, tp{world}, batch 1, ctx {CONTEXT}, "
+                               "one CUDA graph per step",
+                   "l2": "inputs larger than L2: every step streams all packed weights of the rank",
+                   "pct_of_8tbs_per_gpu": round(one["per_gpu_gbps"] / 8000 * 100, 2)},
+        "e2e": {"value": world * one["bytes_per_rank"] / one["e2e_ms_per_step"] / 1e6, "unit": "GB/s",
+                "h2d_bytes_per_step": 12, "d2h_bytes_per_step": 8},
+        "gpu_launches": results["launches_per_step"] * args.steps,
+        "clocks": sampler.summary,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind,
+                     "kernel": f"gemv_tiled_kernel<4, raw> on the gate|up shard {results['kernel']['shape']}, M=1, rank 0",
+                     "bytes_per_launch": results["kernel"]["bytes"], "us_per_launch": results["kernel"]["us"]},
+        "decode": {
+            "tokens_per_s": {"batch1": one["tokens_per_s"], "batch8": eight["tokens_per_s"]},
+            "e2e_tokens_per_s": {"batch1": one["e2e_tokens_per_s"], "batch8": eight["e2e_tokens_per_s"]},
+            "per_gpu_roofline_frac": {"batch1": one["per_gpu_gbps"] / peak, "batch8": eight["per_gpu_gbps"] / peak},
+            "per_gpu_gbps": {"batch1": one["per_gpu_gbps"], "batch8": eight["per_gpu_gbps"]},
+            "collectives_per_step": results["collectives_per_step"],
+        },
+    }))

@@ -1,0 +1,257 @@
+"""GPU tests of the decode operators and the tensor-parallel decoder.
+
+The operators are compared with fp32 torch restatements of the same formulas.  The decoder is compared,
+on one GPU, with a dense fp32 torch decoder built from the oracle's reconstruction of the same packed
+weights; shards for 2, 4 and 8 ranks are summed on one GPU against the unsharded projection; the
+NCCL path runs when two GPUs are visible.
+"""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+import mlkit_b200 as mk
+from mlkit_b200 import kernels, tp
+from oracle import matvec
+
+pytestmark = pytest.mark.gpu
+SMALL = tp.DecoderConfig(layers=2, hidden=256, q_heads=4, kv_heads=2, head_dim=128, intermediate=512, vocab=512)
+
+
+def rel(a, b):
+    return matvec.relative_l2(a.float().cpu().numpy(), b.float().cpu().numpy())
+
+
+def test_add_rmsnorm_matches_torch():
+    torch.manual_seed(0)
+    for rows, hidden in ((1, 256), (8, 8192), (3, 4096)):
+        residual = torch.randn(rows, hidden, device="cuda").half()
+        delta = torch.randn(rows, hidden, device="cuda").half()
+        weight = (torch.rand(hidden, device="cuda") + 0.5).half()
+        expected_residual = (residual.float() + delta.float()).half()
+        variance = expected_residual.float().pow(2).mean(-1, keepdim=True)
+        expected = (expected_residual.float() * torch.rsqrt(variance + 1e-5)).half().float() * weight.float()
+        normed = torch.empty_like(residual)
+        kernels.add_rmsnorm(residual, delta, weight, normed, 1e-5)
+        assert torch.equal(residual, expected_residual)
+        assert rel(normed, expected) < 1e-3
+        first = torch.empty_like(residual)
+        kernels.add_rmsnorm(residual, None, weight, first, 1e-5)
+        assert torch.equal(first, normed) and torch.equal(residual, expected_residual)
+
+
+def rope_reference(vec, position, theta):
+    dim = vec.shape[-1]
+    freq = theta ** (-torch.arange(0, dim, 2, device=vec.device).float() / dim)
+    angle = position * freq
+    a, b = vec[..., : dim // 2].float(), vec[..., dim // 2:].float()
+    return torch.cat((a * angle.cos() - b * angle.sin(), b * angle.cos() + a * angle.sin()), -1)
+
+
+def test_rope_append_and_attention_match_torch():
+    torch.manual_seed(1)
+    batch, q_heads, kv_heads, dim, capacity = 3, 8, 2, 128, 96
+    qkv = torch.randn(batch, (q_heads + 2 * kv_heads) * dim, device="cuda").half()
+    original = qkv.clone()
+    positions = torch.tensor([0, 17, 95], dtype=torch.int32, device="cuda")
+    k_cache = torch.randn(batch, kv_heads, capacity, dim, device="cuda").half()
+    v_cache = torch.randn(batch, kv_heads, capacity, dim, device="cuda").half()
+    kernels.rope_append(qkv, positions, k_cache, v_cache, q_heads=q_heads, kv_heads=kv_heads, head_dim=dim, theta=5e5)
+    heads = original.view(batch, q_heads + 2 * kv_heads, dim)
+    got = qkv.view(batch, q_heads + 2 * kv_heads, dim)
+    for m in range(batch):
+        p = int(positions[m])
+        expected = rope_reference(heads[m, : q_heads + kv_heads], p, 5e5)
+        assert rel(got[m, : q_heads + kv_heads], expected) < 1e-3
+        assert torch.equal(got[m, q_heads + kv_heads:], heads[m, q_heads + kv_heads:])
+        assert torch.equal(k_cache[m, :, p], got[m, q_heads:q_heads + kv_heads])
+        assert torch.equal(v_cache[m, :, p], got[m, q_heads + kv_heads:])
+    out = torch.empty(batch, q_heads * dim, device="cuda", dtype=torch.float16)
+    kernels.attention_decode(qkv, positions, k_cache, v_cache, out, q_heads=q_heads, kv_heads=kv_heads, head_dim=dim)
+    for m in range(batch):
+        length = int(positions[m]) + 1
+        q = got[m, :q_heads].float()
+        keys = k_cache[m, :, :length].float().repeat_interleave(q_heads // kv_heads, 0)
+        values = v_cache[m, :, :length].float().repeat_interleave(q_heads // kv_heads, 0)
+        weights = torch.softmax(torch.einsum("hd,hpd->hp", q, keys) / dim ** 0.5, -1)
+        expected = torch.einsum("hp,hpd->hd", weights, values).reshape(-1)
+        assert rel(out[m], expected) < 2e-3
+
+
+def test_silu_mul_matches_torch():
+    torch.manual_seed(2)
+    gate_up = torch.randn(5, 2 * 1024, device="cuda").half()
+    out = torch.empty(5, 1024, device="cuda", dtype=torch.float16)
+    kernels.silu_mul(gate_up, out)
+    expected = F.silu(gate_up[:, :1024].float()).half().float() * gate_up[:, 1024:].float()
+    assert rel(out, expected) < 1e-3
+
+
+def quantised_block(config, seed):
+    generator = torch.Generator(device="cuda").manual_seed(seed)
+    fmt = mk.int(config.bits, group=config.group)
+    shapes = {"q": (config.q_heads * config.head_dim, config.hidden), "k": (config.kv_heads * config.head_dim, config.hidden),
+              "v": (config.kv_heads * config.head_dim, config.hidden), "o": (config.hidden, config.q_heads * config.head_dim),
+              "gate": (config.intermediate, config.hidden), "up": (config.intermediate, config.hidden),
+              "down": (config.hidden, config.intermediate)}
+    return {name: fmt((torch.randn(shape, device="cuda", generator=generator) * 0.05).half().float())
+            for name, shape in shapes.items()}
+
+
+def dense_reference_step(config, blocks, embedding, final_norm, head, tokens, positions, k_caches, v_caches):
+    """fp32 torch decoder over the dense reconstructions; caches are [batch, kv, capacity, dim] fp32."""
+    def norm(x, w):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + config.eps) * w
+
+    x = embedding.float()[tokens]
+    batch = tokens.shape[0]
+    for index, block in enumerate(blocks):
+        w = {name: q.w.half().float() for name, q in block.items()}
+        h = norm(x, 1.0)
+        q = (h @ w["q"].T).view(batch, config.q_heads, config.head_dim)
+        k = (h @ w["k"].T).view(batch, config.kv_heads, config.head_dim)
+        v = (h @ w["v"].T).view(batch, config.kv_heads, config.head_dim)
+        outs = []
+        for m in range(batch):
+            p = int(positions[m])
+            qm, km = rope_reference(q[m], p, config.rope_theta), rope_reference(k[m], p, config.rope_theta)
+            k_caches[index][m, :, p], v_caches[index][m, :, p] = km, v[m]
+            repeat = config.q_heads // config.kv_heads
+            keys = k_caches[index][m, :, : p + 1].repeat_interleave(repeat, 0)
+            values = v_caches[index][m, :, : p + 1].repeat_interleave(repeat, 0)
+            weights = torch.softmax(torch.einsum("hd,hpd->hp", qm, keys) / config.head_dim ** 0.5, -1)
+            outs.append(torch.einsum("hp,hpd->hd", weights, values).reshape(-1))
+        x = x + torch.stack(outs) @ w["o"].T
+        h = norm(x, 1.0)
+        x = x + (F.silu(h @ w["gate"].T) * (h @ w["up"].T)) @ w["down"].T
+    return norm(x, final_norm.float()) @ head.float().T
+
+
+def build_model(config, blocks, embedding, final_norm, head, rank=0, world=1, **options):
+    model = tp.TensorParallelDecoder(config, rank=rank, world=world, device="cuda", max_batch=4, capacity=64, **options)
+    ones = torch.ones(config.hidden, device="cuda")
+    for block in blocks:
+        model.add_block(tp.shard_block(block, config, rank, world, torch.device("cuda")), ones, ones)
+    model.set_head(embedding, final_norm, head)
+    return model
+
+
+def test_decoder_matches_dense_reference_and_graph_replay():
+    torch.manual_seed(3)
+    config = SMALL
+    blocks = [quantised_block(config, 10 + i) for i in range(config.layers)]
+    embedding = torch.randn(config.vocab, config.hidden, device="cuda").half()
+    final_norm = (torch.rand(config.hidden, device="cuda") + 0.5).half()
+    head = (torch.randn(config.vocab, config.hidden, device="cuda") * 0.05).half()
+    model = build_model(config, blocks, embedding, final_norm, head)
+    model.fill_cache(5, seed=1)
+    k_ref = [cache.float().clone() for cache in model.k_cache]
+    v_ref = [cache.float().clone() for cache in model.v_cache]
+    tokens = torch.tensor([3, 500, 77], device="cuda")
+    positions = torch.tensor([5, 5, 5], dtype=torch.int32, device="cuda")
+    captured = None
+    for step in range(3):
+        expected = dense_reference_step(config, blocks, embedding, final_norm, head, tokens, positions, k_ref, v_ref)
+        if step < 2:
+            logits = model.step(tokens, positions).clone()
+        else:   # the third token goes through the captured graph
+            captured = model.capture(3)
+            for cache, saved in zip(model.k_cache + model.v_cache, saved_caches):
+                cache.copy_(saved)   # capture warm-ups wrote position 0 slots: restore the context
+            captured.tokens.copy_(tokens)
+            captured.positions.copy_(positions)
+            logits = captured.replay().clone()
+        assert rel(logits, expected) < 1e-2, step
+        assert torch.equal(logits.argmax(-1), expected.argmax(-1))
+        tokens = expected.argmax(-1)
+        positions = positions + 1
+        saved_caches = [cache.clone() for cache in model.k_cache + model.v_cache]
+    assert model.weight_bytes > 0
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_shards_sum_to_the_full_projection(world):
+    config = tp.DecoderConfig(layers=1, hidden=512, q_heads=8, kv_heads=4, head_dim=128, intermediate=1024, vocab=512)
+    block = quantised_block(config, 42)
+    device = torch.device("cuda")
+    full = tp.shard_block(block, config, 0, 1, device)
+    torch.manual_seed(5)
+    x = torch.randn(4, config.hidden, device="cuda").half()
+    wide_q = torch.randn(4, config.q_heads * config.head_dim, device="cuda").half()
+    wide_i = torch.randn(4, config.intermediate, device="cuda").half()
+    out = lambda shard: torch.empty(4, shard.out_rows, device="cuda", dtype=torch.float16)
+    qkv_full, gu_full = full["qkv"](x, out(full["qkv"])), full["gate_up"](x, out(full["gate_up"]))
+    o_full, down_full = full["o"](wide_q, out(full["o"])), full["down"](wide_i, out(full["down"]))
+    q_rows, kv_rows = config.q_heads * config.head_dim, config.kv_heads * config.head_dim
+    o_sum, down_sum = torch.zeros_like(o_full, dtype=torch.float32), torch.zeros_like(down_full, dtype=torch.float32)
+    for rank in range(world):
+        shards = tp.shard_block(block, config, rank, world, device)
+        qkv = shards["qkv"](x, out(shards["qkv"]))
+        rq, rk = tp.rows_of(rank, world, q_rows), tp.rows_of(rank, world, kv_rows)
+        expected = torch.cat((qkv_full[:, rq], qkv_full[:, q_rows:][:, rk], qkv_full[:, q_rows + kv_rows:][:, rk]), 1)
+        assert torch.equal(qkv, expected)   # same rows, same arithmetic: bit-identical
+        gu = shards["gate_up"](x, out(shards["gate_up"]))
+        ri = tp.rows_of(rank, world, config.intermediate)
+        assert torch.equal(gu, torch.cat((gu_full[:, ri], gu_full[:, config.intermediate:][:, ri]), 1))
+        share_q, share_i = q_rows // world, config.intermediate // world
+        o_sum += shards["o"](wide_q[:, rank * share_q:(rank + 1) * share_q].contiguous(), out(shards["o"])).float()
+        down_sum += shards["down"](wide_i[:, rank * share_i:(rank + 1) * share_i].contiguous(), out(shards["down"])).float()
+    assert rel(o_sum, o_full) < 2e-3 and rel(down_sum, down_full) < 2e-3
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _nccl_worker(rank, world, port, results):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    config = SMALL
+    with torch.cuda.device(rank):
+        blocks = [quantised_block(config, 10 + i) for i in range(config.layers)]   # same seeds on every rank
+        generator = torch.Generator(device="cuda").manual_seed(3)
+        embedding = torch.randn(config.vocab, config.hidden, device="cuda", generator=generator).half()
+        final_norm = (torch.rand(config.hidden, device="cuda", generator=generator) + 0.5).half()
+        head = (torch.randn(config.vocab, config.hidden, device="cuda", generator=generator) * 0.05).half()
+        model = tp.TensorParallelDecoder(config, rank=rank, world=world, device=torch.device("cuda", rank),
+                                         max_batch=4, capacity=64)
+        ones = torch.ones(config.hidden, device="cuda")
+        for block in blocks:
+            model.add_block(tp.shard_block(block, config, rank, world, torch.device("cuda", rank)), ones, ones)
+        model.set_head(embedding, final_norm, head)
+        tokens = torch.tensor([3, 500, 77], device="cuda")
+        positions = torch.zeros(3, dtype=torch.int32, device="cuda")
+        logits = model.step(tokens, positions).float().cpu()
+        if rank == 0:
+            k_ref = [torch.zeros(4, config.kv_heads, 64, config.head_dim, device="cuda") for _ in blocks]
+            v_ref = [torch.zeros(4, config.kv_heads, 64, config.head_dim, device="cuda") for _ in blocks]
+            expected = dense_reference_step(config, blocks, embedding, final_norm, head, tokens, positions, k_ref, v_ref)
+            results.put(matvec.relative_l2(logits.numpy(), expected.cpu().numpy()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gpu_decode_matches_dense_reference():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    context = mp.get_context("spawn")
+    results = context.Queue()
+    port = _free_port()
+    workers = [context.Process(target=_nccl_worker, args=(rank, 2, port, results)) for rank in range(2)]
+    for worker in workers:
+        worker.start()
+    for worker in workers:
+        worker.join(timeout=300)
+    assert all(worker.exitcode == 0 for worker in workers)
+    assert results.get(timeout=5) < 1e-2
