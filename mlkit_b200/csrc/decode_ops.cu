@@ -83,55 +83,92 @@ __global__ void rope_append_kernel(__half* __restrict__ qkv, const int* __restri
   }
 }
 
-// One CTA per (sequence m, query head).  Warps split the cached positions, keep an online softmax
-// each, and merge in shared memory.  D == 128: a lane owns four dimensions.
-__global__ void __launch_bounds__(128) attention_decode_kernel(const __half* __restrict__ qkv, const int* __restrict__ positions,
+// One CTA of 256 threads per (sequence m, query head), head_dim 128.
+//   1. scores: a thread owns whole cached positions (independent 256-byte key reads, q in registers);
+//   2. block-wide max and sum of exp;
+//   3. values: thread (slice, dim pair) accumulates its quarter of the positions, four loads in
+//      flight; the four slices meet in shared memory.
+__global__ void __launch_bounds__(256) attention_decode_kernel(const __half* __restrict__ qkv, const int* __restrict__ positions,
                                                                const __half* __restrict__ k_cache,
                                                                const __half* __restrict__ v_cache, __half* __restrict__ out,
                                                                int q_heads, int kv_heads, int capacity, float scale) {
   constexpr int D = 128;
+  extern __shared__ float score_s[];  // [capacity]
+  __shared__ float q_s[D];
+  __shared__ float part_s[8];
+  __shared__ float acc_s[4][D];
   const int m = blockIdx.x, head = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int length = positions[m] + 1;  // the new token was appended already
   const int kv = head / (q_heads / kv_heads);
   const int row = (q_heads + 2 * kv_heads) * D;
-  const __half* q = qkv + int64_t(m) * row + int64_t(head) * D + lane * 4;
-  const float2 q01 = __half22float2(*reinterpret_cast<const __half2*>(q));
-  const float2 q23 = __half22float2(*reinterpret_cast<const __half2*>(q + 2));
-  const __half* keys = k_cache + (int64_t(m) * kv_heads + kv) * capacity * D + lane * 4;
-  const __half* values = v_cache + (int64_t(m) * kv_heads + kv) * capacity * D + lane * 4;
-  float running_max = -INFINITY, running_sum = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int p = warp; p < length; p += 4) {
-    const uint2 kraw = *reinterpret_cast<const uint2*>(keys + int64_t(p) * D);
-    const float2 k01 = __half22float2(*reinterpret_cast<const __half2*>(&kraw.x));
-    const float2 k23 = __half22float2(*reinterpret_cast<const __half2*>(&kraw.y));
-    const float score = warp_sum(q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y) * scale;
-    const float new_max = fmaxf(running_max, score);
-    const float rescale = __expf(running_max - new_max), weight = __expf(score - new_max);
-    const uint2 vraw = *reinterpret_cast<const uint2*>(values + int64_t(p) * D);
-    const float2 v01 = __half22float2(*reinterpret_cast<const __half2*>(&vraw.x));
-    const float2 v23 = __half22float2(*reinterpret_cast<const __half2*>(&vraw.y));
-    acc[0] = acc[0] * rescale + weight * v01.x;
-    acc[1] = acc[1] * rescale + weight * v01.y;
-    acc[2] = acc[2] * rescale + weight * v23.x;
-    acc[3] = acc[3] * rescale + weight * v23.y;
-    running_sum = running_sum * rescale + weight;
-    running_max = new_max;
-  }
-  __shared__ float max_s[4], sum_s[4], acc_s[4][D];
-  if (lane == 0) { max_s[warp] = running_max; sum_s[warp] = running_sum; }
+  if (threadIdx.x < D) q_s[threadIdx.x] = __half2float(qkv[int64_t(m) * row + int64_t(head) * D + threadIdx.x]) * scale;
+  __syncthreads();
+  const __half* keys = k_cache + (int64_t(m) * kv_heads + kv) * capacity * D;
+  const __half* values = v_cache + (int64_t(m) * kv_heads + kv) * capacity * D;
+
+  float local_max = -INFINITY;
+  for (int p = threadIdx.x; p < length; p += 256) {
+    const uint4* key = reinterpret_cast<const uint4*>(keys + int64_t(p) * D);
+    float dot = 0.f;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) acc_s[warp][lane * 4 + i] = acc[i];
+    for (int v = 0; v < D / 8; ++v) {
+      const uint4 raw = __ldg(key + v);
+      const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&words[i]));
+        dot = fmaf(q_s[v * 8 + 2 * i], k2.x, dot);
+        dot = fmaf(q_s[v * 8 + 2 * i + 1], k2.y, dot);
+      }
+    }
+    score_s[p] = dot;
+    local_max = fmaxf(local_max, dot);
+  }
+  local_max = warp_max(local_max);
+  if (lane == 0) part_s[warp] = local_max;
+  __syncthreads();
+  float top = part_s[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) top = fmaxf(top, part_s[w]);
+  __syncthreads();
+  float local_sum = 0.f;
+  for (int p = threadIdx.x; p < length; p += 256) {
+    const float weight = __expf(score_s[p] - top);
+    score_s[p] = weight;
+    local_sum += weight;
+  }
+  local_sum = warp_sum(local_sum);
+  if (lane == 0) part_s[warp] = local_sum;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) total += part_s[w];
+
+  const int slice = threadIdx.x >> 6, pair = threadIdx.x & 63;
+  float2 acc = make_float2(0.f, 0.f);
+  int p = slice;
+  for (; p + 12 < length; p += 16) {
+    __half2 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const __half2*>(values + int64_t(p + 4 * u) * D + 2 * pair);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float2 f = __half22float2(v[u]);
+      const float weight = score_s[p + 4 * u];
+      acc.x = fmaf(weight, f.x, acc.x);
+      acc.y = fmaf(weight, f.y, acc.y);
+    }
+  }
+  for (; p < length; p += 4) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(values + int64_t(p) * D + 2 * pair));
+    acc.x = fmaf(score_s[p], f.x, acc.x);
+    acc.y = fmaf(score_s[p], f.y, acc.y);
+  }
+  acc_s[slice][2 * pair] = acc.x;
+  acc_s[slice][2 * pair + 1] = acc.y;
   __syncthreads();
   if (threadIdx.x < D) {
-    float top = -INFINITY;
-    for (int w = 0; w < 4; ++w) top = fmaxf(top, max_s[w]);
-    float total = 0.f, value = 0.f;
-    for (int w = 0; w < 4; ++w) {
-      if (max_s[w] == -INFINITY) continue;  // a warp that saw no position
-      const float factor = __expf(max_s[w] - top);
-      total += sum_s[w] * factor;
-      value += acc_s[w][threadIdx.x] * factor;
-    }
+    const float value = acc_s[0][threadIdx.x] + acc_s[1][threadIdx.x] + acc_s[2][threadIdx.x] + acc_s[3][threadIdx.x];
     out[(int64_t(m) * q_heads + head) * D + threadIdx.x] = __float2half_rn(value / total);
   }
 }
@@ -195,7 +232,14 @@ extern "C" int mkb_attention_decode(const void* qkv, const int* positions, const
               "attention_decode: bad shape");
   if (M == 0) return MKB_OK;
   MKB_REQUIRE(qkv && positions && k_cache && v_cache && out, MKB_E_ARGUMENT, "attention_decode: null pointer");
-  attention_decode_kernel<<<dim3(M, q_heads), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  MKB_REQUIRE(capacity <= 40960, MKB_E_UNSUPPORTED, "attention_decode: capacity %d exceeds 40960 positions", capacity);
+  const size_t smem = size_t(capacity) * 4;
+  static bool opted = false;
+  if (smem > 40 * 1024 && !opted) {
+    cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 164 * 1024);
+    opted = true;
+  }
+  attention_decode_kernel<<<dim3(M, q_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __half*>(qkv), positions, static_cast<const __half*>(k_cache),
       static_cast<const __half*>(v_cache), static_cast<__half*>(out), q_heads, kv_heads, capacity, scale);
   MKB_LAUNCH_CHECK("attention_decode launch");
