@@ -36,7 +36,8 @@ enum {
 enum {
   MKB_GEMV_AUTO = 0,   /* fastest kernel that covers the arguments */
   MKB_GEMV_SCALAR = 1, /* word-at-a-time fp32 kernel: every layout the reference's fused kernel accepts */
-  MKB_GEMV_TILED = 2   /* 16-row x 128-code register-tiled kernel (fp16 activations) */
+  MKB_GEMV_TILED = 2,  /* 16-row x 128-code register-tiled kernel (fp16 activations) */
+  MKB_GEMV_TMEM = 3    /* tcgen05 kernel: weights through tensor memory (INT4 integer grid, fp16, needs a workspace) */
 };
 
 int mkb_version(void);
@@ -78,6 +79,26 @@ int mkb_gemv_ex(const void* x, const uint8_t* packed, const void* scales, const 
                 int x_dtype, int scale_dtype,
                 int64_t packed_row_stride, int64_t scale_row_stride,
                 int integer_grid, float grid_minimum, int kernel, void* stream);
+
+/*
+ * The matvec with a caller-provided workspace, which lets MKB_GEMV_AUTO choose the tensor-memory
+ * kernel (it splits K over CTAs and meets through the workspace).  Same contract as mkb_gemv_ex.
+ * workspace: device memory of at least mkb_gemv_workspace_bytes(M, N, K, bits) bytes, 16-byte aligned,
+ *         ZERO-FILLED ONCE before its first use; the kernel leaves it ready for the next call.  Calls
+ *         that may overlap on the GPU (different streams) need workspaces of their own.  A null or
+ *         short workspace simply rules the tensor-memory kernel out.
+ * mkb_gemv_workspace_bytes returns 0 when no workspace is of use for the shape.
+ * No counterpart in the reference: its Triton kernel gives every program whole rows
+ * (src/mlkit/kernels/packed_linear.py:131-167).
+ */
+int64_t mkb_gemv_workspace_bytes(int M, int N, int K, int bits);
+int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* scales, const float* lut,
+                const void* zeros, const void* bias, void* y,
+                int M, int N, int K, int group, int bits, int lut_len,
+                int x_dtype, int scale_dtype,
+                int64_t packed_row_stride, int64_t scale_row_stride,
+                int integer_grid, float grid_minimum, int kernel,
+                void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
  * Unpack and dequantise a packed weight:

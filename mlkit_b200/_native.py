@@ -11,13 +11,16 @@ from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 from mlkit_b200 import build as _build
 
 F16, BF16, F32 = 0, 1, 2
-GEMV_AUTO, GEMV_SCALAR, GEMV_TILED = 0, 1, 2
+GEMV_AUTO, GEMV_SCALAR, GEMV_TILED, GEMV_TMEM = 0, 1, 2, 3
 
 SIGNATURES = {
     "mkb_version": (c_int, []),
     "mkb_last_error": (c_char_p, []),
     "mkb_gemv": (c_int, [c_void_p] * 7 + [c_int] * 8 + [c_int64, c_int64, c_int, c_float, c_void_p]),
     "mkb_gemv_ex": (c_int, [c_void_p] * 7 + [c_int] * 8 + [c_int64, c_int64, c_int, c_float, c_int, c_void_p]),
+    "mkb_gemv_workspace_bytes": (c_int64, [c_int] * 4),
+    "mkb_gemv_ws": (c_int, [c_void_p] * 7 + [c_int] * 8 + [c_int64, c_int64, c_int, c_float, c_int, c_void_p, c_int64,
+                            c_void_p]),
     "mkb_dequant": (c_int, [c_void_p] * 6 + [c_int64, c_int64] + [c_int] * 5 + [c_int64, c_void_p]),
     "mkb_dequant_rows": (c_int, [c_void_p] * 6 + [c_int64] * 3 + [c_int] * 5 + [c_int64, c_void_p]),
     "mkb_hadamard": (c_int, [c_void_p] * 4 + [c_int64] + [c_int] * 6 + [c_void_p]),

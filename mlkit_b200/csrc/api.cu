@@ -48,17 +48,36 @@ int launch_gemv_tiled(const void* x, const uint8_t* packed, const void* scales, 
                       int bits, int lut_len, int64_t packed_row_stride, int64_t scale_row_stride,
                       int integer_grid, float grid_minimum, cudaStream_t stream);
 
+int gemv_umma_supported(int M, int K, int group, int bits, int x_dtype, int scale_dtype, const void* x,
+                        const uint8_t* packed, int64_t packed_row_stride, const void* zeros, int integer_grid);
+int64_t gemv_umma_workspace_bytes(int M, int N, int K);
+bool prefer_tmem();
+int launch_gemv_umma(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y,
+                     void* workspace, int M, int N, int K, int group, int64_t packed_row_stride,
+                     int64_t scale_row_stride, float grid_minimum, cudaStream_t stream);
+
 }  // namespace mkb
 
-extern "C" int mkb_version(void) { return 100; }
+extern "C" int mkb_version(void) { return 101; }
+
+namespace mkb {
+// Which kernel MKB_GEMV_AUTO takes when both cover the arguments (set from measurements).
+bool prefer_tmem() { return false; }
+}  // namespace mkb
 
 extern "C" const char* mkb_last_error(void) { return mkb::g_error; }
 
-extern "C" int mkb_gemv_ex(const void* x, const uint8_t* packed, const void* scales, const float* lut,
+extern "C" int64_t mkb_gemv_workspace_bytes(int M, int N, int K, int bits) {
+  if (bits != 4 || M < 1 || M > 8 || N < 1 || K < 512 || K % 512 != 0) return 0;
+  return mkb::gemv_umma_workspace_bytes(M, N, K);
+}
+
+extern "C" int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* scales, const float* lut,
                            const void* zeros, const void* bias, void* y, int M, int N, int K, int group,
                            int bits, int lut_len, int x_dtype, int scale_dtype,
                            int64_t packed_row_stride, int64_t scale_row_stride, int integer_grid,
-                           float grid_minimum, int kernel, void* stream) {
+                           float grid_minimum, int kernel, void* workspace, int64_t workspace_bytes,
+                           void* stream) {
   using namespace mkb;
   MKB_REQUIRE(M >= 1 && M <= 8, MKB_E_UNSUPPORTED, "gemv: M=%d outside 1..8", M);
   MKB_REQUIRE(N >= 0 && K >= 0, MKB_E_ARGUMENT, "gemv: negative shape");
@@ -68,7 +87,7 @@ extern "C" int mkb_gemv_ex(const void* x, const uint8_t* packed, const void* sca
               MKB_E_ARGUMENT, "gemv: unknown dtype");
   MKB_REQUIRE(lut_len >= 1 && lut_len <= (1 << bits), MKB_E_ARGUMENT,
               "gemv: lut_len=%d does not fit %d-bit codes", lut_len, bits);
-  MKB_REQUIRE(kernel >= MKB_GEMV_AUTO && kernel <= MKB_GEMV_TILED, MKB_E_ARGUMENT, "gemv: unknown kernel choice");
+  MKB_REQUIRE(kernel >= MKB_GEMV_AUTO && kernel <= MKB_GEMV_TMEM, MKB_E_ARGUMENT, "gemv: unknown kernel choice");
   if (N == 0) return MKB_OK;
   MKB_REQUIRE(x && packed && scales && lut && y, MKB_E_ARGUMENT, "gemv: null pointer");
   MKB_REQUIRE(gemv_scalar_supported(K, group, bits), MKB_E_UNSUPPORTED,
@@ -76,6 +95,16 @@ extern "C" int mkb_gemv_ex(const void* x, const uint8_t* packed, const void* sca
   MKB_REQUIRE(K > 0, MKB_E_UNSUPPORTED, "gemv: empty reduction");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tiled_ok = gemv_tiled_supported(M, K, group, bits, x_dtype, scale_dtype, x, packed, packed_row_stride);
+  const bool tmem_ok = workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) % 16) == 0 && lut_len == 16 &&
+                       gemv_umma_supported(M, K, group, bits, x_dtype, scale_dtype, x, packed, packed_row_stride, zeros,
+                                           integer_grid) &&
+                       workspace_bytes >= gemv_umma_workspace_bytes(M, N, K);
+  if (kernel == MKB_GEMV_TMEM)
+    MKB_REQUIRE(tmem_ok, MKB_E_UNSUPPORTED,
+                "gemv: the tensor-memory kernel does not cover these arguments or the workspace is too small");
+  if (kernel == MKB_GEMV_TMEM || (kernel == MKB_GEMV_AUTO && tmem_ok && mkb::prefer_tmem()))
+    return launch_gemv_umma(x, packed, scales, bias, y, workspace, M, N, K, group, packed_row_stride,
+                            scale_row_stride, grid_minimum, s);
   if (kernel == MKB_GEMV_TILED)
     MKB_REQUIRE(tiled_ok, MKB_E_UNSUPPORTED, "gemv: the tiled kernel does not cover these arguments");
   if (kernel == MKB_GEMV_TILED || (kernel == MKB_GEMV_AUTO && tiled_ok))
@@ -83,6 +112,15 @@ extern "C" int mkb_gemv_ex(const void* x, const uint8_t* packed, const void* sca
                              packed_row_stride, scale_row_stride, integer_grid, grid_minimum, s);
   return launch_gemv_scalar(x, packed, scales, lut, zeros, bias, y, M, N, K, group, bits, lut_len, x_dtype,
                             scale_dtype, packed_row_stride, scale_row_stride, s);
+}
+
+extern "C" int mkb_gemv_ex(const void* x, const uint8_t* packed, const void* scales, const float* lut,
+                           const void* zeros, const void* bias, void* y, int M, int N, int K, int group,
+                           int bits, int lut_len, int x_dtype, int scale_dtype,
+                           int64_t packed_row_stride, int64_t scale_row_stride, int integer_grid,
+                           float grid_minimum, int kernel, void* stream) {
+  return mkb_gemv_ws(x, packed, scales, lut, zeros, bias, y, M, N, K, group, bits, lut_len, x_dtype, scale_dtype,
+                     packed_row_stride, scale_row_stride, integer_grid, grid_minimum, kernel, nullptr, 0, stream);
 }
 
 extern "C" int mkb_gemv(const void* x, const uint8_t* packed, const void* scales, const float* lut,

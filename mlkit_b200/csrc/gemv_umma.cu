@@ -1,0 +1,412 @@
+// Packed INT4 matvec on the 5th-generation tensor cores (tcgen05, sm_100a), M <= 8, fp16.
+//
+// Why tensor memory: at 4 bits per weight one SM must turn ~46 weights per clock into products to
+// keep up with HBM.  With register-fragment tensor-core instructions every lane pays for operand
+// shuffling, fragment loads and per-tile bookkeeping; here a thread owns one weight ROW, decodes its
+// codes with one AND per pair, and hands them to the tensor core through tensor memory (TMEM) as the
+// A operand of tcgen05.mma.  Activations are the B operand, read by the tensor core from shared
+// memory; accumulators live in TMEM.  A thread touches nothing but its own row.
+//
+// Work: a unit is 128 output rows x 512 codes (4 scale groups, 32 KB of codes).  A CTA is one
+// warpgroup; it keeps one K slab (so its activation tiles are staged once, 16 KB) and walks units
+// blockIdx.x, blockIdx.x + gridDim.x, ...  Per group of 128 codes:
+//   * the 128 x 64 B code tile arrives by cp.async (coalesced) in a 3-deep shared-memory ring;
+//   * thread r reads the 64 bytes of row r, masks codes into fp16 subnormals c * 2^-24 (low nibbles)
+//     and c * 2^-20 (high nibbles), and stores them to TMEM (tcgen05.st), 64 columns;
+//   * one thread issues 8 tcgen05.mma (M128 N16 K16): low-nibble steps accumulate in D0, high-nibble
+//     steps in D1, so no operand is rescaled and nothing is rounded;
+//   * after tcgen05.commit signals the mbarrier, thread r loads its row of D0/D1 (tcgen05.ld) and
+//     adds scale[r, group] * (D0 + D1 / 16 + min * sum(x)) to its fp32 outputs.
+// K is split over slabs, so a unit ends with a partial [M x 128] in a workspace; the CTA that
+// completes a row block (atomic counter) adds the partials in slab order, adds the bias and stores
+// fp16.  The counter is left at zero again, so the workspace needs zeroing only once.
+// Every wait on the mbarrier is bounded; on expiry the kernel records a status word and drains.
+#include "mkb_common.cuh"
+
+namespace mkb {
+namespace {
+
+constexpr int kThreadsU = 128;
+constexpr int kSlabGroups = 4;            // scale groups (of 128 codes) per unit
+constexpr int kDepthU = 3;                // ring stages, one group each
+constexpr int kPitch = 80;                // bytes per row in a stage: 64 of codes + 16 of padding
+constexpr int kStageBytes = 128 * kPitch;
+constexpr int kTileBytes = 512;           // one B tile: [2 k-chunks][16 rows][8 halves]
+constexpr int kTmemColumns = 128;         // A: 0..63, D0: 64..79, D1: 80..95
+constexpr uint32_t kSpinLimit = 4000000;
+
+struct UmmaArgs {
+  const __half* x;
+  const uint8_t* packed;
+  const __half* scales;
+  const __half* bias;
+  __half* y;
+  float* partials;   // [row_blocks][slabs][M][128]
+  int* counters;     // [row_blocks], zero between launches
+  int* status;       // set non-zero when a bounded wait expired
+#ifdef MKB_TRACE
+  long long* trace;
+#endif
+  int M, N, K, group_shift;
+  int64_t packed_row_stride, scale_row_stride;
+  int row_blocks, slabs, units;
+  float grid_min;
+};
+
+__device__ __forceinline__ uint32_t smem_address(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void copy16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+// which code of a 32-code chunk faces K index kk (0..15) of the tensor-core step of class cls:
+// register i = kk / 2 holds the mask pair of word i / 2; class 0 pairs are (0,4) and (2,6),
+// class 1 pairs are (1,5) and (3,7)
+__device__ __forceinline__ int chunk_code(int cls, int kk) {
+  const int i = kk >> 1, h = kk & 1, w = i >> 1, second = i & 1;
+  return 8 * w + cls + 2 * second + 4 * h;
+}
+
+__global__ void __launch_bounds__(kThreadsU) gemv_umma_kernel(const UmmaArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* tiles_s = smem;                                                  // [groups][4 chunks][2 classes][512 B]
+  float* corr_s = reinterpret_cast<float*>(smem + kSlabGroups * 8 * kTileBytes);  // [groups][8]
+  float* part_s = corr_s + kSlabGroups * 8;                                 // [groups][8][4 chunks]
+  uint8_t* ring_s = reinterpret_cast<uint8_t*>(part_s + kSlabGroups * 32);  // [depth][128][pitch]
+  __shared__ __align__(8) uint64_t mbar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int last_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int slab = int(blockIdx.x) % a.slabs;
+  const int n_units = a.units > int(blockIdx.x) ? (a.units - 1 - int(blockIdx.x)) / int(gridDim.x) + 1 : 0;
+  const int total = n_units * kSlabGroups;  // stages this CTA consumes
+
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_address(&tmem_base_s)),
+                 "r"(kTmemColumns));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_address(&mbar)), "r"(1));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+
+  // ---- code stream: stage t = (unit t / 4, group t % 4); thread copies vectors j * 128 + tid ----
+  // vector v = j * 128 + tid is 16 bytes of row v / 4 at chunk v % 4: a warp instruction reads 8 rows x 64 B
+  const uint32_t ring_base = smem_address(ring_s);
+  const uint32_t ring_lane = ring_base + (tid >> 2) * kPitch + (tid & 3) * 16;  // + j * 32 rows
+  const int64_t lane_column = int64_t(slab) * kSlabGroups * 64 + (tid & 3) * 16;
+  int ld_stage = 0, ld_group = 0, ld_slot = 0, ld_unit = int(blockIdx.x);
+  const uint8_t* ld_pointer[4];
+  auto ld_rows = [&]() {
+    const int row_block = ld_unit / a.slabs;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t global_row = min(row_block * 128 + j * 32 + (tid >> 2), a.N - 1);
+      ld_pointer[j] = a.packed + global_row * a.packed_row_stride + lane_column;
+    }
+  };
+  ld_rows();
+  auto issue = [&]() {
+    if (ld_stage < total) {
+      const uint32_t slot = ring_lane + ld_slot * kStageBytes;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) copy16(slot + j * 32 * kPitch, ld_pointer[j] + ld_group * 64);
+      ++ld_stage;
+      if (++ld_group == kSlabGroups) {
+        ld_group = 0;
+        ld_unit += int(gridDim.x);
+        ld_rows();
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    ld_slot = ld_slot + 1 == kDepthU ? 0 : ld_slot + 1;
+  };
+#pragma unroll
+  for (int d = 0; d < kDepthU - 1; ++d) issue();
+
+  // ---- activation tiles of this slab (B operand), and min * sum(x) * 2^-24 per group and row ----
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  for (int i = tid; i < kSlabGroups * 8 * kTileBytes / 16; i += kThreadsU)
+    reinterpret_cast<uint4*>(tiles_s)[i] = make_uint4(0u, 0u, 0u, 0u);
+  __syncthreads();
+  if (tid < a.M * kSlabGroups * 4) {
+    const int chunk = tid & 3, group = (tid >> 2) % kSlabGroups, m = (tid >> 2) / kSlabGroups;
+    const __half* source = a.x + int64_t(m) * a.K + (int64_t(slab) * kSlabGroups + group) * 128 + chunk * 32;
+    __half values[32];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(values + 8 * q) = __ldg(reinterpret_cast<const uint4*>(source) + q);
+    float sum = 0.f;
+#pragma unroll
+    for (int q = 0; q < 32; ++q) sum += __half2float(values[q]);
+    part_s[(group * 8 + m) * 4 + chunk] = sum;
+#pragma unroll
+    for (int cls = 0; cls < 2; ++cls) {
+      uint8_t* tile = tiles_s + ((group * 4 + chunk) * 2 + cls) * kTileBytes;
+#pragma unroll
+      for (int kc = 0; kc < 2; ++kc) {
+        __half out[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out[i] = values[chunk_code(cls, kc * 8 + i)];
+        *reinterpret_cast<uint4*>(tile + (kc * 16 + m) * 16) = *reinterpret_cast<uint4*>(out);
+      }
+    }
+  }
+  __syncthreads();
+  if (tid < kSlabGroups * 8) {
+    const float* p = part_s + tid * 4;
+    const bool live = (tid & 7) < a.M;
+    corr_s[tid] = live ? ((p[0] + p[1]) + (p[2] + p[3])) * a.grid_min * 5.9604644775390625e-08f : 0.f;
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  const uint32_t tmem_base = tmem_base_s;
+  const uint32_t lane_base = uint32_t(warp * 32) << 16;
+  const uint32_t tmem_a = tmem_base + lane_base, tmem_d0 = tmem_base + 64 + lane_base, tmem_d1 = tmem_base + 80 + lane_base;
+  const uint32_t tiles_address = smem_address(tiles_s);
+  // instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = 16, M = 128
+  const uint32_t idesc = (1u << 4) | (2u << 17) | (8u << 24);
+  // shared-memory descriptor fields: version 1, no swizzle, leading (next 8 K) 256 B, stride (next 8 rows) 128 B
+  const uint64_t desc_high = (uint64_t(256 >> 4) << 16) | (uint64_t(128 >> 4) << 32) | (uint64_t(1) << 46);
+
+  float y_acc[8];
+#pragma unroll
+  for (int m = 0; m < 8; ++m) y_acc[m] = 0.f;
+  uint32_t phase = 0;
+  bool pending = false;       // a committed batch of steps whose accumulators were not read yet
+  int pending_group = 0;
+  float pending_scale = 0.f;
+  bool failed = false;
+
+  // reads D0/D1 of the batch in flight and folds them into y_acc
+  auto retire = [&]() {
+    uint32_t done = 0, spins = 0;
+    while (!done && spins < kSpinLimit) {
+      asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                   : "=r"(done) : "r"(smem_address(&mbar)), "r"(phase) : "memory");
+      ++spins;
+    }
+    if (!done) { failed = true; return; }
+    phase ^= 1u;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    uint32_t d0[8], d1[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(d0[0]), "=r"(d0[1]), "=r"(d0[2]), "=r"(d0[3]), "=r"(d0[4]), "=r"(d0[5]), "=r"(d0[6]), "=r"(d0[7])
+                 : "r"(tmem_d0) : "memory");
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(d1[0]), "=r"(d1[1]), "=r"(d1[2]), "=r"(d1[3]), "=r"(d1[4]), "=r"(d1[5]), "=r"(d1[6]), "=r"(d1[7])
+                 : "r"(tmem_d1) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    const float4 c_lo = *reinterpret_cast<const float4*>(corr_s + pending_group * 8);
+    const float4 c_hi = *reinterpret_cast<const float4*>(corr_s + pending_group * 8 + 4);
+    const float corr[8] = {c_lo.x, c_lo.y, c_lo.z, c_lo.w, c_hi.x, c_hi.y, c_hi.z, c_hi.w};
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+      const float tile_sum = fmaf(__uint_as_float(d1[m]), 0.0625f, __uint_as_float(d0[m])) + corr[m];
+      y_acc[m] = fmaf(pending_scale, tile_sum, y_acc[m]);
+    }
+    pending = false;
+  };
+
+#ifdef MKB_TRACE
+#define MKB_MARK(slot) if (tid == 0 && blockIdx.x == 0 && t < 12) a.trace[t * 8 + (slot)] = clock64();
+#else
+#define MKB_MARK(slot)
+#endif
+  int group = 0, slot_index = 0, row_block = int(blockIdx.x) / a.slabs, unit = int(blockIdx.x);
+  const __half* scale_row = a.scales + int64_t(min(row_block * 128 + tid, a.N - 1)) * a.scale_row_stride;
+  // descriptors of the 8 activation tiles of a group differ by 512 B (32 in descriptor units)
+  const uint64_t desc_base = desc_high | uint64_t((tiles_address & 0x3FFFF) >> 4);
+  for (int t = 0; t < total && !failed; ++t) {
+    MKB_MARK(0)
+    const float scale = __half2float(__ldg(scale_row + (((slab * kSlabGroups + group) * 128) >> a.group_shift)));
+    issue();
+    asm volatile("cp.async.wait_group %0;" ::"n"(kDepthU - 1) : "memory");
+    __syncthreads();  // every thread's share of this stage has landed
+    MKB_MARK(1)
+    const uint8_t* mine = ring_s + slot_index * kStageBytes + tid * kPitch;
+    slot_index = slot_index + 1 == kDepthU ? 0 : slot_index + 1;
+    uint4 chunk[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) chunk[c] = *reinterpret_cast<const uint4*>(mine + 16 * c);
+
+    MKB_MARK(2)
+    if (pending) retire();  // frees the A columns and the accumulators of the previous group
+    if (failed) break;
+    MKB_MARK(3)
+
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const uint32_t words[4] = {chunk[c].x, chunk[c].y, chunk[c].z, chunk[c].w};
+      uint32_t r[16];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const uint32_t q = words[w], q8 = q >> 8;
+        r[2 * w] = q & 0x000f000fu;          // class 0: codes (0,4) then (2,6), c * 2^-24
+        r[2 * w + 1] = q8 & 0x000f000fu;
+        r[8 + 2 * w] = q & 0x00f000f0u;      // class 1: codes (1,5) then (3,7), c * 2^-20
+        r[8 + 2 * w + 1] = q8 & 0x00f000f0u;
+      }
+      asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                   :: "r"(tmem_a + 16 * c), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+    }
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();  // all 128 rows of A are in tensor memory
+    MKB_MARK(4)
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint64_t desc_group = desc_base + uint64_t(group * 8 * (kTileBytes >> 4));
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int cls = 0; cls < 2; ++cls) {
+          const uint64_t desc = desc_group + uint64_t((c * 2 + cls) * (kTileBytes >> 4));
+          const uint32_t d = tmem_base + (cls ? 80 : 64);
+          if (c == 0)
+            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 0, 0;\n\t"
+                         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%4, %4, %4, %4}, p;\n\t}\n"
+                         :: "r"(d), "r"(tmem_base + 16 * c + 8 * cls), "l"(desc), "r"(idesc), "r"(0u) : "memory");
+          else
+            asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 1, 0;\n\t"
+                         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%4, %4, %4, %4}, p;\n\t}\n"
+                         :: "r"(d), "r"(tmem_base + 16 * c + 8 * cls), "l"(desc), "r"(idesc), "r"(0u) : "memory");
+        }
+      }
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_address(&mbar)) : "memory");
+    }
+    MKB_MARK(5)
+    pending = true;
+    pending_group = group;
+    pending_scale = scale;
+
+    if (++group == kSlabGroups) {
+      group = 0;
+      // ---- end of a unit: partial results to the workspace; the last slab to arrive finishes the rows ----
+      retire();
+      if (failed) break;
+      float* slot = a.partials + (int64_t(row_block) * a.slabs + slab) * a.M * 128;
+      for (int m = 0; m < a.M; ++m) slot[m * 128 + tid] = y_acc[m] * 16777216.f;  // 2^24: codes were c * 2^-24
+#pragma unroll
+      for (int m = 0; m < 8; ++m) y_acc[m] = 0.f;
+      __syncthreads();
+      if (tid == 0) {
+        __threadfence();  // cumulative: publishes the partials of all threads that passed the barrier
+        last_s = atomicAdd(a.counters + row_block, 1) == a.slabs - 1;
+      }
+      __syncthreads();
+      if (last_s) {
+        __threadfence();
+        const int row = row_block * 128 + tid;
+        const float* first = a.partials + int64_t(row_block) * a.slabs * a.M * 128;
+        for (int m = 0; m < a.M; ++m) {
+          float sum = 0.f;
+          for (int s = 0; s < a.slabs; ++s) sum += __ldcg(first + (int64_t(s) * a.M + m) * 128 + tid);
+          if (row < a.N) {
+            if (a.bias != nullptr) sum += __half2float(a.bias[row]);
+            a.y[int64_t(m) * a.N + row] = __float2half_rn(sum);
+          }
+        }
+        if (tid == 0) a.counters[row_block] = 0;
+      }
+      unit += int(gridDim.x);
+      row_block = unit / a.slabs;
+      scale_row = a.scales + int64_t(min(row_block * 128 + tid, a.N - 1)) * a.scale_row_stride;
+      MKB_MARK(6)
+    }
+  }
+
+  if (failed && tid == 0) atomicExch(a.status, 1);
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
+}
+
+constexpr size_t kSmemU = size_t(kSlabGroups) * 8 * kTileBytes + kSlabGroups * 8 * 4 + kSlabGroups * 32 * 4 +
+                          size_t(kDepthU) * kStageBytes;
+
+}  // namespace
+
+int gemv_umma_supported(int M, int K, int group, int bits, int x_dtype, int scale_dtype, const void* x,
+                        const uint8_t* packed, int64_t packed_row_stride, const void* zeros, int integer_grid) {
+  if (bits != 4 || !integer_grid || zeros != nullptr) return 0;
+  if (x_dtype != MKB_F16 || scale_dtype != MKB_F16 || M < 1 || M > 8) return 0;
+  if (K % (128 * kSlabGroups) != 0 || group % 128 != 0 || (group & (group - 1)) != 0) return 0;
+  if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(packed) % 16 || packed_row_stride % 16) return 0;
+  return 1;
+}
+
+// bytes of workspace (partials, then counters, then one status word) for a problem size
+int64_t gemv_umma_workspace_bytes(int M, int N, int K) {
+  const int64_t row_blocks = (N + 127) / 128, slabs = K / (128 * kSlabGroups);
+  return row_blocks * slabs * M * 128 * 4 + row_blocks * 4 + 4;
+}
+
+int launch_gemv_umma(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y,
+                     void* workspace, int M, int N, int K, int group, int64_t packed_row_stride,
+                     int64_t scale_row_stride, float grid_minimum, cudaStream_t stream) {
+  UmmaArgs a{};
+  a.x = static_cast<const __half*>(x); a.packed = packed; a.scales = static_cast<const __half*>(scales);
+  a.bias = static_cast<const __half*>(bias); a.y = static_cast<__half*>(y);
+  a.M = M; a.N = N; a.K = K; a.packed_row_stride = packed_row_stride; a.scale_row_stride = scale_row_stride;
+  a.group_shift = 0;
+  while ((1 << a.group_shift) < group) ++a.group_shift;
+  a.grid_min = grid_minimum;
+  a.row_blocks = (N + 127) / 128;
+  a.slabs = K / (128 * kSlabGroups);
+  a.units = a.row_blocks * a.slabs;
+  a.partials = static_cast<float*>(workspace);
+  a.counters = reinterpret_cast<int*>(a.partials + int64_t(a.row_blocks) * a.slabs * M * 128);
+  a.status = a.counters + a.row_blocks;
+
+  const DeviceInfo& info = device_info();
+  static bool configured[64];
+  int device = 0;
+  cudaGetDevice(&device);
+  static int ctas_per_sm[64];
+  if (device >= 0 && device < 64 && !configured[device]) {
+    // opt in to the device maximum and the largest shared-memory carve-out, so that several CTAs fit one SM
+    cudaError_t status = cudaFuncSetAttribute(gemv_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              info.max_smem_optin - 1024);  // the kernel also has static shared
+    if (status != cudaSuccess) return cuda_fail(status, "gemv_umma: shared memory opt-in");
+    status = cudaFuncSetAttribute(gemv_umma_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                  cudaSharedmemCarveoutMaxShared);
+    if (status != cudaSuccess) return cuda_fail(status, "gemv_umma: shared memory carve-out");
+    int blocks = 0;
+    status = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, gemv_umma_kernel, kThreadsU, kSmemU);
+    if (status != cudaSuccess) return cuda_fail(status, "gemv_umma: occupancy query");
+    MKB_REQUIRE(blocks >= 1, MKB_E_UNSUPPORTED, "gemv_umma: kernel does not fit one SM");
+    // tensor memory has 512 columns per SM: at most four CTAs of this kernel share one; the kernel
+    // is correct for any grid, so the grid is sized for that bound even where the query is more cautious
+    (void)blocks;
+    ctas_per_sm[device] = 512 / kTmemColumns;
+    configured[device] = true;
+  }
+  int grid = info.sm_count * ctas_per_sm[device] / a.slabs * a.slabs;  // a multiple of the slab count
+  if (grid < a.slabs) grid = a.slabs;
+  if (grid > a.units) grid = a.units;
+
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(grid, 1, 1);
+  config.blockDim = dim3(kThreadsU, 1, 1);
+  config.dynamicSmemBytes = kSmemU;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  cudaError_t launched = cudaLaunchKernelEx(&config, gemv_umma_kernel, a);
+  if (launched != cudaSuccess) return cuda_fail(launched, "gemv_umma launch");
+  return MKB_OK;
+}
+
+}  // namespace mkb

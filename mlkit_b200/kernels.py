@@ -12,7 +12,26 @@ from torch import Tensor
 from mlkit_b200 import _native
 
 DTYPE_TAGS = {torch.float16: _native.F16, torch.bfloat16: _native.BF16, torch.float32: _native.F32}
-KERNEL_CHOICES = {"auto": _native.GEMV_AUTO, "scalar": _native.GEMV_SCALAR, "tiled": _native.GEMV_TILED}
+KERNEL_CHOICES = {"auto": _native.GEMV_AUTO, "scalar": _native.GEMV_SCALAR, "tiled": _native.GEMV_TILED,
+                  "tmem": _native.GEMV_TMEM}
+
+_workspaces: dict[tuple[int, int], Tensor] = {}
+
+
+def matvec_workspace(device: torch.device, rows: int, outputs: int, width: int, bits: int) -> Tensor | None:
+    """Zero-initialised scratch the tensor-memory matvec meets through (it splits K over CTAs), or
+    ``None`` when the shape cannot use it.  One buffer per (device, stream) grows to the largest request;
+    the kernel leaves it zeroed where it must be, so it is cleared only when (re)allocated.  Launches on
+    one stream run in order and may share it."""
+    need = _native.library().mkb_gemv_workspace_bytes(rows, outputs, width, bits)
+    if need <= 0:
+        return None
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    held = _workspaces.get(key)
+    if held is None or held.numel() < need:
+        held = _workspaces[key] = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+    return held
 
 
 def _tag(dtype: torch.dtype, what: str) -> int:
@@ -58,7 +77,7 @@ def integer_grid_of(values: Tensor) -> tuple[bool, float]:
 def packed_matvec(x: Tensor, packed: Tensor, scales: Tensor, values: Tensor, zeros: Tensor | None,
                   bias: Tensor | None, out: Tensor, *, group: int, bits: int, integer_grid: bool = False,
                   grid_minimum: float = 0.0, kernel: str = "auto", packed_row_stride: int | None = None,
-                  scale_row_stride: int | None = None) -> Tensor:
+                  scale_row_stride: int | None = None, workspace: Tensor | None = None) -> Tensor:
     """``out[m, n] = sum_k x[m, k] * (values[code[n, k]] * scales[n, k // group] (+ zeros)) (+ bias[n])``.
 
     ``x`` is ``[M, K]`` contiguous with ``M <= 8``; ``out`` is ``[M, N]`` in the dtype of ``x``.
@@ -79,12 +98,14 @@ def packed_matvec(x: Tensor, packed: Tensor, scales: Tensor, values: Tensor, zer
     if scale_row_stride is None:
         scale_row_stride = scales.stride(0) if scales.dim() == 2 else -(-width // group)
     with torch.cuda.device(device):
-        status = _native.library().mkb_gemv_ex(
+        if workspace is None and kernel in ("auto", "tmem") and x.dtype == torch.float16 and integer_grid:
+            workspace = matvec_workspace(device, rows, outputs, width, bits)
+        status = _native.library().mkb_gemv_ws(
             x.data_ptr(), packed.data_ptr(), scales.data_ptr(), values.data_ptr(), _pointer(zeros),
             _pointer(bias), out.data_ptr(), rows, outputs, width, group, bits, values.numel(),
             _tag(x.dtype, "activation"), _tag(scales.dtype, "scale"), packed_row_stride,
             scale_row_stride, int(integer_grid), float(grid_minimum), KERNEL_CHOICES[kernel],
-            _stream(device))
+            _pointer(workspace), 0 if workspace is None else workspace.numel(), _stream(device))
     _native.check(status, "packed_matvec")
     return out
 
@@ -98,7 +119,8 @@ class MatvecPlan:
     whenever the layer's buffers move (``PackedLinear._apply`` drops it).
     """
 
-    __slots__ = ("function", "head", "tail", "outputs", "width", "dtype", "device", "device_index", "keep")
+    __slots__ = ("function", "head", "tail", "outputs", "width", "bits", "dtype", "device", "device_index", "keep",
+                 "integer_grid", "workspaces")
 
     def __init__(self, packed: Tensor, scales: Tensor, values: Tensor, zeros: Tensor | None, bias: Tensor | None,
                  *, outputs: int, width: int, group: int, bits: int, dtype: torch.dtype, integer_grid: bool,
@@ -108,13 +130,15 @@ class MatvecPlan:
             raise ValueError("offsets must share the dtype of the scales")
         if bias is not None and bias.dtype != dtype:
             bias = bias.to(dtype)
-        self.function = _native.library().mkb_gemv
+        self.function = _native.library().mkb_gemv_ws
         self.head = (packed.data_ptr(), scales.data_ptr(), values.data_ptr(), _pointer(zeros), _pointer(bias))
         self.tail = (outputs, width, group, bits, values.numel(), _tag(dtype, "activation"),
                      _tag(scales.dtype, "scale"), width * bits // 8,
                      scales.stride(0) if scales.dim() == 2 else -(-width // group), int(integer_grid),
-                     float(grid_minimum))
-        self.outputs, self.width, self.dtype, self.device = outputs, width, dtype, device
+                     float(grid_minimum), _native.GEMV_AUTO)
+        self.outputs, self.width, self.bits, self.dtype, self.device = outputs, width, bits, dtype, device
+        self.integer_grid = bool(integer_grid) and dtype == torch.float16 and zeros is None
+        self.workspaces: dict[tuple[int, int], tuple[int | None, int, Tensor | None]] = {}
         self.device_index = device.index
         self.keep = (packed, scales, values, zeros, bias)  # the pointers above stay valid while these live
 
@@ -123,8 +147,13 @@ class MatvecPlan:
         if torch.cuda.current_device() != self.device_index:
             with torch.cuda.device(self.device):
                 return self(x, out)
-        status = self.function(x.data_ptr(), *self.head, out.data_ptr(), x.shape[0], *self.tail,
-                               torch.cuda.current_stream().cuda_stream)
+        stream = torch.cuda.current_stream().cuda_stream
+        rows = x.shape[0]
+        held = self.workspaces.get((rows, stream))
+        if held is None:  # (pointer, bytes, tensor kept alive) of the scratch for this row count and stream
+            tensor = matvec_workspace(self.device, rows, self.outputs, self.width, self.bits) if self.integer_grid else None
+            held = self.workspaces[(rows, stream)] = (_pointer(tensor), 0 if tensor is None else tensor.numel(), tensor)
+        status = self.function(x.data_ptr(), *self.head, out.data_ptr(), rows, *self.tail, held[0], held[1], stream)
         if status:
             _native.check(status, "packed_matvec")
         return out
