@@ -339,15 +339,21 @@ int gemv_umma_supported(int M, int K, int group, int bits, int x_dtype, int scal
                         const uint8_t* packed, int64_t packed_row_stride, const void* zeros, int integer_grid) {
   if (bits != 4 || !integer_grid || zeros != nullptr) return 0;
   if (x_dtype != MKB_F16 || scale_dtype != MKB_F16 || M < 1 || M > 8) return 0;
-  if (K % (128 * kSlabGroups) != 0 || group % 128 != 0 || (group & (group - 1)) != 0) return 0;
+  if (K < 128 * kSlabGroups || K % (128 * kSlabGroups) != 0 || group % 128 != 0 || (group & (group - 1)) != 0) return 0;
   if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(packed) % 16 || packed_row_stride % 16) return 0;
   return 1;
 }
 
-// bytes of workspace (partials, then counters, then one status word) for a problem size
+// Workspace layout: a fixed head of kCounterBytes (one counter per row block, then a status word),
+// then the partials.  The head has the same place for every problem size, and every launch leaves
+// its counters at zero, so one zero-filled buffer serves calls of different shapes in turn.
+constexpr int64_t kCounterBytes = 65536;
+constexpr int64_t kMaxRowBlocks = kCounterBytes / 4 - 1;
+
 int64_t gemv_umma_workspace_bytes(int M, int N, int K) {
   const int64_t row_blocks = (N + 127) / 128, slabs = K / (128 * kSlabGroups);
-  return row_blocks * slabs * M * 128 * 4 + row_blocks * 4 + 4;
+  if (row_blocks > kMaxRowBlocks) return 0;
+  return kCounterBytes + row_blocks * slabs * M * 128 * 4;
 }
 
 int launch_gemv_umma(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y,
@@ -363,9 +369,10 @@ int launch_gemv_umma(const void* x, const uint8_t* packed, const void* scales, c
   a.row_blocks = (N + 127) / 128;
   a.slabs = K / (128 * kSlabGroups);
   a.units = a.row_blocks * a.slabs;
-  a.partials = static_cast<float*>(workspace);
-  a.counters = reinterpret_cast<int*>(a.partials + int64_t(a.row_blocks) * a.slabs * M * 128);
-  a.status = a.counters + a.row_blocks;
+  MKB_REQUIRE(a.row_blocks <= kMaxRowBlocks, MKB_E_UNSUPPORTED, "gemv_umma: %d row blocks exceed the counter area", a.row_blocks);
+  a.counters = static_cast<int*>(workspace);
+  a.status = a.counters + kMaxRowBlocks;
+  a.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kCounterBytes);
 
   const DeviceInfo& info = device_info();
   static bool configured[64];

@@ -127,7 +127,7 @@ def test_matvec_matches_golden_vectors(golden_meta, golden_codecs):
 
 
 @pytest.mark.parametrize("rows_in", [1, 2, 3, 4, 5, 7, 8])
-@pytest.mark.parametrize("kernel", ["scalar", "tiled"])
+@pytest.mark.parametrize("kernel", ["scalar", "tiled", "tmem"])
 def test_matvec_int4_g128_every_row_count(rows_in, kernel):
     layer = helpers.make_layer(1000, 1024, 4, 128, seed=3)   # 1000 rows: a ragged last row tile
     x = helpers.activations(rows_in, 1024, seed=rows_in)
@@ -188,6 +188,22 @@ def test_matvec_other_dtypes_use_the_scalar_kernel():
         assert matvec.relative_l2(out.float().cpu().numpy(), expected) < bound
 
 
+@pytest.mark.parametrize("group", [128, 256, 512])
+def test_matvec_tmem_groups_bias_and_ragged_rows(group):
+    layer = helpers.make_layer(300, 1536, 4, group, seed=group)
+    bias = (np.random.default_rng(2).standard_normal(300) * 0.1).astype(np.float16)
+    for rows_in in (1, 5, 8):
+        x = helpers.activations(rows_in, 1536, seed=rows_in, outliers=True)
+        expected = oracle_matvec(layer, x, bias)
+        assert matvec.relative_l2(run_matvec(layer, x, "tmem", bias), expected) < TOLERANCE
+
+
+def test_matvec_tmem_refuses_what_it_does_not_cover():
+    layer = helpers.make_layer(64, 640, 4, 128, seed=1)   # 640 codes: not a whole number of 512-code slabs
+    with pytest.raises(ValueError, match="tensor-memory kernel"):
+        run_matvec(layer, helpers.activations(1, 640), "tmem")
+
+
 def test_matvec_rejects_bad_arguments():
     from mlkit_b200 import kernels
 
@@ -224,6 +240,9 @@ def test_matvec_llama8b_shapes_full_size(name):
         assert matvec.relative_l2(y, expected) < TOLERANCE
         again = run_matvec(layer, x, "auto")
         assert np.array_equal(y, again)   # fixed summation order: run-to-run identical
+        through_tmem = run_matvec(layer, x, "tmem")   # the tcgen05 kernel on the same inputs
+        assert matvec.relative_l2(through_tmem, expected) < TOLERANCE
+        assert np.array_equal(through_tmem, run_matvec(layer, x, "tmem"))
         # linearity, a size-independent property: f(2x) == 2 f(x) exactly in binary floating point
         # (products and fp32 sums scale by two without rounding)
         # (outputs in the fp16 subnormal range are excluded: their rounding step does not scale)
