@@ -101,6 +101,26 @@ int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* scales, const 
                 void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
+ * The INT4 matvec for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference.  Same arithmetic and kernel as mkb_gemv_ws with MKB_GEMV_TMEM (fp16 activations and
+ * scales, integer grid lut[c] = grid_minimum + c with 16 levels, no offsets, K a multiple of 512,
+ * power-of-two group >= 128), but the split-K scratch is a fixed array inside the library image
+ * instead of a caller workspace: mkb_gemv_static_scratch_bytes() bytes (8 MiB), held by every GPU
+ * that loads the library until the process exits.  A shape that needs more scratch
+ * (65536 + ceil(N/128) * (K/512) * M * 512 bytes) is rejected with MKB_E_UNSUPPORTED.
+ *   - The call itself calls no allocator.  The first call on each device looks up the array's
+ *     device address (cudaGetSymbolAddress): make that first call with the device current and
+ *     before any stream capture begins.
+ *   - All calls on a device share the one array.  Calls that may overlap on the GPU (different
+ *     streams, or two threads) race on it; order them on one stream.
+ */
+int64_t mkb_gemv_static_scratch_bytes(void);
+int mkb_gemv_static(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y,
+                    int M, int N, int K, int group,
+                    int64_t packed_row_stride, int64_t scale_row_stride,
+                    float grid_minimum, void* stream);
+
+/*
  * Unpack and dequantise a packed weight:
  *   codes_out[n,k] = code (uint8), w_out[n,k] = lut[code] * scale (+ zero) rounded once to out_dtype.
  * Either output may be null.  The multiply and the add are separate IEEE binary32 operations,

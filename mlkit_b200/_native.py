@@ -21,6 +21,8 @@ SIGNATURES = {
     "mkb_gemv_workspace_bytes": (c_int64, [c_int] * 4),
     "mkb_gemv_ws": (c_int, [c_void_p] * 7 + [c_int] * 8 + [c_int64, c_int64, c_int, c_float, c_int, c_void_p, c_int64,
                             c_void_p]),
+    "mkb_gemv_static_scratch_bytes": (c_int64, []),
+    "mkb_gemv_static": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_int64, c_int64, c_float, c_void_p]),
     "mkb_dequant": (c_int, [c_void_p] * 6 + [c_int64, c_int64] + [c_int] * 5 + [c_int64, c_void_p]),
     "mkb_dequant_rows": (c_int, [c_void_p] * 6 + [c_int64] * 3 + [c_int] * 5 + [c_int64, c_void_p]),
     "mkb_hadamard": (c_int, [c_void_p] * 4 + [c_int64] + [c_int] * 6 + [c_void_p]),

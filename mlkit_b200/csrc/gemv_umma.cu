@@ -417,3 +417,69 @@ int launch_gemv_umma(const void* x, const uint8_t* packed, const void* scales, c
 }
 
 }  // namespace mkb
+
+// ---- the matvec for callers that cannot allocate ---------------------------------------------------
+// Some hosts of this library have no way to hand over a workspace: a serving runtime that gave all
+// of HBM to its KV cache at start-up, a plugin that is forbidden to call the CUDA allocator, code
+// that runs while a stream is being captured (where cudaMalloc is an error).  For them the split-K
+// scratch of the tensor-memory kernel lives in the library image itself.
+namespace mkb {
+namespace {
+
+constexpr int64_t kStaticScratchBytes = int64_t(8) << 20;  // 8 MiB per GPU that loads the library
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address; the
+// address a kernel may use comes from cudaGetSymbolAddress, asked once per device while that
+// device is current.
+int static_scratch_address(void** address) {
+  static void* cached[64];
+  int device = 0;
+  cudaError_t status = cudaGetDevice(&device);
+  if (status != cudaSuccess) return cuda_fail(status, "gemv_static: cudaGetDevice");
+  MKB_REQUIRE(device >= 0 && device < 64, MKB_E_UNSUPPORTED, "gemv_static: device ordinal %d out of range", device);
+  if (cached[device] == nullptr) {
+    void* pointer = nullptr;
+    status = cudaGetSymbolAddress(&pointer, g_static_scratch);
+    if (status != cudaSuccess) return cuda_fail(status, "gemv_static: cudaGetSymbolAddress");
+    MKB_REQUIRE(pointer != nullptr, MKB_E_CUDA, "gemv_static: the scratch symbol has no device address");
+    cached[device] = pointer;
+  }
+  *address = cached[device];
+  return MKB_OK;
+}
+
+}  // namespace
+}  // namespace mkb
+
+extern "C" int64_t mkb_gemv_static_scratch_bytes(void) { return mkb::kStaticScratchBytes; }
+
+extern "C" int mkb_gemv_static(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y,
+                               int M, int N, int K, int group, int64_t packed_row_stride, int64_t scale_row_stride,
+                               float grid_minimum, void* stream) {
+  using namespace mkb;
+  MKB_REQUIRE(M >= 1 && M <= 8 && N >= 1 && K >= 1 && group >= 1, MKB_E_ARGUMENT, "gemv_static: bad shape");
+  MKB_REQUIRE(x && packed && scales && y, MKB_E_ARGUMENT, "gemv_static: null pointer");
+  MKB_REQUIRE(grid_minimum == float(int(grid_minimum)) && grid_minimum >= -512.f && grid_minimum <= 512.f, MKB_E_ARGUMENT,
+              "gemv_static: grid_minimum must be a small integer");
+  MKB_REQUIRE(gemv_umma_supported(M, K, group, 4, MKB_F16, MKB_F16, x, packed, packed_row_stride, nullptr, 1),
+              MKB_E_UNSUPPORTED,
+              "gemv_static: needs K a multiple of 512, a power-of-two group of at least 128 and 16-byte aligned x and packed");
+  const int64_t need = gemv_umma_workspace_bytes(M, N, K);
+  MKB_REQUIRE(need > 0 && need <= kStaticScratchBytes, MKB_E_UNSUPPORTED,
+              "gemv_static: M=%d N=%d K=%d needs %lld B of scratch, the built-in scratch holds %lld B", M, N, K,
+              (long long)need, (long long)kStaticScratchBytes);
+  void* scratch = nullptr;
+  const int status = static_scratch_address(&scratch);
+  if (status != MKB_OK) return status;
+  // the array keeps what the previous call left: the row-block counters and the status word of this
+  // launch must start at zero
+  const int64_t row_blocks = (N + 127) / 128;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t cleared = cudaMemsetAsync(scratch, 0, size_t(row_blocks) * 4, s);
+  if (cleared == cudaSuccess) cleared = cudaMemsetAsync(static_cast<uint8_t*>(scratch) + kMaxRowBlocks * 4, 0, 4, s);
+  if (cleared != cudaSuccess) return cuda_fail(cleared, "gemv_static: clearing the counters");
+  return launch_gemv_umma(x, packed, scales, bias, y, scratch, M, N, K, group, packed_row_stride, scale_row_stride,
+                          grid_minimum, s);
+}
+
