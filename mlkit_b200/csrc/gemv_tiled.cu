@@ -59,7 +59,7 @@ struct TiledArgs {
   __half* y;
   int M, N, K, group, lut_len;
   int64_t packed_row_stride, scale_row_stride;
-  int row_tiles, k_tiles, k_tiles_cta, splits, mpad, group_shift;
+  int row_tiles, first_tile, k_tiles, k_tiles_cta, splits, mpad, group_shift;  // row tiles [first_tile, first_tile + row_tiles)
   float grid_min;
 };
 
@@ -308,7 +308,7 @@ __global__ void __launch_bounds__(kThreadsT, MODE == MODE_TABLE ? 2 : 3) gemv_ti
   const uint32_t ring_end = ring_begin + DEPTH * G::SLOT_BYTES;
   const int64_t lane_column = int64_t(wk0) * TILE_BYTES + t * G::BYTES;
   uint32_t ld_address = ring_begin;
-  int ld_left = n_rt * nk_w, ld_k_left = nk_w, ld_rt = int(blockIdx.x);
+  int ld_left = n_rt * nk_w, ld_k_left = nk_w, ld_rt = a.first_tile + int(blockIdx.x);
   const uint8_t *ld_p0, *ld_p1;
   auto ld_rows = [&]() {
     const int64_t r0 = min(ld_rt * 16 + g, a.N - 1), r1 = min(ld_rt * 16 + g + 8, a.N - 1);
@@ -406,7 +406,7 @@ __global__ void __launch_bounds__(kThreadsT, MODE == MODE_TABLE ? 2 : 3) gemv_ti
   for (int w = 0; w < 4; ++w) b[w] = make_uint4(0u, 0u, 0u, 0u);
   float y_even[4] = {0.f, 0.f, 0.f, 0.f}, y_odd[4] = {0.f, 0.f, 0.f, 0.f};
   for (int rt_local = 0; rt_local < n_rt; ++rt_local) {
-    const int rt = int(blockIdx.x) + rt_local * stride_rt;
+    const int rt = a.first_tile + int(blockIdx.x) + rt_local * stride_rt;
     const int64_t r0 = min(rt * 16 + g, a.N - 1), r1 = min(rt * 16 + g + 8, a.N - 1);
     const __half* scale_row0 = a.scales + r0 * a.scale_row_stride;
     const __half* scale_row1 = a.scales + r1 * a.scale_row_stride;
@@ -527,7 +527,7 @@ __global__ void __launch_bounds__(kThreadsT, MODE == MODE_TABLE ? 2 : 3) gemv_ti
         for (int peer = 0; peer < a.splits; ++peer)
           sum += cluster.map_shared_rank(acc_s, peer)[rt_local * 128 + threadIdx.x];
         const int m = threadIdx.x >> 4;
-        const int row = (int(blockIdx.x) + rt_local * stride_rt) * 16 + (threadIdx.x & 15);
+        const int row = (a.first_tile + int(blockIdx.x) + rt_local * stride_rt) * 16 + (threadIdx.x & 15);
         if (m < a.M && row < a.N) {
           if (a.bias != nullptr) sum += __half2float(a.bias[row]);
           a.y[int64_t(m) * a.N + row] = __float2half_rn(sum);
@@ -591,35 +591,37 @@ int launch_variant(TiledArgs a, cudaStream_t stream) {
   if (status != MKB_OK) return status;
   int columns = info.sm_count * ctas_per_sm / splits;
   if (columns < 1) columns = 1;
-  if (columns > a.row_tiles) columns = a.row_tiles;
-  if (splits > 1) {
-    const int per_cta = (a.row_tiles + columns - 1) / columns;
-    MKB_REQUIRE(per_cta <= kMaxRowTilesPerCta, MKB_E_UNSUPPORTED,
-                "gemv_tiled: %d row tiles per CTA exceed the split accumulator", per_cta);
-  }
+  // with a K split every CTA keeps one accumulator per row tile it owns: bound the tiles per launch
+  const int total_tiles = a.row_tiles;
+  const int tiles_per_launch = splits > 1 ? columns * kMaxRowTilesPerCta : total_tiles;
+  for (int first = 0; first < total_tiles; first += tiles_per_launch) {
+    a.first_tile = first;
+    a.row_tiles = total_tiles - first < tiles_per_launch ? total_tiles - first : tiles_per_launch;
+    const int grid_columns = columns > a.row_tiles ? a.row_tiles : columns;
 
-  cudaLaunchConfig_t config{};
-  config.gridDim = dim3(columns, splits, 1);
-  config.blockDim = dim3(kThreadsT, 1, 1);
-  config.dynamicSmemBytes = smem;
-  config.stream = stream;
-  // Programmatic dependent launch: the kernel may become resident while its predecessor in the
-  // stream drains.  It prefetches weights at once (constants) and executes griddepcontrol.wait
-  // before it reads activations or writes anything.
-  cudaLaunchAttribute attribute[2];
-  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute[0].val.programmaticStreamSerializationAllowed = 1;
-  config.attrs = attribute;
-  config.numAttrs = 1;
-  if (splits > 1) {
-    attribute[1].id = cudaLaunchAttributeClusterDimension;
-    attribute[1].val.clusterDim.x = 1;
-    attribute[1].val.clusterDim.y = splits;
-    attribute[1].val.clusterDim.z = 1;
-    config.numAttrs = 2;
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(grid_columns, splits, 1);
+    config.blockDim = dim3(kThreadsT, 1, 1);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    // Programmatic dependent launch: the kernel may become resident while its predecessor in the
+    // stream drains.  It prefetches weights at once (constants) and executes griddepcontrol.wait
+    // before it reads activations or writes anything.
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    if (splits > 1) {
+      attribute[1].id = cudaLaunchAttributeClusterDimension;
+      attribute[1].val.clusterDim.x = 1;
+      attribute[1].val.clusterDim.y = splits;
+      attribute[1].val.clusterDim.z = 1;
+      config.numAttrs = 2;
+    }
+    cudaError_t launched = cudaLaunchKernelEx(&config, kernel, a);
+    if (launched != cudaSuccess) return cuda_fail(launched, "gemv_tiled launch");
   }
-  cudaError_t launched = cudaLaunchKernelEx(&config, kernel, a);
-  if (launched != cudaSuccess) return cuda_fail(launched, "gemv_tiled launch");
   return MKB_OK;
 }
 

@@ -7,33 +7,40 @@
 // A operand of tcgen05.mma.  Activations are the B operand, read by the tensor core from shared
 // memory; accumulators live in TMEM.  A thread touches nothing but its own row.
 //
-// Work: a unit is 128 output rows x 512 codes (4 scale groups, 32 KB of codes).  A CTA is one
-// warpgroup; it keeps one K slab (so its activation tiles are staged once, 16 KB) and walks units
-// blockIdx.x, blockIdx.x + gridDim.x, ...  Per group of 128 codes:
-//   * the 128 x 64 B code tile arrives by cp.async (coalesced) in a 3-deep shared-memory ring;
-//   * thread r reads the 64 bytes of row r, masks codes into fp16 subnormals c * 2^-24 (low nibbles)
-//     and c * 2^-20 (high nibbles), and stores them to TMEM (tcgen05.st), 64 columns;
-//   * one thread issues 8 tcgen05.mma (M128 N16 K16): low-nibble steps accumulate in D0, high-nibble
-//     steps in D1, so no operand is rescaled and nothing is rounded;
-//   * after tcgen05.commit signals the mbarrier, thread r loads its row of D0/D1 (tcgen05.ld) and
-//     adds scale[r, group] * (D0 + D1 / 16 + min * sum(x)) to its fp32 outputs.
-// K is split over slabs, so a unit ends with a partial [M x 128] in a workspace; the CTA that
-// completes a row block (atomic counter) adds the partials in slab order, adds the bias and stores
-// fp16.  The counter is left at zero again, so the workspace needs zeroing only once.
-// Every wait on the mbarrier is bounded; on expiry the kernel records a status word and drains.
+// Work: a unit is 128 output rows x 512 codes (4 scale groups, 32 KB of codes).  A CTA keeps one K
+// slab (so its activation tiles are staged once, 16 KB) and walks units blockIdx.x,
+// blockIdx.x + gridDim.x, ...  Roles inside the CTA (224 threads):
+//   * warps 0-3, "row" threads: thread r owns row r of the current unit.  Per group of 128 codes the
+//     128 x 64 B code tile arrives by cp.async (coalesced) in a shared-memory ring; the thread reads
+//     its 64 bytes, masks codes into fp16 subnormals c * 2^-24 (low nibbles) and c * 2^-20 (high
+//     nibbles) and stores them to its TMEM lane (tcgen05.st), 64 columns of the A buffer of that
+//     group's parity; one group later it loads its row of the accumulators (tcgen05.ld) and adds
+//     scale[r, group] * (D0 + D1 / 16 + min * sum(x)) to its fp32 outputs;
+//   * warps 4 and 6, "issuers": one lane of each waits for an A buffer and issues four of the group's
+//     eight tcgen05.mma (M128 N16 K16) -- warp 4 the low-nibble steps, which accumulate in D0, warp 6 the
+//     high-nibble steps, which accumulate in D1, so no operand is rescaled and nothing is rounded -- and
+//     commits them to an mbarrier.  A and D are double buffered, so issuing overlaps the decode of the
+//     next group;
+//   * warp 5, "publisher": K is split over slabs, so a unit ends with a partial [M x 128] in the
+//     workspace.  This warp publishes the unit (fence, atomic counter per row block) and, when its
+//     unit was the last of the row block, adds the partials in slab order, adds the bias and
+//     stores fp16.  The counter is left at zero, so the workspace needs zeroing only once.
+// All hand-offs are mbarriers; every wait is bounded: on expiry the CTA records a status word,
+// stops issuing and drains.
 #include "mkb_common.cuh"
 
 namespace mkb {
 namespace {
 
-constexpr int kThreadsU = 128;
+constexpr int kRowThreads = 128;
+constexpr int kThreadsU = 224;            // 4 row warps, issuer warp, publisher warp, second issuer warp
 constexpr int kSlabGroups = 4;            // scale groups (of 128 codes) per unit
-constexpr int kDepthU = 3;                // ring stages, one group each
+constexpr int kDepthU = 8;                // ring stages, one group each
 constexpr int kPitch = 80;                // bytes per row in a stage: 64 of codes + 16 of padding
 constexpr int kStageBytes = 128 * kPitch;
 constexpr int kTileBytes = 512;           // one B tile: [2 k-chunks][16 rows][8 halves]
-constexpr int kTmemColumns = 128;         // A: 0..63, D0: 64..79, D1: 80..95
-constexpr uint32_t kSpinLimit = 4000000;
+constexpr int kTmemColumns = 256;         // A[2]: 0..127; D[2][2]: 128..191
+constexpr uint32_t kSpinLimit = 2000000;
 
 struct UmmaArgs {
   const __half* x;
@@ -53,10 +60,43 @@ struct UmmaArgs {
   float grid_min;
 };
 
+#ifdef MKB_TRACE
+#define MKB_MARK(who, t, slot) if (blockIdx.x == 0 && (t) < 12) a.trace[((who) * 12 + (t)) * 8 + (slot)] = clock64();
+#else
+#define MKB_MARK(who, t, slot)
+#endif
+
+struct Barriers {          // shared-memory mbarriers
+  uint64_t a_full[2];      // row threads -> issuer: A buffer written (128 arrivals)
+  uint64_t d_full[2];      // issuers -> row threads: steps of the group complete (two tcgen05.commit)
+  uint64_t d_empty[2];     // row threads -> issuer: accumulators read (128 arrivals)
+  uint64_t unit_done[2];   // row threads -> publisher: partials of a unit stored (128 arrivals)
+  uint64_t slot_free[2];   // publisher -> row threads: partial slot bookkeeping consumed (1 arrival)
+};
+
 __device__ __forceinline__ uint32_t smem_address(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
 
 __device__ __forceinline__ void copy16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void barrier_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_address(bar)), "r"(count));
+}
+__device__ __forceinline__ void barrier_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_address(bar)) : "memory");
+}
+// Bounded wait for the phase with the given parity; false when it gave up (or another role did).
+__device__ __forceinline__ bool barrier_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
+  uint32_t done = 0;
+  for (uint32_t spins = 0; spins < kSpinLimit; ++spins) {
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                 : "=r"(done) : "r"(smem_address(bar)), "r"(parity) : "memory");
+    if (done) return true;
+    if ((spins & 1023) == 1023 && *failed) return false;
+  }
+  *failed = 1;
+  return false;
 }
 
 // which code of a 32-code chunk faces K index kk (0..15) of the tensor-core step of class cls:
@@ -73,32 +113,41 @@ __global__ void __launch_bounds__(kThreadsU) gemv_umma_kernel(const UmmaArgs a) 
   float* corr_s = reinterpret_cast<float*>(smem + kSlabGroups * 8 * kTileBytes);  // [groups][8]
   float* part_s = corr_s + kSlabGroups * 8;                                 // [groups][8][4 chunks]
   uint8_t* ring_s = reinterpret_cast<uint8_t*>(part_s + kSlabGroups * 32);  // [depth][128][pitch]
-  __shared__ __align__(8) uint64_t mbar;
+  __shared__ __align__(8) Barriers bars;
   __shared__ uint32_t tmem_base_s;
-  __shared__ int last_s;
+  __shared__ int failed_s;
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool row_thread = tid < kRowThreads;
   const int slab = int(blockIdx.x) % a.slabs;
   const int n_units = a.units > int(blockIdx.x) ? (a.units - 1 - int(blockIdx.x)) / int(gridDim.x) + 1 : 0;
-  const int total = n_units * kSlabGroups;  // stages this CTA consumes
+  const int total = n_units * kSlabGroups;  // groups (= ring stages) this CTA consumes
+  volatile int* failed = &failed_s;
 
-  if (warp == 0) {
+  if (warp == 4) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_address(&tmem_base_s)),
                  "r"(kTmemColumns));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   if (tid == 0) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_address(&mbar)), "r"(1));
+    failed_s = 0;
+    for (int b = 0; b < 2; ++b) {
+      barrier_init(&bars.a_full[b], kRowThreads);
+      barrier_init(&bars.d_full[b], 2);  // one commit per issuer
+      barrier_init(&bars.d_empty[b], kRowThreads);
+      barrier_init(&bars.unit_done[b], kRowThreads);
+      barrier_init(&bars.slot_free[b], 1);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
 
-  // ---- code stream: stage t = (unit t / 4, group t % 4); thread copies vectors j * 128 + tid ----
-  // vector v = j * 128 + tid is 16 bytes of row v / 4 at chunk v % 4: a warp instruction reads 8 rows x 64 B
+  // ---- code stream (row threads): stage t = (unit t / 4, group t % 4); vector j * 128 + tid is 16 bytes of
+  // row (j * 32 + tid / 4) at chunk tid % 4, so a warp instruction reads 8 rows x 64 B ----
   const uint32_t ring_base = smem_address(ring_s);
-  const uint32_t ring_lane = ring_base + (tid >> 2) * kPitch + (tid & 3) * 16;  // + j * 32 rows
+  const uint32_t ring_lane = ring_base + (tid >> 2) * kPitch + (tid & 3) * 16;
   const int64_t lane_column = int64_t(slab) * kSlabGroups * 64 + (tid & 3) * 16;
   int ld_stage = 0, ld_group = 0, ld_slot = 0, ld_unit = int(blockIdx.x);
-  const uint8_t* ld_pointer[4];
+  const uint8_t* ld_pointer[4] = {nullptr, nullptr, nullptr, nullptr};
   auto ld_rows = [&]() {
     const int row_block = ld_unit / a.slabs;
 #pragma unroll
@@ -107,7 +156,6 @@ __global__ void __launch_bounds__(kThreadsU) gemv_umma_kernel(const UmmaArgs a) 
       ld_pointer[j] = a.packed + global_row * a.packed_row_stride + lane_column;
     }
   };
-  ld_rows();
   auto issue = [&]() {
     if (ld_stage < total) {
       const uint32_t slot = ring_lane + ld_slot * kStageBytes;
@@ -123,8 +171,11 @@ __global__ void __launch_bounds__(kThreadsU) gemv_umma_kernel(const UmmaArgs a) 
     asm volatile("cp.async.commit_group;" ::: "memory");
     ld_slot = ld_slot + 1 == kDepthU ? 0 : ld_slot + 1;
   };
+  if (row_thread) {
+    ld_rows();
 #pragma unroll
-  for (int d = 0; d < kDepthU - 1; ++d) issue();
+    for (int d = 0; d < kDepthU - 1; ++d) issue();
+  }
 
   // ---- activation tiles of this slab (B operand), and min * sum(x) * 2^-24 per group and row ----
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -164,169 +215,203 @@ __global__ void __launch_bounds__(kThreadsU) gemv_umma_kernel(const UmmaArgs a) 
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
   const uint32_t tmem_base = tmem_base_s;
-  const uint32_t lane_base = uint32_t(warp * 32) << 16;
-  const uint32_t tmem_a = tmem_base + lane_base, tmem_d0 = tmem_base + 64 + lane_base, tmem_d1 = tmem_base + 80 + lane_base;
-  const uint32_t tiles_address = smem_address(tiles_s);
-  // instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = 16, M = 128
-  const uint32_t idesc = (1u << 4) | (2u << 17) | (8u << 24);
-  // shared-memory descriptor fields: version 1, no swizzle, leading (next 8 K) 256 B, stride (next 8 rows) 128 B
-  const uint64_t desc_high = (uint64_t(256 >> 4) << 16) | (uint64_t(128 >> 4) << 32) | (uint64_t(1) << 46);
 
-  float y_acc[8];
+  if (row_thread) {
+    // ================================ row threads ================================
+    const uint32_t lane_base = uint32_t(warp * 32) << 16;
+    float y_acc[8];
 #pragma unroll
-  for (int m = 0; m < 8; ++m) y_acc[m] = 0.f;
-  uint32_t phase = 0;
-  bool pending = false;       // a committed batch of steps whose accumulators were not read yet
-  int pending_group = 0;
-  float pending_scale = 0.f;
-  bool failed = false;
+    for (int m = 0; m < 8; ++m) y_acc[m] = 0.f;
+    int group = 0, slot_index = 0, unit = int(blockIdx.x), local_unit = 0;
+    int row_block = unit / a.slabs;
+    const __half* scale_row = a.scales + int64_t(min(row_block * 128 + tid, a.N - 1)) * a.scale_row_stride;
+    __half unit_scales[kSlabGroups];  // the four group scales of this row for the current unit, loaded at its start
+    auto load_scales = [&]() {
+#pragma unroll
+      for (int gi = 0; gi < kSlabGroups; ++gi)
+        unit_scales[gi] = __ldg(scale_row + (((slab * kSlabGroups + gi) * 128) >> a.group_shift));
+    };
+    load_scales();
+    float previous_scale = 0.f;
+    int previous_group = 0, previous_row_block = row_block;
+    bool alive = true;
 
-  // reads D0/D1 of the batch in flight and folds them into y_acc
-  auto retire = [&]() {
-    uint32_t done = 0, spins = 0;
-    while (!done && spins < kSpinLimit) {
-      asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
-                   : "=r"(done) : "r"(smem_address(&mbar)), "r"(phase) : "memory");
-      ++spins;
-    }
-    if (!done) { failed = true; return; }
-    phase ^= 1u;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    uint32_t d0[8], d1[8];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(d0[0]), "=r"(d0[1]), "=r"(d0[2]), "=r"(d0[3]), "=r"(d0[4]), "=r"(d0[5]), "=r"(d0[6]), "=r"(d0[7])
-                 : "r"(tmem_d0) : "memory");
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(d1[0]), "=r"(d1[1]), "=r"(d1[2]), "=r"(d1[3]), "=r"(d1[4]), "=r"(d1[5]), "=r"(d1[6]), "=r"(d1[7])
-                 : "r"(tmem_d1) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-    const float4 c_lo = *reinterpret_cast<const float4*>(corr_s + pending_group * 8);
-    const float4 c_hi = *reinterpret_cast<const float4*>(corr_s + pending_group * 8 + 4);
-    const float corr[8] = {c_lo.x, c_lo.y, c_lo.z, c_lo.w, c_hi.x, c_hi.y, c_hi.z, c_hi.w};
-#pragma unroll
-    for (int m = 0; m < 8; ++m) {
-      const float tile_sum = fmaf(__uint_as_float(d1[m]), 0.0625f, __uint_as_float(d0[m])) + corr[m];
-      y_acc[m] = fmaf(pending_scale, tile_sum, y_acc[m]);
-    }
-    pending = false;
-  };
-
-#ifdef MKB_TRACE
-#define MKB_MARK(slot) if (tid == 0 && blockIdx.x == 0 && t < 12) a.trace[t * 8 + (slot)] = clock64();
-#else
-#define MKB_MARK(slot)
-#endif
-  int group = 0, slot_index = 0, row_block = int(blockIdx.x) / a.slabs, unit = int(blockIdx.x);
-  const __half* scale_row = a.scales + int64_t(min(row_block * 128 + tid, a.N - 1)) * a.scale_row_stride;
-  // descriptors of the 8 activation tiles of a group differ by 512 B (32 in descriptor units)
-  const uint64_t desc_base = desc_high | uint64_t((tiles_address & 0x3FFFF) >> 4);
-  for (int t = 0; t < total && !failed; ++t) {
-    MKB_MARK(0)
-    const float scale = __half2float(__ldg(scale_row + (((slab * kSlabGroups + group) * 128) >> a.group_shift)));
-    issue();
-    asm volatile("cp.async.wait_group %0;" ::"n"(kDepthU - 1) : "memory");
-    __syncthreads();  // every thread's share of this stage has landed
-    MKB_MARK(1)
-    const uint8_t* mine = ring_s + slot_index * kStageBytes + tid * kPitch;
-    slot_index = slot_index + 1 == kDepthU ? 0 : slot_index + 1;
-    uint4 chunk[4];
-#pragma unroll
-    for (int c = 0; c < 4; ++c) chunk[c] = *reinterpret_cast<const uint4*>(mine + 16 * c);
-
-    MKB_MARK(2)
-    if (pending) retire();  // frees the A columns and the accumulators of the previous group
-    if (failed) break;
-    MKB_MARK(3)
-
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const uint32_t words[4] = {chunk[c].x, chunk[c].y, chunk[c].z, chunk[c].w};
-      uint32_t r[16];
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const uint32_t q = words[w], q8 = q >> 8;
-        r[2 * w] = q & 0x000f000fu;          // class 0: codes (0,4) then (2,6), c * 2^-24
-        r[2 * w + 1] = q8 & 0x000f000fu;
-        r[8 + 2 * w] = q & 0x00f000f0u;      // class 1: codes (1,5) then (3,7), c * 2^-20
-        r[8 + 2 * w + 1] = q8 & 0x00f000f0u;
-      }
-      asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-                   :: "r"(tmem_a + 16 * c), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-                      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
-    }
-    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();  // all 128 rows of A are in tensor memory
-    MKB_MARK(4)
-    if (tid == 0) {
+    // reads the accumulators of group t (buffer t & 1) and folds them into y_acc; ends the unit after its last group
+    auto retire = [&](int t) {
+      const int b = t & 1;
+      if (!barrier_wait(&bars.d_full[b], uint32_t(t >> 1) & 1u, failed)) { alive = false; return; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint64_t desc_group = desc_base + uint64_t(group * 8 * (kTileBytes >> 4));
+      uint32_t d0[8], d1[8];
+      const uint32_t address = tmem_base + lane_base + 128 + b * 32;
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                   : "=r"(d0[0]), "=r"(d0[1]), "=r"(d0[2]), "=r"(d0[3]), "=r"(d0[4]), "=r"(d0[5]), "=r"(d0[6]), "=r"(d0[7])
+                   : "r"(address) : "memory");
+      asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                   : "=r"(d1[0]), "=r"(d1[1]), "=r"(d1[2]), "=r"(d1[3]), "=r"(d1[4]), "=r"(d1[5]), "=r"(d1[6]), "=r"(d1[7])
+                   : "r"(address + 16) : "memory");
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      barrier_arrive(&bars.d_empty[b]);
+      const float4 c_lo = *reinterpret_cast<const float4*>(corr_s + previous_group * 8);
+      const float4 c_hi = *reinterpret_cast<const float4*>(corr_s + previous_group * 8 + 4);
+      const float corr[8] = {c_lo.x, c_lo.y, c_lo.z, c_lo.w, c_hi.x, c_hi.y, c_hi.z, c_hi.w};
+#pragma unroll
+      for (int m = 0; m < 8; ++m) {
+        const float tile_sum = fmaf(__uint_as_float(d1[m]), 0.0625f, __uint_as_float(d0[m])) + corr[m];
+        y_acc[m] = fmaf(previous_scale, tile_sum, y_acc[m]);
+      }
+      if (previous_group == kSlabGroups - 1) {
+        // the partial slot of this parity is reused every second unit: wait until the publisher is done with it
+        if (local_unit >= 2 && !barrier_wait(&bars.slot_free[local_unit & 1], uint32_t((local_unit >> 1) - 1) & 1u, failed)) {
+          alive = false;
+          return;
+        }
+        float* slot = a.partials + (int64_t(previous_row_block) * a.slabs + slab) * a.M * 128;
+        for (int m = 0; m < a.M; ++m) slot[m * 128 + tid] = y_acc[m] * 16777216.f;  // 2^24: codes were c * 2^-24
+#pragma unroll
+        for (int m = 0; m < 8; ++m) y_acc[m] = 0.f;
+        barrier_arrive(&bars.unit_done[local_unit & 1]);
+        ++local_unit;
+      }
+    };
+
+    for (int t = 0; t < total && alive; ++t) {
+      if (tid == 0) { MKB_MARK(0, t, 0) }
+      asm volatile("cp.async.wait_group %0;" ::"n"(kDepthU - 2) : "memory");
+      if (tid == 0) { MKB_MARK(0, t, 1) }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // every row thread's share of stage t has landed
+      if (tid == 0) { MKB_MARK(0, t, 2) }
+      issue();                                         // refills the stage read one iteration ago
+      const uint8_t* mine = ring_s + slot_index * kStageBytes + tid * kPitch;
+      slot_index = slot_index + 1 == kDepthU ? 0 : slot_index + 1;
+      uint4 chunk[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) chunk[c] = *reinterpret_cast<const uint4*>(mine + 16 * c);
+      if (tid == 0) { MKB_MARK(0, t, 5) }
+      const uint32_t a_address = tmem_base + lane_base + (t & 1) * 64;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
+        const uint32_t words[4] = {chunk[c].x, chunk[c].y, chunk[c].z, chunk[c].w};
+        uint32_t r[16];
 #pragma unroll
-        for (int cls = 0; cls < 2; ++cls) {
+        for (int w = 0; w < 4; ++w) {
+          const uint32_t q = words[w], q8 = q >> 8;
+          r[2 * w] = q & 0x000f000fu;          // class 0: codes (0,4) then (2,6), c * 2^-24
+          r[2 * w + 1] = q8 & 0x000f000fu;
+          r[8 + 2 * w] = q & 0x00f000f0u;      // class 1: codes (1,5) then (3,7), c * 2^-20
+          r[8 + 2 * w + 1] = q8 & 0x00f000f0u;
+        }
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                     :: "r"(a_address + 16 * c), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+      }
+      if (tid == 0) { MKB_MARK(0, t, 6) }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      if (tid == 0) { MKB_MARK(0, t, 7) }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      barrier_arrive(&bars.a_full[t & 1]);
+      if (tid == 0) { MKB_MARK(0, t, 3) }
+      if (t > 0) retire(t - 1);
+      if (tid == 0) { MKB_MARK(0, t, 4) }
+      previous_scale = __half2float(group == 0 ? unit_scales[0] : group == 1 ? unit_scales[1]
+                                    : group == 2 ? unit_scales[2] : unit_scales[3]);
+      previous_group = group;
+      previous_row_block = row_block;
+      if (++group == kSlabGroups) {
+        group = 0;
+        unit += int(gridDim.x);
+        row_block = unit / a.slabs;
+        scale_row = a.scales + int64_t(min(row_block * 128 + tid, a.N - 1)) * a.scale_row_stride;
+        if (t + 1 < total) load_scales();
+      }
+    }
+    if (alive && total > 0) retire(total - 1);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  } else if (warp == 4 || warp == 6) {
+    // ================================ issuers: warp 4 takes the low-nibble steps, warp 6 the high-nibble steps =====
+    if (lane == 0) {
+      const int cls = warp == 4 ? 0 : 1;
+      const uint32_t idesc = (1u << 4) | (2u << 17) | (8u << 24);  // fp32 accumulate, fp16 A/B, K-major, N = 16, M = 128
+      // shared-memory descriptor: version 1, no swizzle, leading (next 8 K) 256 B, stride (next 8 rows) 128 B
+      const uint64_t desc_base = (uint64_t(256 >> 4) << 16) | (uint64_t(128 >> 4) << 32) | (uint64_t(1) << 46) |
+                                 uint64_t((smem_address(tiles_s) & 0x3FFFF) >> 4);
+      int group = 0;
+      for (int g = 0; g < total; ++g) {
+        const int b = g & 1;
+        if (cls == 0) { MKB_MARK(1, g, 0) }
+        if (!barrier_wait(&bars.a_full[b], uint32_t(g >> 1) & 1u, failed)) break;
+        if (cls == 0) { MKB_MARK(1, g, 1) }
+        if (g >= 2 && !barrier_wait(&bars.d_empty[b], uint32_t((g >> 1) - 1) & 1u, failed)) break;
+        if (cls == 0) { MKB_MARK(1, g, 2) }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t desc_group = desc_base + uint64_t(group * 8 * (kTileBytes >> 4));
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
           const uint64_t desc = desc_group + uint64_t((c * 2 + cls) * (kTileBytes >> 4));
-          const uint32_t d = tmem_base + (cls ? 80 : 64);
+          const uint32_t d = tmem_base + 128 + b * 32 + cls * 16;
+          const uint32_t a_columns = tmem_base + b * 64 + 16 * c + 8 * cls;
           if (c == 0)
             asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 0, 0;\n\t"
                          "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%4, %4, %4, %4}, p;\n\t}\n"
-                         :: "r"(d), "r"(tmem_base + 16 * c + 8 * cls), "l"(desc), "r"(idesc), "r"(0u) : "memory");
+                         :: "r"(d), "r"(a_columns), "l"(desc), "r"(idesc), "r"(0u) : "memory");
           else
             asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 1, 0;\n\t"
                          "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%4, %4, %4, %4}, p;\n\t}\n"
-                         :: "r"(d), "r"(tmem_base + 16 * c + 8 * cls), "l"(desc), "r"(idesc), "r"(0u) : "memory");
+                         :: "r"(d), "r"(a_columns), "l"(desc), "r"(idesc), "r"(0u) : "memory");
         }
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_address(&bars.d_full[b]))
+                     : "memory");
+        if (cls == 0) { MKB_MARK(1, g, 3) }
+        group = group + 1 == kSlabGroups ? 0 : group + 1;
       }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_address(&mbar)) : "memory");
     }
-    MKB_MARK(5)
-    pending = true;
-    pending_group = group;
-    pending_scale = scale;
-
-    if (++group == kSlabGroups) {
-      group = 0;
-      // ---- end of a unit: partial results to the workspace; the last slab to arrive finishes the rows ----
-      retire();
-      if (failed) break;
-      float* slot = a.partials + (int64_t(row_block) * a.slabs + slab) * a.M * 128;
-      for (int m = 0; m < a.M; ++m) slot[m * 128 + tid] = y_acc[m] * 16777216.f;  // 2^24: codes were c * 2^-24
-#pragma unroll
-      for (int m = 0; m < 8; ++m) y_acc[m] = 0.f;
-      __syncthreads();
-      if (tid == 0) {
-        __threadfence();  // cumulative: publishes the partials of all threads that passed the barrier
-        last_s = atomicAdd(a.counters + row_block, 1) == a.slabs - 1;
+  } else if (warp == 5) {
+    // ================================ publisher ================================
+    for (int i = 0; i < n_units; ++i) {
+      int ok = 1;
+      if (lane == 0) ok = barrier_wait(&bars.unit_done[i & 1], uint32_t(i >> 1) & 1u, failed) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      const int row_block = (int(blockIdx.x) + i * int(gridDim.x)) / a.slabs;
+      int last = 0;
+      if (lane == 0) {
+        __threadfence();  // cumulative: publishes the partials whose stores the barrier ordered before this point
+        last = atomicAdd(a.counters + row_block, 1) == a.slabs - 1;
       }
-      __syncthreads();
-      if (last_s) {
+      last = __shfl_sync(0xffffffffu, last, 0);
+      if (last) {
         __threadfence();
-        const int row = row_block * 128 + tid;
-        const float* first = a.partials + int64_t(row_block) * a.slabs * a.M * 128;
+        const float* first = a.partials + int64_t(row_block) * a.slabs * a.M * 128 + lane * 4;
+        const int row = row_block * 128 + lane * 4;
         for (int m = 0; m < a.M; ++m) {
-          float sum = 0.f;
-          for (int s = 0; s < a.slabs; ++s) sum += __ldcg(first + (int64_t(s) * a.M + m) * 128 + tid);
-          if (row < a.N) {
-            if (a.bias != nullptr) sum += __half2float(a.bias[row]);
-            a.y[int64_t(m) * a.N + row] = __float2half_rn(sum);
+          float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int s = 0; s < a.slabs; ++s) {
+            const float4 part = __ldcg(reinterpret_cast<const float4*>(first + (int64_t(s) * a.M + m) * 128));
+            sum.x += part.x; sum.y += part.y; sum.z += part.z; sum.w += part.w;
+          }
+          const float values[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            if (row + e < a.N) {
+              float v = values[e];
+              if (a.bias != nullptr) v += __half2float(a.bias[row + e]);
+              a.y[int64_t(m) * a.N + row + e] = __float2half_rn(v);
+            }
           }
         }
-        if (tid == 0) a.counters[row_block] = 0;
+        if (lane == 0) a.counters[row_block] = 0;
       }
-      unit += int(gridDim.x);
-      row_block = unit / a.slabs;
-      scale_row = a.scales + int64_t(min(row_block * 128 + tid, a.N - 1)) * a.scale_row_stride;
-      MKB_MARK(6)
+      __syncwarp();
+      if (lane == 0) barrier_arrive(&bars.slot_free[i & 1]);
     }
   }
 
-  if (failed && tid == 0) atomicExch(a.status, 1);
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  if (tid == 0 && failed_s) atomicExch(a.status, 1);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 0)
+  if (tid == 0 && failed_s) atomicExch(a.status, 1);
+  if (warp == 4)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns));
 }
 
