@@ -39,6 +39,9 @@ ROW_COUNTS = (1, 2, 4, 8)
 BLOCKS = 8
 BITS, GROUP = 4, 128
 METRIC = "packed_int4_g128_gemv_hbm_gbps"
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate-shape launch (4096 -> 14336, M = 1) from the
+# profiler capture summarised in profiles/gemv_tiled_gate_4096x14336.md; refreshed when the kernel changes
+GATE_DRAM_BYTES_PER_LAUNCH = 30.35e6
 
 
 def gemv_bytes(out_rows: int, width: int, rows_in: int) -> int:
@@ -234,12 +237,48 @@ def time_cpu_route(repetitions: int, warmup: int):
     return seconds, threads, bytes_per_pass
 
 
+def run_case(spec: str, device: torch.device, launches: int) -> None:
+    """One layer shape, ``launches`` launches over distinct weight copies (each cold in L2), nothing
+    else on the device: the small case a profiler captures.  Prints the mean launch time."""
+    from mlkit_b200 import kernels
+
+    fields = spec.split(":")
+    out_rows, width = LLAMA8B[fields[0]]
+    rows = int(fields[1]) if len(fields) > 1 else 1
+    kernel = fields[2] if len(fields) > 2 else "auto"
+    generator = torch.Generator(device=device).manual_seed(5)
+    packed = [torch.randint(0, 256, (out_rows * width * BITS // 8,), dtype=torch.uint8, device=device, generator=generator)
+              for _ in range(launches)]
+    scales = [(torch.rand(out_rows, width // GROUP, device=device, generator=generator) * 0.01 + 0.001).half()
+              for _ in range(launches)]
+    values = torch.arange(-8, 8, dtype=torch.float32, device=device)
+    x = torch.randn(rows, width, device=device, generator=generator).half()
+    out = torch.empty(rows, out_rows, device=device, dtype=torch.float16)
+
+    def launch(i):
+        kernels.packed_matvec(x, packed[i], scales[i], values, None, None, out, group=GROUP, bits=BITS,
+                              integer_grid=True, grid_minimum=-8.0, kernel=kernel)
+    launch(0)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(launches):
+        launch(i)
+    stop.record()
+    torch.cuda.synchronize()
+    us = start.elapsed_time(stop) * 1e3 / launches
+    print(json.dumps({"case": spec, "launches": launches, "us_per_launch_eager": round(us, 2),
+                      "bytes_per_launch": gemv_bytes(out_rows, width, rows)}))
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    parser.add_argument("--case", default=None,
+                        help="small single-shape run for a profiler: NAME[:ROWS[:KERNEL]], NAME one of " + ",".join(LLAMA8B))
     args = parser.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -273,6 +312,10 @@ def main() -> None:
 
         tp_bench.run(args, rank, world, device, peaks())
         dist.destroy_process_group()
+        return
+
+    if args.case:
+        run_case(args.case, device, max(1, args.steps))
         return
 
     peak, peak_kind = peaks()
@@ -360,9 +403,7 @@ def main() -> None:
         "per_gpu_roofline_frac": {f"batch{b}": r["per_gpu_gbps"] / peak for b, r in decode["batches"].items()},
         "launches_per_step": decode["launches_per_step"],
     }
-    traffic_file = ROOT / "profiles" / "gemv_tiled_gate_traffic.json"
-    if traffic_file.exists():
-        line["roofline"]["traffic"] = json.loads(traffic_file.read_text()).get("dram_bytes_per_launch")
+    line["roofline"]["traffic"] = GATE_DRAM_BYTES_PER_LAUNCH
     print(json.dumps(line))
 
 
