@@ -37,7 +37,9 @@ enum {
   MKB_GEMV_AUTO = 0,   /* fastest kernel that covers the arguments */
   MKB_GEMV_SCALAR = 1, /* word-at-a-time fp32 kernel: every layout the reference's fused kernel accepts */
   MKB_GEMV_TILED = 2,  /* 16-row x 128-code register-tiled kernel (fp16 activations) */
-  MKB_GEMV_TMEM = 3    /* tcgen05 kernel: weights through tensor memory (INT4 integer grid, fp16, needs a workspace) */
+  MKB_GEMV_TMEM = 3,   /* tcgen05 kernel: weights through tensor memory (INT4 integer grid, fp16, needs a workspace) */
+  MKB_GEMV_BULK = 4    /* TMA-fed kernel: whole 16-row units by cp.async.bulk.tensor into a shared-memory ring
+                          (INT4 integer grid, fp16, K % 256 == 0; needs the workspace when K is split) */
 };
 
 int mkb_version(void);
@@ -81,12 +83,13 @@ int mkb_gemv_ex(const void* x, const uint8_t* packed, const void* scales, const 
                 int integer_grid, float grid_minimum, int kernel, void* stream);
 
 /*
- * The matvec with a caller-provided workspace, which lets MKB_GEMV_AUTO choose the tensor-memory
- * kernel (it splits K over CTAs and meets through the workspace).  Same contract as mkb_gemv_ex.
+ * The matvec with a caller-provided workspace, which lets MKB_GEMV_AUTO choose the kernels that
+ * split K over CTAs and meet through the workspace (MKB_GEMV_BULK, MKB_GEMV_TMEM).  Same contract as
+ * mkb_gemv_ex.
  * workspace: device memory of at least mkb_gemv_workspace_bytes(M, N, K, bits) bytes, 16-byte aligned,
  *         ZERO-FILLED ONCE before its first use; the kernel leaves it ready for the next call.  Calls
  *         that may overlap on the GPU (different streams) need workspaces of their own.  A null or
- *         short workspace simply rules the tensor-memory kernel out.
+ *         short workspace simply rules those kernels out for the shapes that need it.
  * mkb_gemv_workspace_bytes returns 0 when no workspace is of use for the shape.
  * No counterpart in the reference: its Triton kernel gives every program whole rows
  * (src/mlkit/kernels/packed_linear.py:131-167).

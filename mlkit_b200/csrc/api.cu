@@ -56,20 +56,32 @@ int launch_gemv_umma(const void* x, const uint8_t* packed, const void* scales, c
                      void* workspace, int M, int N, int K, int group, int64_t packed_row_stride,
                      int64_t scale_row_stride, float grid_minimum, cudaStream_t stream);
 
+int gemv_bulk_supported(int M, int N, int K, int group, int bits, int x_dtype, int scale_dtype, const void* x,
+                        const uint8_t* packed, int64_t packed_row_stride, const void* zeros, int integer_grid,
+                        float grid_minimum);
+int64_t gemv_bulk_workspace_bytes(int M, int N, int K);
+int launch_gemv_bulk(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y,
+                     void* workspace, int64_t workspace_bytes, int M, int N, int K, int group,
+                     int64_t packed_row_stride, int64_t scale_row_stride, float grid_minimum, cudaStream_t stream);
+bool prefer_bulk();
+
 }  // namespace mkb
 
-extern "C" int mkb_version(void) { return 101; }
+extern "C" int mkb_version(void) { return 102; }
 
 namespace mkb {
 // Which kernel MKB_GEMV_AUTO takes when both cover the arguments (set from measurements).
 bool prefer_tmem() { return false; }
+bool prefer_bulk() { return false; }
 }  // namespace mkb
 
 extern "C" const char* mkb_last_error(void) { return mkb::g_error; }
 
 extern "C" int64_t mkb_gemv_workspace_bytes(int M, int N, int K, int bits) {
-  if (bits != 4 || M < 1 || M > 8 || N < 1 || K < 512 || K % 512 != 0) return 0;
-  return mkb::gemv_umma_workspace_bytes(M, N, K);
+  if (bits != 4 || M < 1 || M > 8 || N < 1 || K < 256) return 0;
+  const int64_t tmem = K % 512 == 0 ? mkb::gemv_umma_workspace_bytes(M, N, K) : 0;
+  const int64_t bulk = K % 256 == 0 ? mkb::gemv_bulk_workspace_bytes(M, N, K) : 0;
+  return tmem > bulk ? tmem : bulk;
 }
 
 extern "C" int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* scales, const float* lut,
@@ -87,7 +99,7 @@ extern "C" int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* sca
               MKB_E_ARGUMENT, "gemv: unknown dtype");
   MKB_REQUIRE(lut_len >= 1 && lut_len <= (1 << bits), MKB_E_ARGUMENT,
               "gemv: lut_len=%d does not fit %d-bit codes", lut_len, bits);
-  MKB_REQUIRE(kernel >= MKB_GEMV_AUTO && kernel <= MKB_GEMV_TMEM, MKB_E_ARGUMENT, "gemv: unknown kernel choice");
+  MKB_REQUIRE(kernel >= MKB_GEMV_AUTO && kernel <= MKB_GEMV_BULK, MKB_E_ARGUMENT, "gemv: unknown kernel choice");
   if (N == 0) return MKB_OK;
   MKB_REQUIRE(x && packed && scales && lut && y, MKB_E_ARGUMENT, "gemv: null pointer");
   MKB_REQUIRE(gemv_scalar_supported(K, group, bits), MKB_E_UNSUPPORTED,
@@ -105,6 +117,18 @@ extern "C" int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* sca
   if (kernel == MKB_GEMV_TMEM || (kernel == MKB_GEMV_AUTO && tmem_ok && mkb::prefer_tmem()))
     return launch_gemv_umma(x, packed, scales, bias, y, workspace, M, N, K, group, packed_row_stride,
                             scale_row_stride, grid_minimum, s);
+  const bool workspace_aligned = workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) % 16) == 0;
+  const bool bulk_ok = lut_len == 16 && workspace_aligned &&
+                       gemv_bulk_supported(M, N, K, group, bits, x_dtype, scale_dtype, x, packed, packed_row_stride,
+                                           zeros, integer_grid, grid_minimum) &&
+                       (gemv_bulk_workspace_bytes(M, N, K) == 0 ||
+                        (workspace != nullptr && workspace_bytes >= gemv_bulk_workspace_bytes(M, N, K)));
+  if (kernel == MKB_GEMV_BULK)
+    MKB_REQUIRE(bulk_ok, MKB_E_UNSUPPORTED,
+                "gemv: the TMA-fed kernel does not cover these arguments or the workspace is too small");
+  if (kernel == MKB_GEMV_BULK || (kernel == MKB_GEMV_AUTO && bulk_ok && mkb::prefer_bulk()))
+    return launch_gemv_bulk(x, packed, scales, bias, y, workspace, workspace_bytes, M, N, K, group,
+                            packed_row_stride, scale_row_stride, grid_minimum, s);
   if (kernel == MKB_GEMV_TILED)
     MKB_REQUIRE(tiled_ok, MKB_E_UNSUPPORTED, "gemv: the tiled kernel does not cover these arguments");
   if (kernel == MKB_GEMV_TILED || (kernel == MKB_GEMV_AUTO && tiled_ok))

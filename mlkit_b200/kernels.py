@@ -13,7 +13,7 @@ from mlkit_b200 import _native
 
 DTYPE_TAGS = {torch.float16: _native.F16, torch.bfloat16: _native.BF16, torch.float32: _native.F32}
 KERNEL_CHOICES = {"auto": _native.GEMV_AUTO, "scalar": _native.GEMV_SCALAR, "tiled": _native.GEMV_TILED,
-                  "tmem": _native.GEMV_TMEM}
+                  "tmem": _native.GEMV_TMEM, "bulk": _native.GEMV_BULK}
 
 _workspaces: dict[tuple[int, int], Tensor] = {}
 
@@ -98,7 +98,7 @@ def packed_matvec(x: Tensor, packed: Tensor, scales: Tensor, values: Tensor, zer
     if scale_row_stride is None:
         scale_row_stride = scales.stride(0) if scales.dim() == 2 else -(-width // group)
     with torch.cuda.device(device):
-        if workspace is None and kernel in ("auto", "tmem") and x.dtype == torch.float16 and integer_grid:
+        if workspace is None and kernel in ("auto", "tmem", "bulk") and x.dtype == torch.float16 and integer_grid:
             workspace = matvec_workspace(device, rows, outputs, width, bits)
         status = _native.library().mkb_gemv_ws(
             x.data_ptr(), packed.data_ptr(), scales.data_ptr(), values.data_ptr(), _pointer(zeros),

@@ -127,7 +127,7 @@ def test_matvec_matches_golden_vectors(golden_meta, golden_codecs):
 
 
 @pytest.mark.parametrize("rows_in", [1, 2, 3, 4, 5, 7, 8])
-@pytest.mark.parametrize("kernel", ["scalar", "tiled", "tmem"])
+@pytest.mark.parametrize("kernel", ["scalar", "tiled", "tmem", "bulk"])
 def test_matvec_int4_g128_every_row_count(rows_in, kernel):
     layer = helpers.make_layer(1000, 1024, 4, 128, seed=3)   # 1000 rows: a ragged last row tile
     x = helpers.activations(rows_in, 1024, seed=rows_in)
@@ -198,6 +198,30 @@ def test_matvec_tmem_groups_bias_and_ragged_rows(group):
         assert matvec.relative_l2(run_matvec(layer, x, "tmem", bias), expected) < TOLERANCE
 
 
+@pytest.mark.parametrize("group", [128, 256, 512])
+@pytest.mark.parametrize("width", [1536, 2304, 5120, 11008 - 11008 % 256])
+def test_matvec_bulk_groups_bias_ragged_rows_and_splits(group, width):
+    """The TMA-fed kernel: widths that need 1, 2 or 3 K slabs, a last slab that is partly empty, a
+    ragged last row tile, a bias, and scale groups wider than a chunk."""
+    layer = helpers.make_layer(300, width, 4, group, seed=group + width)
+    bias = (np.random.default_rng(2).standard_normal(300) * 0.1).astype(np.float16)
+    for rows_in in (1, 3, 8):
+        x = helpers.activations(rows_in, width, seed=rows_in, outliers=True)
+        expected = oracle_matvec(layer, x, bias)
+        first = run_matvec(layer, x, "bulk", bias)
+        assert matvec.relative_l2(first, expected) < TOLERANCE
+        assert np.array_equal(first, run_matvec(layer, x, "bulk", bias))   # fixed summation order
+
+
+def test_matvec_bulk_refuses_what_it_does_not_cover():
+    layer = helpers.make_layer(64, 640, 4, 128, seed=1)   # 640 codes: not a whole number of 256-code chunks
+    with pytest.raises(ValueError, match="TMA-fed kernel"):
+        run_matvec(layer, helpers.activations(1, 640), "bulk")
+    layer = helpers.make_layer(64, 512, 4, 64, seed=1)    # groups narrower than 128 codes
+    with pytest.raises(ValueError, match="TMA-fed kernel"):
+        run_matvec(layer, helpers.activations(1, 512), "bulk")
+
+
 def test_matvec_tmem_refuses_what_it_does_not_cover():
     layer = helpers.make_layer(64, 640, 4, 128, seed=1)   # 640 codes: not a whole number of 512-code slabs
     with pytest.raises(ValueError, match="tensor-memory kernel"):
@@ -243,6 +267,9 @@ def test_matvec_llama8b_shapes_full_size(name):
         through_tmem = run_matvec(layer, x, "tmem")   # the tcgen05 kernel on the same inputs
         assert matvec.relative_l2(through_tmem, expected) < TOLERANCE
         assert np.array_equal(through_tmem, run_matvec(layer, x, "tmem"))
+        through_bulk = run_matvec(layer, x, "bulk")   # the TMA-fed kernel on the same inputs
+        assert matvec.relative_l2(through_bulk, expected) < TOLERANCE
+        assert np.array_equal(through_bulk, run_matvec(layer, x, "bulk"))
         # linearity, a size-independent property: f(2x) == 2 f(x) exactly in binary floating point
         # (products and fp32 sums scale by two without rounding)
         # (outputs in the fp16 subnormal range are excluded: their rounding step does not scale)
