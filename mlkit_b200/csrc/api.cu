@@ -63,7 +63,7 @@ int64_t gemv_bulk_workspace_bytes(int M, int N, int K);
 int launch_gemv_bulk(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y,
                      void* workspace, int64_t workspace_bytes, int M, int N, int K, int group,
                      int64_t packed_row_stride, int64_t scale_row_stride, float grid_minimum, cudaStream_t stream);
-bool prefer_bulk();
+bool prefer_bulk(int M, int N, int K);
 
 }  // namespace mkb
 
@@ -72,7 +72,15 @@ extern "C" int mkb_version(void) { return 102; }
 namespace mkb {
 // Which kernel MKB_GEMV_AUTO takes when both cover the arguments (set from measurements).
 bool prefer_tmem() { return false; }
-bool prefer_bulk() { return false; }
+// Measured on B200 (CUDA-graph replays over weights that are cold in L2): the TMA-fed kernel's time
+// hardly grows with the row count (its activations sit in registers), the tiled kernel's does; the
+// tiled kernel starts faster, which decides small layers.
+bool prefer_bulk(int M, int N, int K) {
+  const int64_t codes = int64_t(N) * K;
+  if (codes < (int64_t(20) << 20)) return false;
+  if (M >= 3) return true;
+  return K > 16384 || (K <= 4096 && N >= 24576);
+}
 }  // namespace mkb
 
 extern "C" const char* mkb_last_error(void) { return mkb::g_error; }
@@ -126,7 +134,7 @@ extern "C" int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* sca
   if (kernel == MKB_GEMV_BULK)
     MKB_REQUIRE(bulk_ok, MKB_E_UNSUPPORTED,
                 "gemv: the TMA-fed kernel does not cover these arguments or the workspace is too small");
-  if (kernel == MKB_GEMV_BULK || (kernel == MKB_GEMV_AUTO && bulk_ok && mkb::prefer_bulk()))
+  if (kernel == MKB_GEMV_BULK || (kernel == MKB_GEMV_AUTO && bulk_ok && mkb::prefer_bulk(M, N, K)))
     return launch_gemv_bulk(x, packed, scales, bias, y, workspace, workspace_bytes, M, N, K, group,
                             packed_row_stride, scale_row_stride, grid_minimum, s);
   if (kernel == MKB_GEMV_TILED)

@@ -32,8 +32,10 @@ namespace mkb {
 namespace {
 
 constexpr int kMaxConsumers = 16;
-constexpr int kReducerWarps = 2;
-constexpr int kMaxThreadsB = (kMaxConsumers + 1 + kReducerWarps) * 32;
+constexpr int kMaxReducers = 3;
+constexpr int kMaxThreadsB = (kMaxConsumers + 1 + kMaxReducers) * 32;
+constexpr int kRedBuffers = 4;            // ring of partial-sum buffers between consumers and reducers
+constexpr int kBatch = 4;                 // units a reducer publishes together when K is split
 constexpr int kChunkBytes = 2048;         // 16 rows x 128 bytes: what one consumer warp takes from a unit
 constexpr int kMaxStages = 24;
 constexpr uint32_t kSpinLimitB = 4000000;
@@ -52,8 +54,27 @@ struct BulkArgs {
   int64_t scale_row_stride;
   int consumers, slabs, row_tiles, units, stages, chunks;  // chunks of 256 codes per row
   int rows_outer;    // 0: a stage is [chunk][row][128 B]; 1: [row][chunk][128 B] (tensor map with natural dimension order)
+  int reducers;
   float grid_min;
+#ifdef MKB_STAMPS
+  unsigned long long* stamps;
+  int launch_id;
+#endif
 };
+
+#ifdef MKB_STAMPS
+static unsigned long long* g_probe_stamps = nullptr;
+static int g_probe_launch = 0, g_probe_consumers = 0, g_probe_stage_cap = 0;
+
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+#define MKB_STAMP(slot) a.stamps[(size_t(a.launch_id) * gridDim.x + blockIdx.x) * 8 + (slot)] = now_ns()
+#else
+#define MKB_STAMP(slot)
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
 
@@ -128,18 +149,22 @@ __device__ __forceinline__ void fragment_units(const uint32_t (&xr)[16], uint4 (
   }
 }
 
-// 32 codes of rows g and g+8 against the lane's activations of that scale group: 8 tensor-core
-// steps; low-nibble codes (c * 2^-24) accumulate in lo, high-nibble codes (c * 2^-20) in hi.
-__device__ __forceinline__ void group_steps(const uint4& c0, const uint4& c1, const uint4 (&b)[4], float (&lo)[4],
-                                            float (&hi)[4]) {
-  const uint32_t q0[4] = {c0.x, c0.y, c0.z, c0.w}, q1[4] = {c1.x, c1.y, c1.z, c1.w};
-  const uint32_t bb[4][4] = {{b[0].x, b[0].y, b[0].z, b[0].w}, {b[1].x, b[1].y, b[1].z, b[1].w},
-                             {b[2].x, b[2].y, b[2].z, b[2].w}, {b[3].x, b[3].y, b[3].z, b[3].w}};
+// 2 x 32 codes of rows g and g+8 (the chunk's two scale groups) against the lane's activations: 16
+// tensor-core steps.  Low-nibble codes (c * 2^-24) and high-nibble codes (c * 2^-20) of each group
+// have accumulators of their own, so four independent chains are in flight.
+__device__ __forceinline__ void group_steps(const uint4& c00, const uint4& c10, const uint4& c01, const uint4& c11,
+                                            const uint4 (&b0)[4], const uint4 (&b1)[4], float (&lo0)[4], float (&hi0)[4],
+                                            float (&lo1)[4], float (&hi1)[4]) {
+  const uint32_t q00[4] = {c00.x, c00.y, c00.z, c00.w}, q10[4] = {c10.x, c10.y, c10.z, c10.w};
+  const uint32_t q01[4] = {c01.x, c01.y, c01.z, c01.w}, q11[4] = {c11.x, c11.y, c11.z, c11.w};
 #pragma unroll
   for (int w = 0; w < 4; ++w) {
-    const uint32_t r0 = q0[w], r1 = q1[w], s0 = r0 >> 8, s1 = r1 >> 8;
-    mma_step(lo, r0 & 0x000f000fu, r1 & 0x000f000fu, s0 & 0x000f000fu, s1 & 0x000f000fu, bb[w][0], bb[w][1]);
-    mma_step(hi, r0 & 0x00f000f0u, r1 & 0x00f000f0u, s0 & 0x00f000f0u, s1 & 0x00f000f0u, bb[w][2], bb[w][3]);
+    const uint32_t r0 = q00[w], r1 = q10[w], s0 = r0 >> 8, s1 = r1 >> 8;
+    const uint32_t u0 = q01[w], u1 = q11[w], v0 = u0 >> 8, v1 = u1 >> 8;
+    mma_step(lo0, r0 & 0x000f000fu, r1 & 0x000f000fu, s0 & 0x000f000fu, s1 & 0x000f000fu, b0[w].x, b0[w].y);
+    mma_step(lo1, u0 & 0x000f000fu, u1 & 0x000f000fu, v0 & 0x000f000fu, v1 & 0x000f000fu, b1[w].x, b1[w].y);
+    mma_step(hi0, r0 & 0x00f000f0u, r1 & 0x00f000f0u, s0 & 0x00f000f0u, s1 & 0x00f000f0u, b0[w].z, b0[w].w);
+    mma_step(hi1, u0 & 0x00f000f0u, u1 & 0x00f000f0u, v0 & 0x00f000f0u, v1 & 0x00f000f0u, b1[w].z, b1[w].w);
   }
 }
 
@@ -152,45 +177,60 @@ gemv_bulk_kernel(const __grid_constant__ CUtensorMap weights, const BulkArgs a) 
   const int W = a.consumers;
   const int stage_bytes = W * kChunkBytes;
   const int outputs = 16 * a.M;                 // results of one unit: [m][row]
-  float* red = reinterpret_cast<float*>(smem + size_t(a.stages) * stage_bytes);   // [2][W][outputs]
-  uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * W * outputs);             // [stages]
+  float* red = reinterpret_cast<float*>(smem + size_t(a.stages) * stage_bytes);   // [kRedBuffers][W][outputs]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + kRedBuffers * W * outputs);   // [stages]
   uint64_t* empty = full + a.stages;                                                // [stages]
-  uint64_t* red_full = empty + a.stages;                                            // [2]
-  uint64_t* red_empty = red_full + 2;                                               // [2]
-  volatile int* failed = reinterpret_cast<volatile int*>(red_empty + 2);
+  uint64_t* red_full = empty + a.stages;                                            // [kRedBuffers]
+  uint64_t* red_empty = red_full + kRedBuffers;                                     // [kRedBuffers]
+  volatile int* failed = reinterpret_cast<volatile int*>(red_empty + kRedBuffers);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int u0 = int(int64_t(blockIdx.x) * a.units / gridDim.x);
   const int u1 = int(int64_t(blockIdx.x + 1) * a.units / gridDim.x);
   const int n_units = u1 - u0;
+  const int slab_first = u0 / a.row_tiles, rt_first = u0 - slab_first * a.row_tiles;
 
-  if (threadIdx.x == 0) {
+  // The producer thread sets the barriers up and has the first ring of units on its way before
+  // anyone else runs: weights are constants, so it does not wait for the previous kernel either.
+  int issue_slab = slab_first, issue_rt = rt_first, issue_stage = 0;
+  auto issue_unit = [&]() {
+    const int stage = issue_stage, slab = issue_slab, rt = issue_rt;
+    if (++issue_stage == a.stages) issue_stage = 0;
+    if (++issue_rt == a.row_tiles) { issue_rt = 0; ++issue_slab; }
+    bar_expect(full + stage, uint32_t(stage_bytes));
+    const uint32_t dst = smem_u32(smem + size_t(stage) * stage_bytes);
+    if (a.rows_outer) unit_load(dst, &weights, slab * W, rt * 16, full + stage);
+    else unit_load(dst, &weights, rt * 16, slab * W, full + stage);
+  };
+  const int first_wave = n_units < a.stages ? n_units : a.stages;
+  if (warp == W && lane == 0) {
+    MKB_STAMP(0);
     for (int s = 0; s < a.stages; ++s) {
       bar_init(full + s, 1);
       bar_init(empty + s, W);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kRedBuffers; ++b) {
       bar_init(red_full + b, W);
       bar_init(red_empty + b, 1);
     }
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    MKB_STAMP(7);
+    for (int i = 0; i < first_wave; ++i) issue_unit();
+    MKB_STAMP(1);
   }
   __syncthreads();
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == W) {
-    // ---- producer: weights are constants, so it does not wait for the previous kernel ----
+    // ---- producer: refill a stage as soon as all consumer warps have read it ----
     if (lane == 0) {
-      int issued = 0;
-      for (int i = 0; i < n_units; ++i) {
-        const int stage = i % a.stages, round = i / a.stages;
-        if (round > 0 && !bar_wait(empty + stage, (round - 1) & 1, failed)) break;
-        const int u = u0 + i, slab = u / a.row_tiles, rt = u - slab * a.row_tiles;
-        bar_expect(full + stage, uint32_t(stage_bytes));
-        const uint32_t dst = smem_u32(smem + size_t(stage) * stage_bytes);
-        if (a.rows_outer) unit_load(dst, &weights, slab * W, rt * 16, full + stage);
-        else unit_load(dst, &weights, rt * 16, slab * W, full + stage);
+      int issued = first_wave;
+      uint32_t empty_phase = 0;
+      for (int i = first_wave; i < n_units; ++i) {
+        if (!bar_wait(empty + issue_stage, empty_phase, failed)) break;
+        if (issue_stage == a.stages - 1) empty_phase ^= 1u;
+        issue_unit();
         issued = i + 1;
       }
       if (*failed) {
@@ -223,23 +263,23 @@ gemv_bulk_kernel(const __grid_constant__ CUtensorMap weights, const BulkArgs a) 
     const uint32_t a00 = base + line0 + ((uint32_t(t) ^ x0) << 4), a01 = base + line0 + ((uint32_t(t + 4) ^ x0) << 4);
     const uint32_t a10 = base + line1 + ((uint32_t(t) ^ x1) << 4), a11 = base + line1 + ((uint32_t(t + 4) ^ x1) << 4);
 
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     uint4 b0[4], b1[4];            // B fragments of the chunk's two scale groups
     float bias0[2], bias1[2];      // min * sum(x) * 2^-24 of the two groups for activation rows 2t, 2t+1
-    int slab_now = -1;
     auto load_activations = [&](int slab) {
       const int chunk = slab * W + warp;
-      float sums[2] = {0.f, 0.f};
+      const bool live = g < a.M && chunk < a.chunks;
+      const uint4* src = reinterpret_cast<const uint4*>(a.x + int64_t(live ? g : 0) * a.K +
+                                                        int64_t(live ? chunk : 0) * 256 + t * 32);
+      uint4 v[8];   // all eight requests leave before the first is used
+#pragma unroll
+      for (int q = 0; q < 8; ++q) v[q] = live ? __ldg(src + (q >> 2) * 16 + (q & 3)) : make_uint4(0u, 0u, 0u, 0u);
+      float sums[2];
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         uint32_t xr[16];
-        const bool live = g < a.M && chunk < a.chunks;
-        const uint4* src = reinterpret_cast<const uint4*>(a.x + int64_t(live ? g : 0) * a.K +
-                                                          int64_t(live ? chunk : 0) * 256 + j * 128 + t * 32);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const uint4 v = live ? __ldg(src + q) : make_uint4(0u, 0u, 0u, 0u);
-          xr[4 * q] = v.x; xr[4 * q + 1] = v.y; xr[4 * q + 2] = v.z; xr[4 * q + 3] = v.w;
+          xr[4 * q] = v[4 * j + q].x; xr[4 * q + 1] = v[4 * j + q].y; xr[4 * q + 2] = v[4 * j + q].z; xr[4 * q + 3] = v[4 * j + q].w;
         }
         float sum = 0.f;
 #pragma unroll
@@ -259,49 +299,77 @@ gemv_bulk_kernel(const __grid_constant__ CUtensorMap weights, const BulkArgs a) 
       bias1[0] = __shfl_sync(0xffffffffu, sums[1], (2 * t) * 4);
       bias1[1] = __shfl_sync(0xffffffffu, sums[1], (2 * t + 1) * 4);
     };
-    // the four scales of a unit: rows rho, rho + 8 of the tile, the chunk's two groups
-    auto load_scales = [&](int u, __half (&s)[4]) {
-      const int slab = u / a.row_tiles, rt = u - slab * a.row_tiles;
+    // the four scales of a unit (rows rho, rho + 8 of the tile x the chunk's two groups) as two
+    // packed pairs; they are constants, so the first ones are requested before the dependency wait,
+    // and the loop keeps two units of them in flight
+    const bool paired = a.group_shift == 7 && (a.scale_row_stride & 1) == 0 && (reinterpret_cast<uintptr_t>(a.scales) & 3) == 0;
+    auto load_scales = [&](int slab, int rt, uint32_t (&s)[2]) {
       const int chunk = min(slab * W + warp, a.chunks - 1);
       const int64_t r0 = min(rt * 16 + rho, a.N - 1), r1 = min(rt * 16 + rho + 8, a.N - 1);
-      const int c0 = (chunk * 256) >> a.group_shift, c1 = (chunk * 256 + 128) >> a.group_shift;
-      s[0] = __ldg(a.scales + r0 * a.scale_row_stride + c0);
-      s[1] = __ldg(a.scales + r0 * a.scale_row_stride + c1);
-      s[2] = __ldg(a.scales + r1 * a.scale_row_stride + c0);
-      s[3] = __ldg(a.scales + r1 * a.scale_row_stride + c1);
+      const __half* p0 = a.scales + r0 * a.scale_row_stride;
+      const __half* p1 = a.scales + r1 * a.scale_row_stride;
+      if (paired) {
+        s[0] = __ldg(reinterpret_cast<const uint32_t*>(p0 + chunk * 2));
+        s[1] = __ldg(reinterpret_cast<const uint32_t*>(p1 + chunk * 2));
+      } else {
+        const int c0 = (chunk * 256) >> a.group_shift, c1 = (chunk * 256 + 128) >> a.group_shift;
+        const unsigned short* q0 = reinterpret_cast<const unsigned short*>(p0);
+        const unsigned short* q1 = reinterpret_cast<const unsigned short*>(p1);
+        s[0] = uint32_t(__ldg(q0 + c0)) | (uint32_t(__ldg(q0 + c1)) << 16);
+        s[1] = uint32_t(__ldg(q1 + c0)) | (uint32_t(__ldg(q1 + c1)) << 16);
+      }
     };
-    __half scale_next[4];
-    if (n_units > 0) load_scales(u0, scale_next);
+    auto advance = [&](int& slab, int& rt) {
+      if (++rt == a.row_tiles) { rt = 0; ++slab; }
+    };
+    int slab = slab_first, rt = rt_first;             // this unit
+    int slab_ahead = slab, rt_ahead = rt;             // the unit whose scales are requested next
+    int slab_now = -1;
+    uint32_t scale_now[2] = {0u, 0u}, scale_next[2] = {0u, 0u};
+    if (n_units > 0) { load_scales(slab_ahead, rt_ahead, scale_now); advance(slab_ahead, rt_ahead); }
+    if (n_units > 1) { load_scales(slab_ahead, rt_ahead, scale_next); advance(slab_ahead, rt_ahead); }
+
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (warp == 0 && lane == 0) { MKB_STAMP(2); }
+    int stage = 0;
+    uint32_t phase = 0, stage_offset = 0;
     for (int i = 0; i < n_units; ++i) {
-      const int u = u0 + i, slab = u / a.row_tiles;
       if (slab != slab_now) {
         load_activations(slab);
         slab_now = slab;
       }
-      const float s00 = __half2float(scale_next[0]), s01 = __half2float(scale_next[1]);
-      const float s10 = __half2float(scale_next[2]), s11 = __half2float(scale_next[3]);
-      if (i + 1 < n_units) load_scales(u + 1, scale_next);
+      uint32_t scale_after[2] = {0u, 0u};
+      if (i + 2 < n_units) { load_scales(slab_ahead, rt_ahead, scale_after); advance(slab_ahead, rt_ahead); }
 
-      const int stage = i % a.stages;
-      if (!bar_wait(full + stage, uint32_t(i / a.stages) & 1u, failed)) break;
-      const uint32_t stage_offset = uint32_t(stage) * uint32_t(stage_bytes);
+      if (!bar_wait(full + stage, phase, failed)) break;
+      if (warp == 0 && lane == 0) {
+        if (i == 0) { MKB_STAMP(3); }
+        if (i == n_units - 1) { MKB_STAMP(4); }
+      }
       const uint4 c00 = lds128(a00 + stage_offset), c10 = lds128(a10 + stage_offset);   // group 0: rows g, g+8
       const uint4 c01 = lds128(a01 + stage_offset), c11 = lds128(a11 + stage_offset);   // group 1
       __syncwarp();
       if (lane == 0) bar_arrive(empty + stage);
+      if (++stage == a.stages) { stage = 0; phase ^= 1u; stage_offset = 0; } else { stage_offset += uint32_t(stage_bytes); }
+      advance(slab, rt);
 
-      float lo[4] = {bias0[0], bias0[1], bias0[0], bias0[1]}, hi[4] = {0.f, 0.f, 0.f, 0.f};
-      group_steps(c00, c10, b0, lo, hi);
+      // 16 tensor-core steps in four independent accumulator chains (two groups x two lift classes)
+      float lo0[4] = {bias0[0], bias0[1], bias0[0], bias0[1]}, hi0[4] = {0.f, 0.f, 0.f, 0.f};
+      float lo1[4] = {bias1[0], bias1[1], bias1[0], bias1[1]}, hi1[4] = {0.f, 0.f, 0.f, 0.f};
+      group_steps(c00, c10, c01, c11, b0, b1, lo0, hi0, lo1, hi1);
+      const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&scale_now[0]));
+      const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&scale_now[1]));
       float y[4];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) y[q] = (q < 2 ? s00 : s10) * fmaf(hi[q], 0.0625f, lo[q]);
-      float lo1[4] = {bias1[0], bias1[1], bias1[0], bias1[1]}, hi1[4] = {0.f, 0.f, 0.f, 0.f};
-      group_steps(c01, c11, b1, lo1, hi1);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) y[q] = fmaf(q < 2 ? s01 : s11, fmaf(hi1[q], 0.0625f, lo1[q]), y[q]);
+      for (int q = 0; q < 4; ++q) {
+        const float first = (q < 2 ? f0.x : f1.x) * fmaf(hi0[q], 0.0625f, lo0[q]);
+        y[q] = fmaf(q < 2 ? f0.y : f1.y, fmaf(hi1[q], 0.0625f, lo1[q]), first);
+      }
+      scale_now[0] = scale_next[0]; scale_now[1] = scale_next[1];
+      scale_next[0] = scale_after[0]; scale_next[1] = scale_after[1];
 
       // partial sums of this warp: [m][memory row of the tile]
-      const int buffer = i & 1, use = i >> 1;
+      const int buffer = i & (kRedBuffers - 1), use = i / kRedBuffers;
       if (use > 0 && !bar_wait(red_empty + buffer, uint32_t(use - 1) & 1u, failed)) break;
       float* mine = red + (buffer * W + warp) * outputs;
       if (2 * t < a.M) {
@@ -315,62 +383,85 @@ gemv_bulk_kernel(const __grid_constant__ CUtensorMap weights, const BulkArgs a) 
       __syncwarp();
       if (lane == 0) bar_arrive(red_full + buffer);
     }
+    if (warp == 0 && lane == 0) { MKB_STAMP(5); }
   } else {
-    // ---- reducers: warp r takes the units of parity r ----
-    const int r = warp - W - 1;
+    // ---- reducers: warp r of R takes the units i = r, r + R, ... in batches, so that the slow part
+    // of a K split (fence, counter, reading the other slabs' sums) is paid once per batch ----
+    const int r = warp - W - 1, R = a.reducers;
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    for (int i = r; i < n_units; i += kReducerWarps) {
-      const int u = u0 + i, slab = u / a.row_tiles, rt = u - slab * a.row_tiles;
-      const int use = i >> 1;
-      if (!bar_wait(red_full + r, uint32_t(use) & 1u, failed)) break;
-      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+    int next_slab = slab_first, next_rt = rt_first + r;
+    while (next_rt >= a.row_tiles) { next_rt -= a.row_tiles; ++next_slab; }
+    auto store_rows = [&](const float (&sum)[4], int rt) {
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const int j = lane + 32 * q;
-        if (j < outputs) {
-          const float* partial = red + r * W * outputs + j;
-          for (int w = 0; w < W; ++w) sum[q] += partial[w * outputs];
+        const int j = lane + 32 * q, m = j >> 4, row = rt * 16 + (j & 15);
+        if (j < outputs && row < a.N) {
+          float value = sum[q] * 16777216.f;  // codes were c * 2^-24
+          if (a.bias != nullptr) value += __half2float(a.bias[row]);
+          a.y[int64_t(m) * a.N + row] = __float2half_rn(value);
         }
       }
-      __syncwarp();
-      if (lane == 0) bar_arrive(red_empty + r);
-
-      bool finish = true;
-      if (a.slabs > 1) {
-        float* slot = a.partials + (int64_t(rt) * a.slabs + slab) * outputs;
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-          if (lane + 32 * q < outputs) slot[lane + 32 * q] = sum[q];
-        __threadfence();
-        __syncwarp();
-        int arrived = 0;
-        if (lane == 0) arrived = atomicAdd(a.counters + rt, 1);
-        arrived = __shfl_sync(0xffffffffu, arrived, 0);
-        finish = arrived == a.slabs - 1;
-        if (finish) {
-          __threadfence();
-          const float* first = a.partials + int64_t(rt) * a.slabs * outputs;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            sum[q] = 0.f;
-            if (lane + 32 * q < outputs)
-              for (int s = 0; s < a.slabs; ++s) sum[q] += __ldcg(first + s * outputs + lane + 32 * q);
-          }
-          if (lane == 0) a.counters[rt] = 0;
-        }
-      }
-      if (finish) {
+    };
+    bool alive = true;
+    for (int i0 = r; i0 < n_units && alive; i0 += R * kBatch) {
+      int my_rt = -1;   // lane b keeps the row tile of the batch's unit b
+      for (int b = 0; b < kBatch; ++b) {
+        const int i = i0 + b * R;
+        if (i >= n_units) break;
+        const int slab = next_slab, rt = next_rt;
+        next_rt += R;
+        while (next_rt >= a.row_tiles) { next_rt -= a.row_tiles; ++next_slab; }
+        const int buffer = i & (kRedBuffers - 1), use = i / kRedBuffers;
+        if (!bar_wait(red_full + buffer, uint32_t(use) & 1u, failed)) { alive = false; break; }
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const int j = lane + 32 * q, m = j >> 4, row = rt * 16 + (j & 15);
-          if (j < outputs && row < a.N) {
-            float value = sum[q] * 16777216.f;  // codes were c * 2^-24
-            if (a.bias != nullptr) value += __half2float(a.bias[row]);
-            a.y[int64_t(m) * a.N + row] = __float2half_rn(value);
+          const int j = lane + 32 * q;
+          if (j < outputs) {
+            const float* partial = red + buffer * W * outputs + j;
+            float part[kMaxConsumers];
+#pragma unroll
+            for (int w = 0; w < kMaxConsumers; ++w) part[w] = w < W ? partial[w * outputs] : 0.f;
+#pragma unroll
+            for (int w = 0; w < kMaxConsumers; ++w) sum[q] += part[w];
           }
+        }
+        __syncwarp();
+        if (lane == 0) bar_arrive(red_empty + buffer);
+        if (a.slabs == 1) {
+          store_rows(sum, rt);
+        } else {
+          float* slot = a.partials + (int64_t(rt) * a.slabs + slab) * outputs;
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            if (lane + 32 * q < outputs) slot[lane + 32 * q] = sum[q];
+          if (lane == b) my_rt = rt;
+        }
+      }
+      if (a.slabs > 1) {
+        // publish the batch: the sums above must be visible before the counters move
+        __threadfence();
+        __syncwarp();
+        const int arrived = my_rt >= 0 ? atomicAdd(a.counters + my_rt, 1) : -1;
+        unsigned finishing = __ballot_sync(0xffffffffu, arrived == a.slabs - 1);
+        if (finishing) __threadfence();
+        while (finishing) {
+          const int b = __ffs(finishing) - 1;
+          finishing &= finishing - 1;
+          const int rt = __shfl_sync(0xffffffffu, my_rt, b);
+          const float* first = a.partials + int64_t(rt) * a.slabs * outputs;
+          float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+          for (int s = 0; s < a.slabs; ++s)
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              if (lane + 32 * q < outputs) sum[q] += __ldcg(first + s * outputs + lane + 32 * q);
+          store_rows(sum, rt);
+          if (lane == b) a.counters[rt] = 0;
         }
       }
     }
+    if (lane == 0 && r == 0) { MKB_STAMP(6); }
     if (*failed && lane == 0 && a.status != nullptr) atomicExch(a.status, 1);
   }
 }
@@ -439,16 +530,31 @@ int weight_map(const uint8_t* packed, int N, int chunks, int64_t row_stride, int
   return MKB_OK;
 }
 
-// K split: W consumer warps take one 256-code chunk each, S slabs of W chunks cover a row.
-void split_for(int N, int K, int sm_count, int& consumers, int& slabs) {
+// K split: W consumer warps take one 256-code chunk each, S slabs of W chunks cover a row.  Thin
+// CTAs (W <= 8) run two to an SM with one reducer warp, wide ones alone with two.
+struct Split {
+  int consumers, slabs, ctas_per_sm, reducers;
+};
+
+Split split_for(int N, int K, int sm_count) {
   const int chunks = K / 256, row_tiles = (N + 15) / 16;
-  slabs = (chunks + kMaxConsumers - 1) / kMaxConsumers;
-  consumers = (chunks + slabs - 1) / slabs;
+  Split split{};
+  split.slabs = (chunks + kMaxConsumers - 1) / kMaxConsumers;
+  split.consumers = (chunks + split.slabs - 1) / split.slabs;
   // small layers: more, thinner units until every SM has a few
-  while (consumers >= 8 && consumers % 2 == 0 && int64_t(slabs) * row_tiles < 2 * sm_count) {
-    slabs *= 2;
-    consumers /= 2;
+  while (split.consumers >= 8 && split.consumers % 2 == 0 && int64_t(split.slabs) * row_tiles < 2 * sm_count) {
+    split.slabs *= 2;
+    split.consumers /= 2;
   }
+#ifdef MKB_STAMPS
+  if (g_probe_consumers > 0) {
+    split.consumers = g_probe_consumers;
+    split.slabs = (chunks + split.consumers - 1) / split.consumers;
+  }
+#endif
+  split.ctas_per_sm = split.consumers <= 8 ? 2 : 1;
+  split.reducers = split.consumers <= 8 ? 1 : 2;
+  return split;
 }
 
 }  // namespace
@@ -468,10 +574,9 @@ int gemv_bulk_supported(int M, int N, int K, int group, int bits, int x_dtype, i
 // Bytes of workspace the K split of this shape needs (0: none).
 int64_t gemv_bulk_workspace_bytes(int M, int N, int K) {
   if (K < 256 || K % 256 != 0 || N < 1) return 0;
-  int consumers = 0, slabs = 0;
-  split_for(N, K, device_info().sm_count, consumers, slabs);
-  if (slabs <= 1) return 0;
-  return kHeadBytes + int64_t((N + 15) / 16) * slabs * 16 * M * 4;
+  const Split split = split_for(N, K, device_info().sm_count);
+  if (split.slabs <= 1) return 0;
+  return kHeadBytes + int64_t((N + 15) / 16) * split.slabs * 16 * M * 4;
 }
 
 int launch_gemv_bulk(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y,
@@ -486,7 +591,8 @@ int launch_gemv_bulk(const void* x, const uint8_t* packed, const void* scales, c
   const DeviceInfo& info = device_info();
   a.chunks = K / 256;
   a.row_tiles = (N + 15) / 16;
-  split_for(N, K, info.sm_count, a.consumers, a.slabs);
+  const Split split = split_for(N, K, info.sm_count);
+  a.consumers = split.consumers; a.slabs = split.slabs; a.reducers = split.reducers;
   a.units = a.row_tiles * a.slabs;
   if (a.slabs > 1) {
     MKB_REQUIRE(workspace != nullptr && workspace_bytes >= gemv_bulk_workspace_bytes(M, N, K), MKB_E_UNSUPPORTED,
@@ -499,17 +605,27 @@ int launch_gemv_bulk(const void* x, const uint8_t* packed, const void* scales, c
     a.status = static_cast<int*>(workspace) + kMaxRowTiles;
   }
 
+  // shared memory: the ring takes what the partial-sum buffers and barriers leave of the CTA's share
   const int stage_bytes = a.consumers * kChunkBytes;
-  const size_t fixed = 1024 + size_t(2) * a.consumers * 16 * M * 4 + size_t(2 * kMaxStages + 4) * 8 + 16;
-  int stages = int((size_t(info.max_smem_optin) - fixed) / stage_bytes);
+  const size_t share = split.ctas_per_sm == 1 ? size_t(info.max_smem_optin)
+                                              : (size_t(info.max_smem_optin) + 1024) / 2 - 1024;
+  const size_t red_bytes = size_t(kRedBuffers) * a.consumers * 16 * M * 4;
+  const size_t fixed = 1024 + red_bytes + size_t(2 * kMaxStages + 2 * kRedBuffers) * 8 + 16;
+  MKB_REQUIRE(share > fixed + 2 * size_t(stage_bytes), MKB_E_UNSUPPORTED, "gemv_bulk: shared memory holds fewer than two stages");
+  int stages = int((share - fixed) / stage_bytes);
   if (stages > kMaxStages) stages = kMaxStages;
-  MKB_REQUIRE(stages >= 2, MKB_E_UNSUPPORTED, "gemv_bulk: shared memory holds fewer than two stages");
-  int grid = info.sm_count < a.units ? info.sm_count : a.units;
+  int grid = info.sm_count * split.ctas_per_sm;
+  if (grid > a.units) grid = a.units;
   const int most = (a.units + grid - 1) / grid;
   if (stages > most) stages = most;  // no CTA ever has more units than this
+#ifdef MKB_STAMPS
+  if (g_probe_stage_cap > 1 && stages > g_probe_stage_cap) stages = g_probe_stage_cap;
+  a.stamps = g_probe_stamps;
+  a.launch_id = g_probe_launch++;
+
+#endif
   a.stages = stages;
-  const size_t smem = 1024 + size_t(stages) * stage_bytes + size_t(2) * a.consumers * 16 * M * 4 +
-                      size_t(2 * stages + 4) * 8 + 16;
+  const size_t smem = 1024 + size_t(stages) * stage_bytes + red_bytes + size_t(2 * stages + 2 * kRedBuffers) * 8 + 16;
 
   MapEntry entry;
   int status = weight_map(packed, N, a.chunks, packed_row_stride, a.consumers, entry);
@@ -522,12 +638,15 @@ int launch_gemv_bulk(const void* x, const uint8_t* packed, const void* scales, c
   if (device >= 0 && device < 64 && !configured[device]) {
     cudaError_t set = cudaFuncSetAttribute(gemv_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            info.max_smem_optin);
+    if (set == cudaSuccess)
+      set = cudaFuncSetAttribute(gemv_bulk_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared);
     if (set != cudaSuccess) return cuda_fail(set, "gemv_bulk: shared memory opt-in");
     configured[device] = true;
   }
   cudaLaunchConfig_t config{};
   config.gridDim = dim3(grid, 1, 1);
-  config.blockDim = dim3((a.consumers + 1 + kReducerWarps) * 32, 1, 1);
+  config.blockDim = dim3((a.consumers + 1 + a.reducers) * 32, 1, 1);
   config.dynamicSmemBytes = smem;
   config.stream = stream;
   cudaLaunchAttribute attribute[1];
