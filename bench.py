@@ -39,9 +39,11 @@ ROW_COUNTS = (1, 2, 4, 8)
 BLOCKS = 8
 BITS, GROUP = 4, 128
 METRIC = "packed_int4_g128_gemv_hbm_gbps"
-# dram__bytes_read.sum + dram__bytes_write.sum of one gate-shape launch (4096 -> 14336, M = 1) from the
-# profiler capture summarised in profiles/gemv_tiled_gate_4096x14336.md; refreshed when the kernel changes
-GATE_DRAM_BYTES_PER_LAUNCH = 30.35e6
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate-shape launch (4096 -> 14336) from the profiler
+# captures summarised in profiles/gemv_tiled_gate_4096x14336_M1.md and gemv_bulk_gate_4096x14336_M8.md;
+# refreshed when a kernel changes
+TILED_GATE_M1_DRAM_BYTES = 30.3145e6
+BULK_GATE_M8_DRAM_BYTES = 30.3875e6
 
 
 def gemv_bytes(out_rows: int, width: int, rows_in: int) -> int:
@@ -364,10 +366,11 @@ def main() -> None:
         table = per_layer_table(blocks, inputs, outputs, peak)
     step_bytes = pass_bytes(BLOCKS)
     value = step_bytes / resident_ms / 1e6
-    gate = [table[f"gate_4096x14336_M{m}"] for m in ROW_COUNTS]
-    gate_bytes = statistics.mean(gemv_bytes(14336, 4096, m) for m in ROW_COUNTS)
-    gate_us = statistics.mean(entry["us"] for entry in gate)
+    # the dominant kernel by share of device time is the tiled kernel (profiles/bench_launch_list.md);
+    # its largest launch is the gate/up shape at one row.  The TMA-fed kernel takes the same shape at 8 rows.
+    gate_bytes, gate_us = gemv_bytes(14336, 4096, 1), table["gate_4096x14336_M1"]["us"]
     achieved = gate_bytes / gate_us / 1e3
+    bulk_bytes, bulk_us = gemv_bytes(14336, 4096, 8), table["gate_4096x14336_M8"]["us"]
 
     cpu_seconds, cpu_threads, cpu_bytes = time_cpu_route(repetitions=3, warmup=1)
     line = {
@@ -382,9 +385,13 @@ def main() -> None:
         "gpu_launches": launches,
         "clocks": sampler.summary,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind,
-                     "kernel": "gemv_tiled_kernel<4, raw> on gate/up 4096->14336, mean over M in {1,2,4,8}",
+                     "traffic": TILED_GATE_M1_DRAM_BYTES, "peak_kind": peak_kind,
+                     "kernel": "gemv_tiled_kernel<4, raw> on gate/up 4096->14336, M=1",
                      "bytes_per_launch": gate_bytes, "us_per_launch": gate_us},
+        "roofline_bulk": {"bound": "hbm", "achieved": bulk_bytes / bulk_us / 1e3, "peak": peak, "unit": "GB/s",
+                          "frac": bulk_bytes / bulk_us / 1e3 / peak, "traffic": BULK_GATE_M8_DRAM_BYTES,
+                          "peak_kind": peak_kind, "kernel": "gemv_bulk_kernel on gate/up 4096->14336, M=8",
+                          "bytes_per_launch": bulk_bytes, "us_per_launch": bulk_us},
         "per_layer": table,
         "cpu_baseline": {"value": cpu_bytes / cpu_seconds / 1e9, "unit": "GB/s", "cores": cpu_threads, "kind": "port",
                          "sample": "one decoder block (7 linears, 109 MB packed), M=1, median of 3 passes"},
@@ -403,7 +410,6 @@ def main() -> None:
         "per_gpu_roofline_frac": {f"batch{b}": r["per_gpu_gbps"] / peak for b, r in decode["batches"].items()},
         "launches_per_step": decode["launches_per_step"],
     }
-    line["roofline"]["traffic"] = GATE_DRAM_BYTES_PER_LAUNCH
     print(json.dumps(line))
 
 
