@@ -32,7 +32,7 @@ namespace mkb {
 namespace {
 
 constexpr int kMaxConsumers = 16;
-constexpr int kMaxReducers = 3;
+constexpr int kMaxReducers = 2;
 constexpr int kMaxThreadsB = (kMaxConsumers + 1 + kMaxReducers) * 32;
 constexpr int kRedBuffers = 4;            // ring of partial-sum buffers between consumers and reducers
 constexpr int kBatch = 4;                 // units a reducer publishes together when K is split
@@ -101,6 +101,14 @@ __device__ __forceinline__ bool bar_wait(uint64_t* bar, uint32_t parity, volatil
   return false;
 }
 
+// One look at the barrier, no waiting.
+__device__ __forceinline__ bool bar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+               : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
+
 // One unit: box {128 bytes, 16 rows, W chunks} at (0, first row, first chunk); rows and chunks past
 // the tensor are filled with zeros and still count toward the barrier's byte total.
 __device__ __forceinline__ void unit_load(uint32_t dst, const CUtensorMap* map, int c1, int c2, uint64_t* bar) {
@@ -122,6 +130,15 @@ __device__ __forceinline__ void mma_step(float (&d)[4], uint32_t a0, uint32_t a1
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// The first step of an accumulator chain: C = 0 comes from the zero register, no initialisation.
+__device__ __forceinline__ void mma_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 
 // Position p = 8*w + 2*j + h of a lane's 32 activations (unit w, register j, half h) faces this code
@@ -161,10 +178,17 @@ __device__ __forceinline__ void group_steps(const uint4& c00, const uint4& c10, 
   for (int w = 0; w < 4; ++w) {
     const uint32_t r0 = q00[w], r1 = q10[w], s0 = r0 >> 8, s1 = r1 >> 8;
     const uint32_t u0 = q01[w], u1 = q11[w], v0 = u0 >> 8, v1 = u1 >> 8;
-    mma_step(lo0, r0 & 0x000f000fu, r1 & 0x000f000fu, s0 & 0x000f000fu, s1 & 0x000f000fu, b0[w].x, b0[w].y);
-    mma_step(lo1, u0 & 0x000f000fu, u1 & 0x000f000fu, v0 & 0x000f000fu, v1 & 0x000f000fu, b1[w].x, b1[w].y);
-    mma_step(hi0, r0 & 0x00f000f0u, r1 & 0x00f000f0u, s0 & 0x00f000f0u, s1 & 0x00f000f0u, b0[w].z, b0[w].w);
-    mma_step(hi1, u0 & 0x00f000f0u, u1 & 0x00f000f0u, v0 & 0x00f000f0u, v1 & 0x00f000f0u, b1[w].z, b1[w].w);
+    if (w == 0) {
+      mma_first(lo0, r0 & 0x000f000fu, r1 & 0x000f000fu, s0 & 0x000f000fu, s1 & 0x000f000fu, b0[w].x, b0[w].y);
+      mma_first(lo1, u0 & 0x000f000fu, u1 & 0x000f000fu, v0 & 0x000f000fu, v1 & 0x000f000fu, b1[w].x, b1[w].y);
+      mma_first(hi0, r0 & 0x00f000f0u, r1 & 0x00f000f0u, s0 & 0x00f000f0u, s1 & 0x00f000f0u, b0[w].z, b0[w].w);
+      mma_first(hi1, u0 & 0x00f000f0u, u1 & 0x00f000f0u, v0 & 0x00f000f0u, v1 & 0x00f000f0u, b1[w].z, b1[w].w);
+    } else {
+      mma_step(lo0, r0 & 0x000f000fu, r1 & 0x000f000fu, s0 & 0x000f000fu, s1 & 0x000f000fu, b0[w].x, b0[w].y);
+      mma_step(lo1, u0 & 0x000f000fu, u1 & 0x000f000fu, v0 & 0x000f000fu, v1 & 0x000f000fu, b1[w].x, b1[w].y);
+      mma_step(hi0, r0 & 0x00f000f0u, r1 & 0x00f000f0u, s0 & 0x00f000f0u, s1 & 0x00f000f0u, b0[w].z, b0[w].w);
+      mma_step(hi1, u0 & 0x00f000f0u, u1 & 0x00f000f0u, v0 & 0x00f000f0u, v1 & 0x00f000f0u, b1[w].z, b1[w].w);
+    }
   }
 }
 
@@ -346,24 +370,23 @@ gemv_bulk_kernel(const __grid_constant__ CUtensorMap weights, const BulkArgs a) 
         if (i == 0) { MKB_STAMP(3); }
         if (i == n_units - 1) { MKB_STAMP(4); }
       }
-      const uint4 c00 = lds128(a00 + stage_offset), c10 = lds128(a10 + stage_offset);   // group 0: rows g, g+8
-      const uint4 c01 = lds128(a01 + stage_offset), c11 = lds128(a11 + stage_offset);   // group 1
+      const uint4 d00 = lds128(a00 + stage_offset), d10 = lds128(a10 + stage_offset);   // group 0: rows g, g+8
+      const uint4 d01 = lds128(a01 + stage_offset), d11 = lds128(a11 + stage_offset);   // group 1
       __syncwarp();
       if (lane == 0) bar_arrive(empty + stage);
       if (++stage == a.stages) { stage = 0; phase ^= 1u; stage_offset = 0; } else { stage_offset += uint32_t(stage_bytes); }
       advance(slab, rt);
 
       // 16 tensor-core steps in four independent accumulator chains (two groups x two lift classes)
-      float lo0[4] = {bias0[0], bias0[1], bias0[0], bias0[1]}, hi0[4] = {0.f, 0.f, 0.f, 0.f};
-      float lo1[4] = {bias1[0], bias1[1], bias1[0], bias1[1]}, hi1[4] = {0.f, 0.f, 0.f, 0.f};
-      group_steps(c00, c10, c01, c11, b0, b1, lo0, hi0, lo1, hi1);
+      float lo0[4], hi0[4], lo1[4], hi1[4];
+      group_steps(d00, d10, d01, d11, b0, b1, lo0, hi0, lo1, hi1);
       const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&scale_now[0]));
       const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&scale_now[1]));
       float y[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const float first = (q < 2 ? f0.x : f1.x) * fmaf(hi0[q], 0.0625f, lo0[q]);
-        y[q] = fmaf(q < 2 ? f0.y : f1.y, fmaf(hi1[q], 0.0625f, lo1[q]), first);
+        const float first = (q < 2 ? f0.x : f1.x) * (fmaf(hi0[q], 0.0625f, lo0[q]) + bias0[q & 1]);
+        y[q] = fmaf(q < 2 ? f0.y : f1.y, fmaf(hi1[q], 0.0625f, lo1[q]) + bias1[q & 1], first);
       }
       scale_now[0] = scale_next[0]; scale_now[1] = scale_next[1];
       scale_next[0] = scale_after[0]; scale_next[1] = scale_after[1];
