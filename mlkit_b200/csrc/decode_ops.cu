@@ -22,6 +22,10 @@ __device__ __forceinline__ float warp_max(float v) {
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(__half* __restrict__ residual, const __half* __restrict__ delta,
                                                           const __half* __restrict__ weight, __half* __restrict__ normed,
                                                           int H, float eps) {
+  // programmatic dependent launch: let the next kernel in the stream become resident now (a matvec
+  // starts streaming its weights), then wait for everything this kernel reads
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   extern __shared__ float row_s[];  // [H]
   __shared__ float part_s[8];
   const int64_t base = int64_t(blockIdx.x) * H;
@@ -59,6 +63,10 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(__half* __restrict__ r
 __global__ void rope_append_kernel(__half* __restrict__ qkv, const int* __restrict__ positions,
                                    __half* __restrict__ k_cache, __half* __restrict__ v_cache, int q_heads,
                                    int kv_heads, int D, int capacity, float theta) {
+  // programmatic dependent launch: let the next kernel in the stream become resident now (a matvec
+  // starts streaming its weights), then wait for everything this kernel reads
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int m = blockIdx.x, head = blockIdx.y;  // head over q_heads + kv_heads (+ kv_heads for v)
   const int position = positions[m];
   const int row = (q_heads + 2 * kv_heads) * D;
@@ -92,6 +100,10 @@ __global__ void __launch_bounds__(256) attention_decode_kernel(const __half* __r
                                                                const __half* __restrict__ k_cache,
                                                                const __half* __restrict__ v_cache, __half* __restrict__ out,
                                                                int q_heads, int kv_heads, int capacity, float scale) {
+  // programmatic dependent launch: let the next kernel in the stream become resident now (a matvec
+  // starts streaming its weights), then wait for everything this kernel reads
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   constexpr int D = 128;
   extern __shared__ float score_s[];  // [capacity]
   __shared__ float q_s[D];
@@ -175,6 +187,10 @@ __global__ void __launch_bounds__(256) attention_decode_kernel(const __half* __r
 
 // out[m, i] = silu(gate_up[m, i]) * gate_up[m, I + i]
 __global__ void silu_mul_kernel(const __half* __restrict__ gate_up, __half* __restrict__ out, int64_t rows, int I) {
+  // programmatic dependent launch: let the next kernel in the stream become resident now (a matvec
+  // starts streaming its weights), then wait for everything this kernel reads
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t index = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) * 2;
   if (index >= rows * I) return;
   const int64_t m = index / I, i = index - m * I;
@@ -184,6 +200,23 @@ __global__ void silu_mul_kernel(const __half* __restrict__ gate_up, __half* __re
   // the activation is rounded to fp16 before the product, as separate fp16 module ops would do
   const float2 act = __half22float2(__floats2half2_rn(a, b));
   *reinterpret_cast<__half2*>(out + m * I + i) = __floats2half2_rn(act.x * u.x, act.y * u.y);
+}
+
+// Launch with the programmatic-stream-serialization attribute: the kernel may become resident while
+// its predecessor drains; it executes griddepcontrol.wait before it touches memory.
+template <typename... Params, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, void* stream, Args... args) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, Params(args)...);
 }
 
 }  // namespace
@@ -202,10 +235,10 @@ extern "C" int mkb_add_rmsnorm(void* residual, const void* delta, const void* we
     cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
     opted = true;
   }
-  add_rmsnorm_kernel<<<M, 256, smem, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__half*>(residual), static_cast<const __half*>(delta), static_cast<const __half*>(weight),
-      static_cast<__half*>(normed), H, eps);
-  MKB_LAUNCH_CHECK("add_rmsnorm launch");
+  const cudaError_t launched = launch_dependent(
+      add_rmsnorm_kernel, dim3(M), dim3(256), smem, stream, static_cast<__half*>(residual),
+      static_cast<const __half*>(delta), static_cast<const __half*>(weight), static_cast<__half*>(normed), H, eps);
+  if (launched != cudaSuccess) return cuda_fail(launched, "add_rmsnorm launch");
   return MKB_OK;
 }
 
@@ -216,10 +249,10 @@ extern "C" int mkb_rope_append(void* qkv, const int* positions, void* k_cache, v
               MKB_E_ARGUMENT, "rope_append: bad shape");
   if (M == 0) return MKB_OK;
   MKB_REQUIRE(qkv && positions && k_cache && v_cache, MKB_E_ARGUMENT, "rope_append: null pointer");
-  rope_append_kernel<<<dim3(M, q_heads + 2 * kv_heads), 64, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__half*>(qkv), positions, static_cast<__half*>(k_cache), static_cast<__half*>(v_cache), q_heads,
-      kv_heads, head_dim, capacity, theta);
-  MKB_LAUNCH_CHECK("rope_append launch");
+  const cudaError_t launched = launch_dependent(
+      rope_append_kernel, dim3(M, q_heads + 2 * kv_heads), dim3(64), 0, stream, static_cast<__half*>(qkv), positions,
+      static_cast<__half*>(k_cache), static_cast<__half*>(v_cache), q_heads, kv_heads, head_dim, capacity, theta);
+  if (launched != cudaSuccess) return cuda_fail(launched, "rope_append launch");
   return MKB_OK;
 }
 
@@ -239,10 +272,11 @@ extern "C" int mkb_attention_decode(const void* qkv, const int* positions, const
     cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 164 * 1024);
     opted = true;
   }
-  attention_decode_kernel<<<dim3(M, q_heads), 256, smem, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __half*>(qkv), positions, static_cast<const __half*>(k_cache),
-      static_cast<const __half*>(v_cache), static_cast<__half*>(out), q_heads, kv_heads, capacity, scale);
-  MKB_LAUNCH_CHECK("attention_decode launch");
+  const cudaError_t launched = launch_dependent(
+      attention_decode_kernel, dim3(M, q_heads), dim3(256), smem, stream, static_cast<const __half*>(qkv), positions,
+      static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), static_cast<__half*>(out), q_heads,
+      kv_heads, capacity, scale);
+  if (launched != cudaSuccess) return cuda_fail(launched, "attention_decode launch");
   return MKB_OK;
 }
 
@@ -252,8 +286,9 @@ extern "C" int mkb_silu_mul(const void* gate_up, void* out, int M, int I, void* 
   if (M == 0) return MKB_OK;
   MKB_REQUIRE(gate_up && out, MKB_E_ARGUMENT, "silu_mul: null pointer");
   const int64_t pairs = int64_t(M) * I / 2;
-  silu_mul_kernel<<<unsigned((pairs + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __half*>(gate_up), static_cast<__half*>(out), M, I);
-  MKB_LAUNCH_CHECK("silu_mul launch");
+  const cudaError_t launched = launch_dependent(silu_mul_kernel, dim3(unsigned((pairs + 255) / 256)), dim3(256), 0,
+                                                stream, static_cast<const __half*>(gate_up), static_cast<__half*>(out),
+                                                int64_t(M), I);
+  if (launched != cudaSuccess) return cuda_fail(launched, "silu_mul launch");
   return MKB_OK;
 }
