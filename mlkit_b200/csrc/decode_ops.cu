@@ -18,8 +18,81 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// residual[m,:] += delta[m,:] (when delta != null); normed[m,:] = residual[m,:] * rsqrt(mean(sq) + eps) * weight
-__global__ void __launch_bounds__(256) add_rmsnorm_kernel(__half* __restrict__ residual, const __half* __restrict__ delta,
+// residual[m,:] += delta[m,:] (when delta != null); normed[m,:] = residual[m,:] * rsqrt(mean(sq) + eps) * weight.
+// One CTA of 1024 threads per row; a thread keeps its (up to two) 8-element pieces in registers
+// between the two passes, so the row is read once.
+constexpr int kNormThreads = 1024;
+constexpr int kNormPieces = 2;   // rows up to 1024 * 2 * 8 = 16384 elements stay in registers
+
+__global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__half* __restrict__ residual,
+                                                                   const __half* __restrict__ delta,
+                                                                   const __half* __restrict__ weight,
+                                                                   __half* __restrict__ normed, int H, float eps) {
+  // programmatic dependent launch: let the next kernel in the stream become resident now (a matvec
+  // starts streaming its weights), then wait for everything this kernel reads
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  __shared__ float part_s[kNormThreads / 32];
+  const int64_t base = int64_t(blockIdx.x) * H;
+  uint4 kept[kNormPieces];
+  float sq = 0.f;
+#pragma unroll
+  for (int piece = 0; piece < kNormPieces; ++piece) {
+    const int i = (piece * kNormThreads + threadIdx.x) * 8;
+    kept[piece] = make_uint4(0u, 0u, 0u, 0u);
+    if (i < H) {
+      uint4 v = *reinterpret_cast<const uint4*>(residual + base + i);
+      if (delta != nullptr) {
+        const uint4 d = *reinterpret_cast<const uint4*>(delta + base + i);
+        // the sum is stored back in fp16: the running residual of the model is an fp16 tensor
+        __half2* vh = reinterpret_cast<__half2*>(&v);
+        const __half2* dh = reinterpret_cast<const __half2*>(&d);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 a = __half22float2(vh[q]), b = __half22float2(dh[q]);
+          vh[q] = __floats2half2_rn(a.x + b.x, a.y + b.y);
+        }
+        *reinterpret_cast<uint4*>(residual + base + i) = v;
+      }
+      kept[piece] = v;
+      const __half2* vh = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 a = __half22float2(vh[q]);
+        sq += a.x * a.x + a.y * a.y;
+      }
+    }
+  }
+  sq = warp_sum(sq);
+  if ((threadIdx.x & 31) == 0) part_s[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int w = 0; w < kNormThreads / 32; ++w) total += part_s[w];
+  const float inv = rsqrtf(total / float(H) + eps);
+#pragma unroll
+  for (int piece = 0; piece < kNormPieces; ++piece) {
+    const int i = (piece * kNormThreads + threadIdx.x) * 8;
+    if (i < H) {
+      const uint4 w = *reinterpret_cast<const uint4*>(weight + i);
+      const __half2* vh = reinterpret_cast<const __half2*>(&kept[piece]);
+      const __half2* wh = reinterpret_cast<const __half2*>(&w);
+      uint4 result;
+      __half2* rh = reinterpret_cast<__half2*>(&result);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 a = __half22float2(vh[q]), ww = __half22float2(wh[q]);
+        // same rounding points as the usual fp16 module: the normalised value is rounded, then scaled
+        const float2 u = __half22float2(__floats2half2_rn(a.x * inv, a.y * inv));
+        rh[q] = __floats2half2_rn(u.x * ww.x, u.y * ww.y);
+      }
+      *reinterpret_cast<uint4*>(normed + base + i) = result;
+    }
+  }
+}
+
+// Any even row length (rows staged in shared memory): residual[m,:] += delta[m,:] (when delta != null); normed[m,:] = residual[m,:] * rsqrt(mean(sq) + eps) * weight
+__global__ void __launch_bounds__(256) add_rmsnorm_generic_kernel(__half* __restrict__ residual, const __half* __restrict__ delta,
                                                           const __half* __restrict__ weight, __half* __restrict__ normed,
                                                           int H, float eps) {
   // programmatic dependent launch: let the next kernel in the stream become resident now (a matvec
@@ -91,15 +164,19 @@ __global__ void rope_append_kernel(__half* __restrict__ qkv, const int* __restri
   }
 }
 
-// One CTA of 256 threads per (sequence m, query head), head_dim 128.
-//   1. scores: a thread owns whole cached positions (independent 256-byte key reads, q in registers);
+// One CTA of 512 threads per (sequence m, query head), head_dim 128.
+//   1. scores: a thread owns whole cached positions (16 independent 16-byte key reads, q in shared
+//      memory, read as broadcasts);
 //   2. block-wide max and sum of exp;
-//   3. values: thread (slice, dim pair) accumulates its quarter of the positions, four loads in
-//      flight; the four slices meet in shared memory.
-__global__ void __launch_bounds__(256) attention_decode_kernel(const __half* __restrict__ qkv, const int* __restrict__ positions,
-                                                               const __half* __restrict__ k_cache,
-                                                               const __half* __restrict__ v_cache, __half* __restrict__ out,
-                                                               int q_heads, int kv_heads, int capacity, float scale) {
+//   3. values: warp w takes positions w, w + 16, ...; a lane owns four dimensions (one 8-byte read
+//      per position, a warp reads a whole 256-byte row), eight positions in flight; the 16 warps
+//      meet in shared memory.
+constexpr int kAttentionThreads = 512;
+constexpr int kAttentionWarps = kAttentionThreads / 32;
+
+__global__ void __launch_bounds__(kAttentionThreads) attention_decode_kernel(
+    const __half* __restrict__ qkv, const int* __restrict__ positions, const __half* __restrict__ k_cache,
+    const __half* __restrict__ v_cache, __half* __restrict__ out, int q_heads, int kv_heads, int capacity, float scale) {
   // programmatic dependent launch: let the next kernel in the stream become resident now (a matvec
   // starts streaming its weights), then wait for everything this kernel reads
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -107,8 +184,8 @@ __global__ void __launch_bounds__(256) attention_decode_kernel(const __half* __r
   constexpr int D = 128;
   extern __shared__ float score_s[];  // [capacity]
   __shared__ float q_s[D];
-  __shared__ float part_s[8];
-  __shared__ float acc_s[4][D];
+  __shared__ float part_s[kAttentionWarps];
+  __shared__ float acc_s[kAttentionWarps][D];
   const int m = blockIdx.x, head = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int length = positions[m] + 1;  // the new token was appended already
   const int kv = head / (q_heads / kv_heads);
@@ -119,20 +196,23 @@ __global__ void __launch_bounds__(256) attention_decode_kernel(const __half* __r
   const __half* values = v_cache + (int64_t(m) * kv_heads + kv) * capacity * D;
 
   float local_max = -INFINITY;
-  for (int p = threadIdx.x; p < length; p += 256) {
+  for (int p = threadIdx.x; p < length; p += kAttentionThreads) {
     const uint4* key = reinterpret_cast<const uint4*>(keys + int64_t(p) * D);
-    float dot = 0.f;
+    uint4 raw[D / 8];
+#pragma unroll
+    for (int v = 0; v < D / 8; ++v) raw[v] = __ldg(key + v);
+    float dot0 = 0.f, dot1 = 0.f;
 #pragma unroll
     for (int v = 0; v < D / 8; ++v) {
-      const uint4 raw = __ldg(key + v);
-      const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+      const uint32_t words[4] = {raw[v].x, raw[v].y, raw[v].z, raw[v].w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float2 k2 = __half22float2(*reinterpret_cast<const __half2*>(&words[i]));
-        dot = fmaf(q_s[v * 8 + 2 * i], k2.x, dot);
-        dot = fmaf(q_s[v * 8 + 2 * i + 1], k2.y, dot);
+        dot0 = fmaf(q_s[v * 8 + 2 * i], k2.x, dot0);
+        dot1 = fmaf(q_s[v * 8 + 2 * i + 1], k2.y, dot1);
       }
     }
+    const float dot = dot0 + dot1;
     score_s[p] = dot;
     local_max = fmaxf(local_max, dot);
   }
@@ -141,10 +221,10 @@ __global__ void __launch_bounds__(256) attention_decode_kernel(const __half* __r
   __syncthreads();
   float top = part_s[0];
 #pragma unroll
-  for (int w = 1; w < 8; ++w) top = fmaxf(top, part_s[w]);
+  for (int w = 1; w < kAttentionWarps; ++w) top = fmaxf(top, part_s[w]);
   __syncthreads();
   float local_sum = 0.f;
-  for (int p = threadIdx.x; p < length; p += 256) {
+  for (int p = threadIdx.x; p < length; p += kAttentionThreads) {
     const float weight = __expf(score_s[p] - top);
     score_s[p] = weight;
     local_sum += weight;
@@ -154,33 +234,38 @@ __global__ void __launch_bounds__(256) attention_decode_kernel(const __half* __r
   __syncthreads();
   float total = 0.f;
 #pragma unroll
-  for (int w = 0; w < 8; ++w) total += part_s[w];
+  for (int w = 0; w < kAttentionWarps; ++w) total += part_s[w];
 
-  const int slice = threadIdx.x >> 6, pair = threadIdx.x & 63;
-  float2 acc = make_float2(0.f, 0.f);
-  int p = slice;
-  for (; p + 12 < length; p += 16) {
-    __half2 v[4];
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const __half* column = values + 4 * lane;
+  int p = warp;
+  for (; p + 7 * kAttentionWarps < length; p += 8 * kAttentionWarps) {
+    uint2 v[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) v[u] = *reinterpret_cast<const __half2*>(values + int64_t(p + 4 * u) * D + 2 * pair);
+    for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const uint2*>(column + int64_t(p + u * kAttentionWarps) * D);
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const float2 f = __half22float2(v[u]);
-      const float weight = score_s[p + 4 * u];
-      acc.x = fmaf(weight, f.x, acc.x);
-      acc.y = fmaf(weight, f.y, acc.y);
+    for (int u = 0; u < 8; ++u) {
+      const float weight = score_s[p + u * kAttentionWarps];
+      const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&v[u].x));
+      const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&v[u].y));
+      acc[0] = fmaf(weight, lo.x, acc[0]); acc[1] = fmaf(weight, lo.y, acc[1]);
+      acc[2] = fmaf(weight, hi.x, acc[2]); acc[3] = fmaf(weight, hi.y, acc[3]);
     }
   }
-  for (; p < length; p += 4) {
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(values + int64_t(p) * D + 2 * pair));
-    acc.x = fmaf(score_s[p], f.x, acc.x);
-    acc.y = fmaf(score_s[p], f.y, acc.y);
+  for (; p < length; p += kAttentionWarps) {
+    const uint2 v = *reinterpret_cast<const uint2*>(column + int64_t(p) * D);
+    const float weight = score_s[p];
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+    const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+    acc[0] = fmaf(weight, lo.x, acc[0]); acc[1] = fmaf(weight, lo.y, acc[1]);
+    acc[2] = fmaf(weight, hi.x, acc[2]); acc[3] = fmaf(weight, hi.y, acc[3]);
   }
-  acc_s[slice][2 * pair] = acc.x;
-  acc_s[slice][2 * pair + 1] = acc.y;
+  *reinterpret_cast<float4*>(&acc_s[warp][4 * lane]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
   __syncthreads();
   if (threadIdx.x < D) {
-    const float value = acc_s[0][threadIdx.x] + acc_s[1][threadIdx.x] + acc_s[2][threadIdx.x] + acc_s[3][threadIdx.x];
+    float value = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAttentionWarps; ++w) value += acc_s[w][threadIdx.x];
     out[(int64_t(m) * q_heads + head) * D + threadIdx.x] = __float2half_rn(value / total);
   }
 }
@@ -229,15 +314,24 @@ extern "C" int mkb_add_rmsnorm(void* residual, const void* delta, const void* we
   MKB_REQUIRE(H * 4 <= 160 * 1024, MKB_E_UNSUPPORTED, "add_rmsnorm: hidden size %d too large", H);
   if (M == 0) return MKB_OK;
   MKB_REQUIRE(residual && weight && normed, MKB_E_ARGUMENT, "add_rmsnorm: null pointer");
-  const size_t smem = size_t(H) * 4;
-  static bool opted = false;
-  if (smem > 48 * 1024 && !opted) {
-    cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    opted = true;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(delta) |
+                         reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(normed)) & 15) == 0;
+  cudaError_t launched;
+  if (aligned && H % 8 == 0 && H <= kNormThreads * kNormPieces * 8) {
+    launched = launch_dependent(add_rmsnorm_kernel, dim3(M), dim3(kNormThreads), 0, stream,
+                                static_cast<__half*>(residual), static_cast<const __half*>(delta),
+                                static_cast<const __half*>(weight), static_cast<__half*>(normed), H, eps);
+  } else {
+    const size_t smem = size_t(H) * 4;
+    static bool opted = false;
+    if (smem > 48 * 1024 && !opted) {
+      cudaFuncSetAttribute(add_rmsnorm_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      opted = true;
+    }
+    launched = launch_dependent(add_rmsnorm_generic_kernel, dim3(M), dim3(256), smem, stream,
+                                static_cast<__half*>(residual), static_cast<const __half*>(delta),
+                                static_cast<const __half*>(weight), static_cast<__half*>(normed), H, eps);
   }
-  const cudaError_t launched = launch_dependent(
-      add_rmsnorm_kernel, dim3(M), dim3(256), smem, stream, static_cast<__half*>(residual),
-      static_cast<const __half*>(delta), static_cast<const __half*>(weight), static_cast<__half*>(normed), H, eps);
   if (launched != cudaSuccess) return cuda_fail(launched, "add_rmsnorm launch");
   return MKB_OK;
 }
@@ -273,7 +367,7 @@ extern "C" int mkb_attention_decode(const void* qkv, const int* positions, const
     opted = true;
   }
   const cudaError_t launched = launch_dependent(
-      attention_decode_kernel, dim3(M, q_heads), dim3(256), smem, stream, static_cast<const __half*>(qkv), positions,
+      attention_decode_kernel, dim3(M, q_heads), dim3(kAttentionThreads), smem, stream, static_cast<const __half*>(qkv), positions,
       static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), static_cast<__half*>(out), q_heads,
       kv_heads, capacity, scale);
   if (launched != cudaSuccess) return cuda_fail(launched, "attention_decode launch");
