@@ -30,6 +30,16 @@ SIGNATURES = {
     "mkb_rope_append": (c_int, [c_void_p] * 4 + [c_int] * 5 + [c_float, c_void_p]),
     "mkb_attention_decode": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_float, c_void_p]),
     "mkb_silu_mul": (c_int, [c_void_p] * 2 + [c_int, c_int, c_void_p]),
+    "mkb_peer_buffer_bytes": (c_int64, [c_int] * 3),
+    "mkb_peer_alloc": (c_int, [c_int64, c_void_p]),
+    "mkb_peer_free": (c_int, [c_void_p]),
+    "mkb_peer_export": (c_int, [c_void_p, c_void_p]),
+    "mkb_peer_open": (c_int, [c_void_p, c_void_p]),
+    "mkb_peer_close": (c_int, [c_void_p]),
+    "mkb_peer_push": (c_int, [c_void_p] * 3 + [c_int] * 5 + [c_void_p]),
+    "mkb_peer_add_rmsnorm": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_float, c_void_p]),
+    "mkb_peer_status": (c_int, [c_void_p, c_void_p]),
+    "mkb_peer_set_poll_limit": (c_int, [c_void_p, c_int64]),
 }
 
 _library = None

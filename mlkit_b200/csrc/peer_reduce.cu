@@ -1,0 +1,279 @@
+// One-shot all-reduce over peer memory for the row-parallel linears of the tensor-parallel decode
+// step (sm_100a, NVLink/NVSwitch), fused with the residual add and RMS norm that consume it.
+//
+// Every rank owns one exchange buffer that all ranks of the node have mapped:
+//   [ flags: 2 parities x world x uint32 | sent: world x uint32 | status | pad to 1024 B ]
+//   [ slots: 2 parities x world x rows x H fp16 ]
+// A reduction is two kernels on each rank, no library collective:
+//   * push: CTA p copies this rank's partial [M, H] into slot[parity][rank] of peer p's buffer with
+//     plain 16-byte stores over NVLink, fences, and then writes flag[parity][rank] = v on that
+//     peer.  v counts this rank's pushes (kept per CTA in the rank's own buffer); all ranks run the
+//     same sequence of reductions, so v is the same number everywhere, and parity = v & 1 keeps a
+//     fast rank's next reduction out of the slots a slow rank is still reading;
+//   * add + norm: waits (bounded) until all `world` flags of the parity carry v, adds the slots in
+//     rank order in fp32 (every rank gets the same bits), rounds the sum to fp16 as the
+//     library all-reduce would, and goes on exactly like add_rmsnorm.
+// Waits give up after a bounded number of polls, set the status word and let the kernel finish.
+#include "mkb_common.cuh"
+
+namespace mkb {
+namespace {
+
+constexpr int kHeaderBytes = 1024;
+constexpr int kMaxWorld = 16;
+constexpr int kPushThreads = 1024;
+constexpr int kGatherThreads = 1024;
+constexpr uint32_t kDefaultPolls = 60000000;  // of the order of half a minute: ranks are separate processes
+
+struct Header {
+  uint32_t flags[2][kMaxWorld];   // written by the peers
+  uint32_t sent[kMaxWorld];       // pushes this rank has made toward peer p (touched by CTA p only)
+  uint32_t status;                // non-zero when a wait expired
+  uint32_t poll_limit;            // polls of one flag before a wait gives up
+};
+static_assert(sizeof(Header) <= kHeaderBytes, "header does not fit");
+
+__device__ __forceinline__ __half* slot_of(void* buffer, int parity, int source, int world, int64_t slot_halves) {
+  return reinterpret_cast<__half*>(static_cast<uint8_t*>(buffer) + kHeaderBytes) +
+         (int64_t(parity) * world + source) * slot_halves;
+}
+
+// grid = world CTAs: CTA p serves peer p
+__global__ void __launch_bounds__(kPushThreads) peer_push_kernel(const __half* __restrict__ partial, void* const* peers,
+                                                                 void* own, int M, int H, int world, int rank,
+                                                                 int64_t slot_halves) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int p = blockIdx.x;
+  Header* mine = static_cast<Header*>(own);
+  const uint32_t v = mine->sent[p] + 1;   // only this CTA touches sent[p]
+  void* peer = peers[p];
+  __half* destination = slot_of(peer, int(v & 1u), rank, world, slot_halves);
+  const int64_t vectors = int64_t(M) * H / 8;
+  const uint4* source = reinterpret_cast<const uint4*>(partial);
+  uint4* target = reinterpret_cast<uint4*>(destination);
+  for (int64_t i = threadIdx.x; i < vectors; i += kPushThreads) target[i] = source[i];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    mine->sent[p] = v;
+    volatile uint32_t* flag = &static_cast<Header*>(peer)->flags[v & 1u][rank];
+    *flag = v;
+  }
+}
+
+// One CTA per row m: residual[m,:] += sum over ranks of slot[r][m,:]; normed = rmsnorm(residual) * weight.
+// `reduced` (optional) receives the fp16 sum, for callers that need the all-reduced tensor itself.
+constexpr int kGatherPieces = 2;   // rows up to 1024 * 2 * 8 = 16384 elements stay in registers
+
+__global__ void __launch_bounds__(kGatherThreads) peer_add_rmsnorm_kernel(__half* __restrict__ residual, void* own,
+                                                                          const __half* __restrict__ weight,
+                                                                          __half* __restrict__ normed,
+                                                                          __half* __restrict__ reduced, int H, int world,
+                                                                          int64_t slot_halves, float eps) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  __shared__ float part_s[kGatherThreads / 32];
+  __shared__ int ready_s;
+  Header* mine = static_cast<Header*>(own);
+  const uint32_t v = mine->sent[0];   // the push that precedes this kernel in the stream has set it
+  const int parity = int(v & 1u);
+  if (threadIdx.x == 0) ready_s = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    const volatile uint32_t* flag = &mine->flags[parity][threadIdx.x];
+    const uint32_t limit = mine->poll_limit;
+    uint32_t polls = 0;
+    while (*flag != v && polls < limit) ++polls;
+    if (*flag != v) {
+      ready_s = 0;
+      atomicExch(&mine->status, 1u);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  const bool ready = ready_s != 0;   // on expiry the kernel still runs through, with whatever arrived
+
+  const int64_t base = int64_t(blockIdx.x) * H;
+  uint4 kept[kGatherPieces];
+  float sq = 0.f;
+#pragma unroll
+  for (int piece = 0; piece < kGatherPieces; ++piece) {
+    const int i = (piece * kGatherThreads + threadIdx.x) * 8;
+    kept[piece] = make_uint4(0u, 0u, 0u, 0u);
+    if (i < H) {
+      float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < world; ++r) {
+        const __half* slot = slot_of(own, parity, r, world, slot_halves);
+        // cache-volatile: the slot was written from outside this GPU
+        const uint4 part = ready ? __ldcv(reinterpret_cast<const uint4*>(slot + base + i)) : make_uint4(0u, 0u, 0u, 0u);
+        const __half2* ph = reinterpret_cast<const __half2*>(&part);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = __half22float2(ph[q]);
+          sum[2 * q] += f.x;
+          sum[2 * q + 1] += f.y;
+        }
+      }
+      uint4 delta;
+      __half2* dh = reinterpret_cast<__half2*>(&delta);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) dh[q] = __floats2half2_rn(sum[2 * q], sum[2 * q + 1]);
+      if (reduced != nullptr) *reinterpret_cast<uint4*>(reduced + base + i) = delta;
+      uint4 value = *reinterpret_cast<const uint4*>(residual + base + i);
+      __half2* vh = reinterpret_cast<__half2*>(&value);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 a = __half22float2(vh[q]), b = __half22float2(dh[q]);
+        vh[q] = __floats2half2_rn(a.x + b.x, a.y + b.y);
+      }
+      *reinterpret_cast<uint4*>(residual + base + i) = value;
+      kept[piece] = value;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 a = __half22float2(vh[q]);
+        sq += a.x * a.x + a.y * a.y;
+      }
+    }
+  }
+#pragma unroll
+  for (int offset = 16; offset; offset >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, offset);
+  if ((threadIdx.x & 31) == 0) part_s[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int w = 0; w < kGatherThreads / 32; ++w) total += part_s[w];
+  const float inv = rsqrtf(total / float(H) + eps);
+#pragma unroll
+  for (int piece = 0; piece < kGatherPieces; ++piece) {
+    const int i = (piece * kGatherThreads + threadIdx.x) * 8;
+    if (i < H) {
+      const uint4 w = *reinterpret_cast<const uint4*>(weight + i);
+      const __half2* vh = reinterpret_cast<const __half2*>(&kept[piece]);
+      const __half2* wh = reinterpret_cast<const __half2*>(&w);
+      uint4 result;
+      __half2* rh = reinterpret_cast<__half2*>(&result);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 a = __half22float2(vh[q]), ww = __half22float2(wh[q]);
+        const float2 u = __half22float2(__floats2half2_rn(a.x * inv, a.y * inv));
+        rh[q] = __floats2half2_rn(u.x * ww.x, u.y * ww.y);
+      }
+      *reinterpret_cast<uint4*>(normed + base + i) = result;
+    }
+  }
+}
+
+template <typename... Params, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, void* stream, Args... args) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = 0;
+  config.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, Params(args)...);
+}
+
+}  // namespace
+}  // namespace mkb
+
+extern "C" int64_t mkb_peer_buffer_bytes(int rows, int H, int world) {
+  if (rows < 1 || H < 8 || world < 1 || world > mkb::kMaxWorld) return 0;
+  return mkb::kHeaderBytes + int64_t(2) * world * rows * H * 2;
+}
+
+extern "C" int mkb_peer_set_poll_limit(void* own, int64_t polls) {
+  using namespace mkb;
+  MKB_REQUIRE(own != nullptr && polls >= 1 && polls <= int64_t(0xffffffffu), MKB_E_ARGUMENT, "peer_set_poll_limit: bad arguments");
+  const uint32_t value = uint32_t(polls);
+  const cudaError_t copied = cudaMemcpy(&static_cast<Header*>(own)->poll_limit, &value, sizeof(value), cudaMemcpyHostToDevice);
+  if (copied != cudaSuccess) return cuda_fail(copied, "peer_set_poll_limit");
+  return MKB_OK;
+}
+
+extern "C" int mkb_peer_alloc(int64_t bytes, void** buffer) {
+  using namespace mkb;
+  MKB_REQUIRE(bytes > 0 && buffer != nullptr, MKB_E_ARGUMENT, "peer_alloc: bad arguments");
+  cudaError_t status = cudaMalloc(buffer, size_t(bytes));
+  if (status != cudaSuccess) return cuda_fail(status, "peer_alloc");
+  status = cudaMemset(*buffer, 0, size_t(bytes));
+  if (status != cudaSuccess) return cuda_fail(status, "peer_alloc: clearing");
+  return mkb_peer_set_poll_limit(*buffer, int64_t(kDefaultPolls));
+}
+
+extern "C" int mkb_peer_free(void* buffer) {
+  using namespace mkb;
+  const cudaError_t status = cudaFree(buffer);
+  if (status != cudaSuccess) return cuda_fail(status, "peer_free");
+  return MKB_OK;
+}
+
+extern "C" int mkb_peer_export(void* buffer, void* handle64) {
+  using namespace mkb;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  MKB_REQUIRE(buffer != nullptr && handle64 != nullptr, MKB_E_ARGUMENT, "peer_export: null pointer");
+  const cudaError_t status = cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle64), buffer);
+  if (status != cudaSuccess) return cuda_fail(status, "peer_export");
+  return MKB_OK;
+}
+
+extern "C" int mkb_peer_open(const void* handle64, void** buffer) {
+  using namespace mkb;
+  MKB_REQUIRE(handle64 != nullptr && buffer != nullptr, MKB_E_ARGUMENT, "peer_open: null pointer");
+  cudaIpcMemHandle_t handle;
+  memcpy(&handle, handle64, sizeof(handle));
+  const cudaError_t status = cudaIpcOpenMemHandle(buffer, handle, cudaIpcMemLazyEnablePeerAccess);
+  if (status != cudaSuccess) return cuda_fail(status, "peer_open");
+  return MKB_OK;
+}
+
+extern "C" int mkb_peer_close(void* buffer) {
+  using namespace mkb;
+  const cudaError_t status = cudaIpcCloseMemHandle(buffer);
+  if (status != cudaSuccess) return cuda_fail(status, "peer_close");
+  return MKB_OK;
+}
+
+extern "C" int mkb_peer_push(const void* partial, void* const* peers, void* own, int M, int H, int rows, int world,
+                             int rank, void* stream) {
+  using namespace mkb;
+  MKB_REQUIRE(partial && peers && own, MKB_E_ARGUMENT, "peer_push: null pointer");
+  MKB_REQUIRE(M >= 1 && M <= rows && H >= 8 && H % 8 == 0 && world >= 1 && world <= kMaxWorld && rank >= 0 && rank < world,
+              MKB_E_ARGUMENT, "peer_push: bad shape");
+  MKB_REQUIRE(reinterpret_cast<uintptr_t>(partial) % 16 == 0, MKB_E_ARGUMENT, "peer_push: partial must be 16-byte aligned");
+  const cudaError_t launched = launch_dependent(peer_push_kernel, dim3(world), dim3(kPushThreads), stream,
+                                                static_cast<const __half*>(partial), peers, own, M, H, world, rank,
+                                                int64_t(rows) * H);
+  if (launched != cudaSuccess) return cuda_fail(launched, "peer_push launch");
+  return MKB_OK;
+}
+
+extern "C" int mkb_peer_add_rmsnorm(void* residual, void* own, const void* weight, void* normed, void* reduced, int M,
+                                    int H, int rows, int world, float eps, void* stream) {
+  using namespace mkb;
+  MKB_REQUIRE(residual && own && weight && normed, MKB_E_ARGUMENT, "peer_add_rmsnorm: null pointer");
+  MKB_REQUIRE(M >= 1 && M <= rows && H % 8 == 0 && H >= 8 && H <= kGatherThreads * kGatherPieces * 8 && world >= 1 &&
+                  world <= kMaxWorld,
+              MKB_E_UNSUPPORTED, "peer_add_rmsnorm: unsupported shape");
+  const cudaError_t launched = launch_dependent(
+      peer_add_rmsnorm_kernel, dim3(M), dim3(kGatherThreads), stream, static_cast<__half*>(residual), own,
+      static_cast<const __half*>(weight), static_cast<__half*>(normed), static_cast<__half*>(reduced), H, world,
+      int64_t(rows) * H, eps);
+  if (launched != cudaSuccess) return cuda_fail(launched, "peer_add_rmsnorm launch");
+  return MKB_OK;
+}
+
+extern "C" int mkb_peer_status(const void* own, int* status) {
+  using namespace mkb;
+  MKB_REQUIRE(own && status, MKB_E_ARGUMENT, "peer_status: null pointer");
+  uint32_t value = 0;
+  const cudaError_t copied = cudaMemcpy(&value, &static_cast<const Header*>(own)->status, sizeof(value), cudaMemcpyDeviceToHost);
+  if (copied != cudaSuccess) return cuda_fail(copied, "peer_status");
+  *status = int(value);
+  return MKB_OK;
+}

@@ -23,7 +23,7 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 
-from mlkit_b200 import kernels
+from mlkit_b200 import _native, kernels
 from mlkit_b200.quantization import Q, pack
 
 
@@ -162,6 +162,87 @@ def synthetic_block(config: DecoderConfig, world: int, device: torch.device,
             "down": make(config.hidden, config.intermediate // world)}
 
 
+# ----------------------------------------------------------------------------------- peer exchange
+
+
+class PeerExchange:
+    """The exchange buffers of the one-shot peer-memory all-reduce (``mkb_peer_*``).
+
+    Every rank allocates one buffer, the ranks swap its 64-byte handle through the process group, and
+    each maps the others' buffers; ``push`` then writes a partial into all of them and
+    ``add_rmsnorm`` consumes the sum.  Ranks must share a node (NVLink/NVSwitch peer access).
+    """
+
+    def __init__(self, *, rank: int, world: int, rows: int, width: int, device: torch.device,
+                 group: "dist.ProcessGroup | None" = None) -> None:
+        import ctypes
+
+        self.rank, self.world, self.rows, self.width, self.device = rank, world, rows, width, device
+        library = _native.library()
+        with torch.cuda.device(device):
+            size = library.mkb_peer_buffer_bytes(rows, width, world)
+            if size <= 0:
+                raise ValueError(f"peer exchange does not cover rows={rows} width={width} world={world}")
+            own = ctypes.c_void_p()
+            _native.check(library.mkb_peer_alloc(size, ctypes.byref(own)), "peer_alloc")
+            self.own = own.value
+            handle = ctypes.create_string_buffer(64)
+            _native.check(library.mkb_peer_export(self.own, handle), "peer_export")
+            handles: list = [None] * world
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            self.opened: list[int] = []
+            pointers = []
+            for peer, raw in enumerate(handles):
+                if peer == rank:
+                    pointers.append(self.own)
+                    continue
+                mapped = ctypes.c_void_p()
+                _native.check(library.mkb_peer_open(ctypes.create_string_buffer(raw, 64), ctypes.byref(mapped)),
+                              "peer_open")
+                self.opened.append(mapped.value)
+                pointers.append(mapped.value)
+            self.peers = torch.tensor(pointers, dtype=torch.int64, device=device)
+        dist.barrier(group=group)
+
+    def push(self, partial: Tensor) -> None:
+        status = _native.library().mkb_peer_push(partial.data_ptr(), self.peers.data_ptr(), self.own, partial.shape[0],
+                                                 self.width, self.rows, self.world, self.rank,
+                                                 torch.cuda.current_stream(self.device).cuda_stream)
+        _native.check(status, "peer_push")
+
+    def add_rmsnorm(self, residual: Tensor, weight: Tensor, normed: Tensor, eps: float,
+                    reduced: Tensor | None = None) -> None:
+        status = _native.library().mkb_peer_add_rmsnorm(
+            residual.data_ptr(), self.own, weight.data_ptr(), normed.data_ptr(),
+            None if reduced is None else reduced.data_ptr(), residual.shape[0], self.width, self.rows, self.world,
+            float(eps), torch.cuda.current_stream(self.device).cuda_stream)
+        _native.check(status, "peer_add_rmsnorm")
+
+    def status(self) -> int:
+        """Non-zero when a bounded wait of an earlier reduction expired."""
+        import ctypes
+
+        value = ctypes.c_int(0)
+        _native.check(_native.library().mkb_peer_status(self.own, ctypes.byref(value)), "peer_status")
+        return value.value
+
+    def set_poll_limit(self, polls: int) -> None:
+        """How long a reduction waits for the other ranks (polls of a flag) before it gives up."""
+        _native.check(_native.library().mkb_peer_set_poll_limit(self.own, int(polls)), "peer_set_poll_limit")
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free this rank's.  Call it after the process group has been
+        destroyed (tearing the library communicator down after these mappings were closed was seen to
+        block), or leave it to process exit."""
+        library = _native.library()
+        for mapped in self.opened:
+            library.mkb_peer_close(mapped)
+        self.opened = []
+        if self.own:
+            library.mkb_peer_free(self.own)
+            self.own = None
+
+
 # ----------------------------------------------------------------------------------- the model
 
 
@@ -182,6 +263,13 @@ class TensorParallelDecoder:
         self.k_cache: list[Tensor] = []
         self.v_cache: list[Tensor] = []
         self._work: dict[int, dict[str, Tensor]] = {}
+        self.exchange: PeerExchange | None = None
+
+    def enable_peer_exchange(self) -> None:
+        """Replace the library all-reduce after o and down by the one-shot peer-memory reduction."""
+        if self.world > 1 and self.exchange is None:
+            self.exchange = PeerExchange(rank=self.rank, world=self.world, rows=self.max_batch,
+                                         width=self.config.hidden, device=self.device, group=self.group)
 
     # -- construction --
     def add_block(self, shards: dict[str, PackedShard], attention_norm: Tensor, mlp_norm: Tensor) -> None:
@@ -261,24 +349,38 @@ class TensorParallelDecoder:
         residual, normed = work["residual"], work["normed"]
         torch.index_select(self.embedding, 0, tokens, out=residual)
         delta = None
+        exchange = self.exchange
         for index, block in enumerate(self.blocks):
             attention_norm, mlp_norm = self.norms[index]
             k_cache, v_cache = self.k_cache[index], self.v_cache[index]
-            kernels.add_rmsnorm(residual, delta, attention_norm, normed, c.eps)
+            if exchange is not None and delta is not None:
+                exchange.add_rmsnorm(residual, attention_norm, normed, c.eps)   # the pushed down-projection
+            else:
+                kernels.add_rmsnorm(residual, delta, attention_norm, normed, c.eps)
             block["qkv"](normed, work["qkv"])
             kernels.rope_append(work["qkv"], positions, k_cache, v_cache, q_heads=local_q, kv_heads=local_kv,
                                 head_dim=c.head_dim, theta=c.rope_theta)
             kernels.attention_decode(work["qkv"], positions, k_cache, v_cache, work["attention"], q_heads=local_q,
                                      kv_heads=local_kv, head_dim=c.head_dim)
             block["o"](work["attention"], work["o"])
-            self._all_reduce(work["o"])
-            kernels.add_rmsnorm(residual, work["o"], mlp_norm, normed, c.eps)
+            if exchange is not None:
+                exchange.push(work["o"])
+                exchange.add_rmsnorm(residual, mlp_norm, normed, c.eps)
+            else:
+                self._all_reduce(work["o"])
+                kernels.add_rmsnorm(residual, work["o"], mlp_norm, normed, c.eps)
             block["gate_up"](normed, work["gate_up"])
             kernels.silu_mul(work["gate_up"], work["act"])
             block["down"](work["act"], work["down"])
-            self._all_reduce(work["down"])
+            if exchange is not None:
+                exchange.push(work["down"])
+            else:
+                self._all_reduce(work["down"])
             delta = work["down"]
-        kernels.add_rmsnorm(residual, delta, self.final_norm, normed, c.eps)
+        if exchange is not None and delta is not None:
+            exchange.add_rmsnorm(residual, self.final_norm, normed, c.eps)
+        else:
+            kernels.add_rmsnorm(residual, delta, self.final_norm, normed, c.eps)
         torch.matmul(normed, self.head.t(), out=work["logits"])
         if w == 1:
             return work["logits"]

@@ -100,8 +100,19 @@ def measure(rank: int, world: int, device: torch.device, steps: int, warmup: int
                                                layers=layers, max_batch=max(BATCHES), capacity=CONTEXT + 64,
                                                group=group)
     model.fill_cache(CONTEXT)
-    results = {"batches": {}, "launches_per_step": len(model.blocks) * 9 + 3,
-               "collectives_per_step": 0 if world == 1 else 2 * len(model.blocks) + 1}
+    results = {"batches": {}, "launches_per_step": len(model.blocks) * (9 if world == 1 else 11) + 3,
+               "collectives_per_step": 0 if world == 1 else 2 * len(model.blocks) + 1, "collective": "none"}
+    if world > 1:
+        # the library all-reduce first, as the yardstick; then the peer-memory reduction, which is the product path
+        captured = model.capture(1)
+        results["nccl_ms_per_step_batch1"] = time_steps(captured, steps, warmup, world, host_io=False)
+        del captured
+        results["collective"] = "nccl all-reduce"
+        try:
+            model.enable_peer_exchange()
+            results["collective"] = "peer-memory push + fused add/norm (mkb_peer_*); logits by nccl all-gather"
+        except Exception as error:  # peer mapping refused on this node: stay on the library collective
+            results["collective"] = f"nccl all-reduce (peer exchange unavailable: {error})"
     for batch in BATCHES:
         captured = model.capture(batch)
         resident = time_steps(captured, steps, warmup, world, host_io=False)
@@ -113,6 +124,8 @@ def measure(rank: int, world: int, device: torch.device, steps: int, warmup: int
             "per_gpu_gbps": bytes_rank / resident / 1e6, "aggregate_gbps": world * bytes_rank / resident / 1e6,
         }
         del captured
+    if model.exchange is not None:
+        results["peer_status"] = model.exchange.status()
     kernel_us, kernel_bytes = dominant_kernel(model, 1)
     results["kernel"] = {"us": kernel_us, "bytes": kernel_bytes,
                          "shape": f"{model.config.hidden}->{model.blocks[0]['gate_up'].out_rows}"}
@@ -154,5 +167,8 @@ def run(args, rank: int, world: int, device: torch.device, peak_info: tuple[floa
             "per_gpu_roofline_frac": {"batch1": one["per_gpu_gbps"] / peak, "batch8": eight["per_gpu_gbps"] / peak},
             "per_gpu_gbps": {"batch1": one["per_gpu_gbps"], "batch8": eight["per_gpu_gbps"]},
             "collectives_per_step": results["collectives_per_step"],
+            "collective": results["collective"],
+            "nccl_ms_per_step_batch1": results.get("nccl_ms_per_step_batch1"),
+            "peer_status": results.get("peer_status"),
         },
     }))

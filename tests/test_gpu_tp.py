@@ -209,7 +209,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _nccl_worker(rank, world, port, results):
+def _nccl_worker(rank, world, port, results, peer_exchange=False):
     import torch.distributed as dist
 
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -230,28 +230,71 @@ def _nccl_worker(rank, world, port, results):
         model.set_head(embedding, final_norm, head)
         tokens = torch.tensor([3, 500, 77], device="cuda")
         positions = torch.zeros(3, dtype=torch.int32, device="cuda")
+        if peer_exchange:
+            # the same step with the library all-reduce first: the peer-memory reduction adds the same
+            # fp16 partials in fp32 and rounds once, so the two may differ by an fp16 rounding only
+            through_nccl = model.step(tokens, positions).float().cpu()
+            model.enable_peer_exchange()
         logits = model.step(tokens, positions).float().cpu()
+        if peer_exchange:
+            # failures are reported through the queue, never raised here: a rank that leaves early would
+            # leave the other one waiting
+            problems = []
+            again = model.step(tokens, positions).float().cpu()       # the other parity of the slots
+            if not torch.equal(logits, again):
+                problems.append("two steps on the same inputs differ")
+            if matvec.relative_l2(logits.numpy(), through_nccl.numpy()) >= 2e-3:
+                problems.append("peer-memory reduction differs from the library all-reduce")
+            captured = model.capture(3)                                # and inside a CUDA graph
+            captured.tokens.copy_(tokens)
+            captured.positions.copy_(positions)
+            dist.barrier()
+            replayed = captured.replay().float().cpu()
+            if matvec.relative_l2(replayed.numpy(), logits.numpy()) >= 2e-3:
+                problems.append("graph replay differs from the eager step")
+            if model.exchange.status() != 0:
+                problems.append("a bounded wait expired")
+            results.put(("problems", rank, problems))
         if rank == 0:
             k_ref = [torch.zeros(4, config.kv_heads, 64, config.head_dim, device="cuda") for _ in blocks]
             v_ref = [torch.zeros(4, config.kv_heads, 64, config.head_dim, device="cuda") for _ in blocks]
             expected = dense_reference_step(config, blocks, embedding, final_norm, head, tokens, positions, k_ref, v_ref)
-            results.put(matvec.relative_l2(logits.numpy(), expected.cpu().numpy()))
+            results.put(("error", rank, matvec.relative_l2(logits.numpy(), expected.cpu().numpy())))
     dist.barrier()
-    dist.destroy_process_group()
+    dist.destroy_process_group()   # the exchange buffers stay mapped until the process exits
 
 
-def test_two_gpu_decode_matches_dense_reference():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+def _run_two_ranks(peer_exchange):
     import torch.multiprocessing as mp
 
     context = mp.get_context("spawn")
     results = context.Queue()
     port = _free_port()
-    workers = [context.Process(target=_nccl_worker, args=(rank, 2, port, results)) for rank in range(2)]
+    workers = [context.Process(target=_nccl_worker, args=(rank, 2, port, results, peer_exchange)) for rank in range(2)]
     for worker in workers:
         worker.start()
     for worker in workers:
-        worker.join(timeout=300)
+        worker.join(timeout=150)
+    for worker in workers:
+        if worker.is_alive():
+            worker.terminate()
     assert all(worker.exitcode == 0 for worker in workers)
-    assert results.get(timeout=5) < 1e-2
+    reports = [results.get(timeout=5) for _ in range(3 if peer_exchange else 1)]
+    for kind, rank, value in reports:
+        if kind == "problems":
+            assert value == [], (rank, value)
+        else:
+            assert value < 1e-2
+
+
+def test_two_gpu_decode_with_peer_memory_reduction():
+    """The one-shot peer-memory all-reduce (mkb_peer_push + mkb_peer_add_rmsnorm) in place of NCCL."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _run_two_ranks(peer_exchange=True)
+
+
+def test_two_gpu_decode_matches_dense_reference():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _run_two_ranks(peer_exchange=False)
