@@ -209,13 +209,13 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _nccl_worker(rank, world, port, results, peer_exchange=False):
+def two_rank_step(rank, world, peer_exchange):
+    """Body of one rank of the 2-GPU tests (run by tests/two_rank_worker.py under torch.distributed.run).
+    Returns a report dict; nothing is raised here, so no rank leaves the other one waiting."""
     import torch.distributed as dist
 
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     config = SMALL
+    report = {"rank": rank, "problems": []}
     with torch.cuda.device(rank):
         blocks = [quantised_block(config, 10 + i) for i in range(config.layers)]   # same seeds on every rank
         generator = torch.Generator(device="cuda").manual_seed(3)
@@ -237,54 +237,46 @@ def _nccl_worker(rank, world, port, results, peer_exchange=False):
             model.enable_peer_exchange()
         logits = model.step(tokens, positions).float().cpu()
         if peer_exchange:
-            # failures are reported through the queue, never raised here: a rank that leaves early would
-            # leave the other one waiting
-            problems = []
             again = model.step(tokens, positions).float().cpu()       # the other parity of the slots
             if not torch.equal(logits, again):
-                problems.append("two steps on the same inputs differ")
+                report["problems"].append("two steps on the same inputs differ")
             if matvec.relative_l2(logits.numpy(), through_nccl.numpy()) >= 2e-3:
-                problems.append("peer-memory reduction differs from the library all-reduce")
+                report["problems"].append("peer-memory reduction differs from the library all-reduce")
             captured = model.capture(3)                                # and inside a CUDA graph
             captured.tokens.copy_(tokens)
             captured.positions.copy_(positions)
             dist.barrier()
             replayed = captured.replay().float().cpu()
             if matvec.relative_l2(replayed.numpy(), logits.numpy()) >= 2e-3:
-                problems.append("graph replay differs from the eager step")
+                report["problems"].append("graph replay differs from the eager step")
             if model.exchange.status() != 0:
-                problems.append("a bounded wait expired")
-            results.put(("problems", rank, problems))
+                report["problems"].append("a bounded wait expired")
         if rank == 0:
             k_ref = [torch.zeros(4, config.kv_heads, 64, config.head_dim, device="cuda") for _ in blocks]
             v_ref = [torch.zeros(4, config.kv_heads, 64, config.head_dim, device="cuda") for _ in blocks]
             expected = dense_reference_step(config, blocks, embedding, final_norm, head, tokens, positions, k_ref, v_ref)
-            results.put(("error", rank, matvec.relative_l2(logits.numpy(), expected.cpu().numpy())))
-    dist.barrier()
-    dist.destroy_process_group()   # the exchange buffers stay mapped until the process exits
+            report["error"] = float(matvec.relative_l2(logits.numpy(), expected.cpu().numpy()))
+    return report
 
 
 def _run_two_ranks(peer_exchange):
-    import torch.multiprocessing as mp
+    """Two ranks under torch.distributed.run, as bench.py is launched; every rank prints one JSON report."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
 
-    context = mp.get_context("spawn")
-    results = context.Queue()
-    port = _free_port()
-    workers = [context.Process(target=_nccl_worker, args=(rank, 2, port, results, peer_exchange)) for rank in range(2)]
-    for worker in workers:
-        worker.start()
-    for worker in workers:
-        worker.join(timeout=150)
-    for worker in workers:
-        if worker.is_alive():
-            worker.terminate()
-    assert all(worker.exitcode == 0 for worker in workers)
-    reports = [results.get(timeout=5) for _ in range(3 if peer_exchange else 1)]
-    for kind, rank, value in reports:
-        if kind == "problems":
-            assert value == [], (rank, value)
-        else:
-            assert value < 1e-2
+    worker = Path(__file__).with_name("two_rank_worker.py")
+    command = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+               "127.0.0.1", "--master-port", str(_free_port()), str(worker)] + (["--peer"] if peer_exchange else [])
+    environment = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    finished = subprocess.run(command, capture_output=True, text=True, timeout=240, env=environment)
+    reports = [json.loads(line[len("REPORT "):]) for line in finished.stdout.splitlines() if line.startswith("REPORT ")]
+    assert finished.returncode == 0 and len(reports) == 2, finished.stdout[-2000:] + finished.stderr[-2000:]
+    for report in reports:
+        assert report["problems"] == [], report
+        if report["rank"] == 0:
+            assert report["error"] < 1e-2
 
 
 def test_two_gpu_decode_with_peer_memory_reduction():
