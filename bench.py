@@ -239,12 +239,66 @@ def time_cpu_route(repetitions: int, warmup: int):
     return seconds, threads, bytes_per_pass
 
 
+def time_transform(device: torch.device, rows: int, width: int, copies: int, repetitions: int = 5) -> float:
+    """Microseconds per launch of the randomised Hadamard transform (signs, FWHT, Paley factor for
+    14336 = 28 x 512) on fp16 ``[rows, width]``, over ``copies`` distinct inputs replayed as one CUDA graph."""
+    import mlkit_b200 as mk
+
+    generator = torch.Generator(device=device).manual_seed(11)
+    inputs = [torch.randn(rows, width, device=device, generator=generator).half() for _ in range(copies)]
+    signs = (torch.randint(0, 2, (width,), device=device, generator=generator) * 2 - 1).to(torch.int8)
+
+    def launch_all():
+        for x in inputs:
+            mk.rht(x, signs=signs)
+    launch_all()
+    torch.cuda.synchronize()
+    graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        launch_all()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            launch_all()
+    torch.cuda.current_stream().wait_stream(side)
+    graph.replay()
+    torch.cuda.synchronize()
+    best = None
+    for _ in range(repetitions):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        elapsed = start.elapsed_time(stop) * 1e3 / copies
+        best = elapsed if best is None else min(best, elapsed)
+    return best
+
+
+def transform_table(device: torch.device, peak: float) -> dict:
+    """The activation transform at decode sizes (latency-bound) and on a large batch (its bandwidth ceiling)."""
+    table = {}
+    for rows, width, copies in ((1, 4096, 16), (8, 4096, 16), (8, 14336, 16), (16384, 4096, 4), (8192, 14336, 4)):
+        us = time_transform(device, rows, width, copies)
+        moved = 2 * rows * width * 2 + width
+        table[f"rht_{rows}x{width}"] = {"us": round(us, 2), "gbps": round(moved / us / 1e3, 1),
+                                        "frac": round(moved / us / 1e3 / peak, 4)}
+    return table
+
+
 def run_case(spec: str, device: torch.device, launches: int) -> None:
     """One layer shape, ``launches`` launches over distinct weight copies (each cold in L2), nothing
-    else on the device: the small case a profiler captures.  Prints the mean launch time."""
+    else on the device: the small case a profiler captures.  Prints the mean launch time.
+    ``rht:ROWS:WIDTH`` runs the activation transform instead."""
     from mlkit_b200 import kernels
 
     fields = spec.split(":")
+    if fields[0] == "rht":
+        rows, width = int(fields[1]), int(fields[2])
+        us = time_transform(device, rows, width, launches, repetitions=2)
+        print(json.dumps({"case": spec, "launches": launches, "us_per_launch": round(us, 2),
+                          "bytes_per_launch": 2 * rows * width * 2 + width}))
+        return
     out_rows, width = LLAMA8B[fields[0]]
     rows = int(fields[1]) if len(fields) > 1 else 1
     kernel = fields[2] if len(fields) > 2 else "auto"
@@ -396,6 +450,10 @@ def main() -> None:
         "cpu_baseline": {"value": cpu_bytes / cpu_seconds / 1e9, "unit": "GB/s", "cores": cpu_threads, "kind": "port",
                          "sample": "one decoder block (7 linears, 109 MB packed), M=1, median of 3 passes"},
     }
+    try:   # an auxiliary table: a failure here must not cost the matvec numbers above
+        line["transform"] = transform_table(device, peak)
+    except Exception as error:
+        line["transform"] = {"error": repr(error)[:200]}
     # the 70B-shaped decode step on this one GPU (the N > 1 runs shard the same model)
     del blocks, graph
     torch.cuda.empty_cache()
