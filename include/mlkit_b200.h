@@ -95,6 +95,9 @@ int mkb_gemv_ex(const void* x, const uint8_t* packed, const void* scales, const 
  * (src/mlkit/kernels/packed_linear.py:131-167).
  */
 int64_t mkb_gemv_workspace_bytes(int M, int N, int K, int bits);
+/* Reads the workspace's status word (synchronises with the device): 0, or non-zero when a bounded
+ * wait inside a kernel that used this workspace expired (the results of that call are not valid). */
+int mkb_gemv_workspace_status(const void* workspace, int64_t workspace_bytes, int* status);
 int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* scales, const float* lut,
                 const void* zeros, const void* bias, void* y,
                 int M, int N, int K, int group, int bits, int lut_len,

@@ -92,6 +92,19 @@ extern "C" int64_t mkb_gemv_workspace_bytes(int M, int N, int K, int bits) {
   return tmem > bulk ? tmem : bulk;
 }
 
+extern "C" int mkb_gemv_workspace_status(const void* workspace, int64_t workspace_bytes, int* status) {
+  using namespace mkb;
+  MKB_REQUIRE(workspace != nullptr && status != nullptr && workspace_bytes >= 65536, MKB_E_ARGUMENT,
+              "gemv_workspace_status: no workspace head");
+  // the status word follows the arrival counters in the 64 KB head of the workspace
+  const uint8_t* word = static_cast<const uint8_t*>(workspace) + (65536 / 4 - 1) * 4;
+  int value = 0;
+  const cudaError_t copied = cudaMemcpy(&value, word, sizeof(value), cudaMemcpyDeviceToHost);
+  if (copied != cudaSuccess) return cuda_fail(copied, "gemv_workspace_status");
+  *status = value;
+  return MKB_OK;
+}
+
 extern "C" int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* scales, const float* lut,
                            const void* zeros, const void* bias, void* y, int M, int N, int K, int group,
                            int bits, int lut_len, int x_dtype, int scale_dtype,

@@ -34,6 +34,21 @@ def matvec_workspace(device: torch.device, rows: int, outputs: int, width: int, 
     return held
 
 
+def workspace_status() -> int:
+    """Non-zero when a bounded wait expired inside any matvec that used one of the pooled workspaces
+    (its results are not valid); synchronises with the devices."""
+    import ctypes
+
+    worst = 0
+    for held in _workspaces.values():
+        value = ctypes.c_int(0)
+        with torch.cuda.device(held.device):
+            check = _native.library().mkb_gemv_workspace_status(held.data_ptr(), held.numel(), ctypes.byref(value))
+        _native.check(check, "workspace_status")
+        worst = max(worst, value.value)
+    return worst
+
+
 def _tag(dtype: torch.dtype, what: str) -> int:
     try:
         return DTYPE_TAGS[dtype]

@@ -344,3 +344,14 @@ def test_rotated_matvec_path(width, rows):
     # the rotation is function preserving: (W R^T)(R x) ~ W x up to quantisation error of W
     plain = x.astype(np.float32) @ weight.T
     assert matvec.relative_l2(y, plain) < 0.2
+
+
+def test_zz_no_bounded_wait_expired_in_this_session():
+    """The split-K kernels report an expired wait through the workspace's status word: after all the
+    matvec tests of this module it must still be clear."""
+    from mlkit_b200 import kernels
+
+    layer = helpers.make_layer(512, 8192, 4, 128, seed=2)   # K split over slabs: uses the workspace
+    x = helpers.activations(8, 8192, seed=1)
+    assert matvec.relative_l2(run_matvec(layer, x, "bulk"), oracle_matvec(layer, x)) < TOLERANCE
+    assert kernels.workspace_status() == 0
