@@ -270,6 +270,168 @@ __global__ void __launch_bounds__(kAttentionThreads) attention_decode_kernel(
   }
 }
 
+// ---- attention with grouped query heads on the tensor cores ----------------------------------------
+constexpr int kGroupWarps = 12;
+constexpr int kGroupThreads = kGroupWarps * 32;
+constexpr int kPitch = 272;                 // bytes per staged row: 256 of data + 16 of padding (ldmatrix conflict-free)
+constexpr int kTileBytes = 16 * kPitch;     // one 16-position tile of K or of V
+
+__device__ __forceinline__ uint32_t shared_address(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t address) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t address) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// One CTA per (sequence m, key-value head): the G query heads that share the head are the rows of the
+// tensor-core tiles, so every cached key and value is read once.  A warp owns 16-position tiles
+// (warp, warp + 16, ...): S = Q K^T (16 steps), running softmax per row, O += P V (16 steps); the
+// warps' (max, sum, O) meet in shared memory in warp order.
+__global__ void __launch_bounds__(kGroupThreads) attention_group_kernel(const __half* __restrict__ qkv, const int* __restrict__ positions,
+                                                                 const __half* __restrict__ k_cache,
+                                                                 const __half* __restrict__ v_cache, __half* __restrict__ out,
+                                                                 int q_heads, int kv_heads, int capacity, float scale) {
+  // programmatic dependent launch: let the next kernel in the stream become resident now, then wait
+  // for everything this kernel reads
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  constexpr int D = 128;
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int m = blockIdx.x, kv = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int G = q_heads / kv_heads;               // <= 8: rows g of the tiles; rows g + 8 are padding
+  const int length = positions[m] + 1;
+  const int row = (q_heads + 2 * kv_heads) * D;
+  const __half* keys = k_cache + (int64_t(m) * kv_heads + kv) * capacity * D;
+  const __half* values = v_cache + (int64_t(m) * kv_heads + kv) * capacity * D;
+  uint8_t* k_tile = smem + warp * 2 * kTileBytes;
+  uint8_t* v_tile = k_tile + kTileBytes;
+
+  // Q fragments of this group: a[ks] = rows (g, g+8) x dims 16ks + (2t, 2t+1, 2t+8, 2t+9)
+  uint32_t qa[8][4];
+  {
+    const __half* q = qkv + int64_t(m) * row + int64_t(kv * G + g) * D;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      qa[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(q + 16 * ks + 2 * t) : 0u;
+      qa[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(q + 16 * ks + 8 + 2 * t) : 0u;
+      qa[ks][1] = 0u;
+      qa[ks][3] = 0u;
+    }
+  }
+  float o[16][2];   // row g x dims 8jn + (2t, 2t+1)
+#pragma unroll
+  for (int jn = 0; jn < 16; ++jn) o[jn][0] = o[jn][1] = 0.f;
+  float row_max = -INFINITY, row_sum = 0.f;   // of row g, over this lane's columns (sum) / the quad (max)
+
+  const int tiles = (length + 15) / 16;
+  for (int tile = warp; tile < tiles; tile += kGroupWarps) {
+    const int p0 = tile * 16;
+    // stage K and V rows p0 .. p0+15: 16 rows x 256 B each = 2 x 256 vectors of 16 B, 8 per lane each
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int vector = i * 32 + lane, r = vector >> 4, c = vector & 15;
+      const int p = min(p0 + r, length - 1);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(shared_address(k_tile + r * kPitch + c * 16)),
+                   "l"(keys + int64_t(p) * D + c * 8) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(shared_address(v_tile + r * kPitch + c * 16)),
+                   "l"(values + int64_t(p) * D + c * 8) : "memory");
+    }
+    asm volatile("cp.async.wait_all;" ::: "memory");
+    __syncwarp();
+    // S[16 heads][16 positions]: two n-tiles of 8 positions
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      // matrices: (pos 0-7, k 16ks..+7), (pos 0-7, k +8..+15), (pos 8-15, k ..+7), (pos 8-15, k +8..)
+      uint32_t b[4];
+      const int mat = lane >> 3, r = (lane & 7) + (mat >> 1) * 8, c = 16 * ks + (mat & 1) * 8;
+      ldmatrix_x4(b, shared_address(k_tile + r * kPitch + c * 2));
+      mma16816(s[0], qa[ks], b[0], b[1]);
+      mma16816(s[1], qa[ks], b[2], b[3]);
+    }
+    // running softmax of row g (rows g + 8 are padding)
+    float tile_max = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int p = p0 + nt * 8 + 2 * t + e;
+        s[nt][e] = p < length ? s[nt][e] * scale : -INFINITY;
+        tile_max = fmaxf(tile_max, s[nt][e]);
+      }
+    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+    tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+    const float new_max = fmaxf(row_max, tile_max);
+    const float correction = __expf(row_max - new_max);   // 0 on the first tile (row_max = -inf)
+    row_max = new_max;
+    float p_[2][2];
+    float partial = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        p_[nt][e] = __expf(s[nt][e] - new_max);
+        partial += p_[nt][e];
+      }
+    row_sum = row_sum * correction + partial;
+#pragma unroll
+    for (int jn = 0; jn < 16; ++jn) { o[jn][0] *= correction; o[jn][1] *= correction; }
+    // P as the A operand of the second product: k = positions
+    uint32_t pa[4] = {pack_half2(p_[0][0], p_[0][1]), 0u, pack_half2(p_[1][0], p_[1][1]), 0u};
+#pragma unroll
+    for (int pair = 0; pair < 8; ++pair) {
+      // matrices (transposed on load): (pos 0-7, dims 16pair..+7), (pos 8-15, same dims), (pos 0-7, dims +8..), (pos 8-15, dims +8..)
+      uint32_t b[4];
+      const int mat = lane >> 3, r = (lane & 7) + (mat & 1) * 8, c = 16 * pair + (mat >> 1) * 8;
+      ldmatrix_x4_trans(b, shared_address(v_tile + r * kPitch + c * 2));
+      float d0[4] = {o[2 * pair][0], o[2 * pair][1], 0.f, 0.f}, d1[4] = {o[2 * pair + 1][0], o[2 * pair + 1][1], 0.f, 0.f};
+      mma16816(d0, pa, b[0], b[1]);
+      mma16816(d1, pa, b[2], b[3]);
+      o[2 * pair][0] = d0[0]; o[2 * pair][1] = d0[1];
+      o[2 * pair + 1][0] = d1[0]; o[2 * pair + 1][1] = d1[1];
+    }
+  }
+  row_sum += __shfl_xor_sync(0xffffffffu, row_sum, 1);
+  row_sum += __shfl_xor_sync(0xffffffffu, row_sum, 2);
+
+  // meet: [warp][8 heads] max and sum, [warp][8 heads][128] outputs (the staging area is free now)
+  __syncthreads();
+  float* max_s = reinterpret_cast<float*>(smem);            // [kGroupWarps][8]
+  float* sum_s = max_s + kGroupWarps * 8;                         // [kGroupWarps][8]
+  float* out_s = sum_s + kGroupWarps * 8;                         // [kGroupWarps][8][D]
+  if (t == 0) { max_s[warp * 8 + g] = row_max; sum_s[warp * 8 + g] = row_sum; }
+#pragma unroll
+  for (int jn = 0; jn < 16; ++jn)
+    *reinterpret_cast<float2*>(out_s + (warp * 8 + g) * D + 8 * jn + 2 * t) = make_float2(o[jn][0], o[jn][1]);
+  __syncthreads();
+  for (int index = threadIdx.x; index < G * D; index += kGroupThreads) {
+    const int head = index / D, dim = index - head * D;
+    float top = -INFINITY;
+    for (int w = 0; w < kGroupWarps; ++w) top = fmaxf(top, max_s[w * 8 + head]);
+    float total = 0.f, value = 0.f;
+    for (int w = 0; w < kGroupWarps; ++w) {
+      const float weight = __expf(max_s[w * 8 + head] - top);   // 0 for warps that saw no position
+      total += sum_s[w * 8 + head] * weight;
+      value += out_s[(w * 8 + head) * D + dim] * weight;
+    }
+    out[(int64_t(m) * q_heads + kv * G + head) * D + dim] = __float2half_rn(value / total);
+  }
+}
+
 // out[m, i] = silu(gate_up[m, i]) * gate_up[m, I + i]
 __global__ void silu_mul_kernel(const __half* __restrict__ gate_up, __half* __restrict__ out, int64_t rows, int I) {
   // programmatic dependent launch: let the next kernel in the stream become resident now (a matvec
@@ -360,6 +522,21 @@ extern "C" int mkb_attention_decode(const void* qkv, const int* positions, const
   if (M == 0) return MKB_OK;
   MKB_REQUIRE(qkv && positions && k_cache && v_cache && out, MKB_E_ARGUMENT, "attention_decode: null pointer");
   MKB_REQUIRE(capacity <= 40960, MKB_E_UNSUPPORTED, "attention_decode: capacity %d exceeds 40960 positions", capacity);
+  if (q_heads / kv_heads <= 8) {
+    // grouped heads: one CTA per (sequence, key-value head), every cached row read once
+    const size_t group_smem = size_t(kGroupWarps) * 2 * kTileBytes;   // the meeting area (64.5 KB) fits inside
+    static bool group_opted = false;
+    if (!group_opted) {
+      cudaFuncSetAttribute(attention_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(group_smem));
+      group_opted = true;
+    }
+    const cudaError_t launched = launch_dependent(
+        attention_group_kernel, dim3(M, kv_heads), dim3(kGroupThreads), group_smem, stream,
+        static_cast<const __half*>(qkv), positions, static_cast<const __half*>(k_cache),
+        static_cast<const __half*>(v_cache), static_cast<__half*>(out), q_heads, kv_heads, capacity, scale);
+    if (launched != cudaSuccess) return cuda_fail(launched, "attention_decode launch");
+    return MKB_OK;
+  }
   const size_t smem = size_t(capacity) * 4;
   static bool opted = false;
   if (smem > 40 * 1024 && !opted) {
