@@ -271,7 +271,9 @@ def _run_two_ranks(peer_exchange):
                "127.0.0.1", "--master-port", str(_free_port()), str(worker)] + (["--peer"] if peer_exchange else [])
     environment = dict(os.environ, NCCL_NVLS_ENABLE="0")
     finished = subprocess.run(command, capture_output=True, text=True, timeout=240, env=environment)
-    reports = [json.loads(line[len("REPORT "):]) for line in finished.stdout.splitlines() if line.startswith("REPORT ")]
+    import re
+
+    reports = [json.loads(found) for found in re.findall(r"REPORT (\{.*?\})(?=\s|REPORT|$)", finished.stdout)]
     assert finished.returncode == 0 and len(reports) == 2, finished.stdout[-2000:] + finished.stderr[-2000:]
     for report in reports:
         assert report["problems"] == [], report

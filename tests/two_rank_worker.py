@@ -21,7 +21,8 @@ def main() -> None:
 
     report = test_gpu_tp.two_rank_step(rank, world, "--peer" in sys.argv)
     dist.barrier()
-    print("REPORT " + json.dumps(report), flush=True)
+    sys.stdout.write("\nREPORT " + json.dumps(report) + "\n")   # one write, so the ranks' lines do not interleave
+    sys.stdout.flush()
     dist.destroy_process_group()   # the exchange buffers stay mapped until the process exits
 
 
