@@ -64,7 +64,7 @@ __device__ __forceinline__ void butterfly_pass(float* buf, int groups, int strid
 __global__ void hadamard_kernel(HadamardArgs a) {
   extern __shared__ __align__(16) float smem_f[];
   float* buf = smem_f;               // [W]
-  float* basis_s = smem_f + a.W;     // [factor * factor] when factor > 1
+  float* basis_s = smem_f + ((a.W + 3) & ~3);   // [factor][factor padded to 4] when factor > 1; 16-byte aligned
   const int64_t row = blockIdx.x;
   const int64_t offset = row * a.W;
 
@@ -197,7 +197,7 @@ extern "C" int mkb_hadamard(const void* x, const int8_t* signs, const float* bas
   if (M == 0) return MKB_OK;
   MKB_REQUIRE(x != nullptr && y != nullptr, MKB_E_ARGUMENT, "hadamard: null pointer");
   MKB_REQUIRE(M <= 0x7fffffffLL, MKB_E_UNSUPPORTED, "hadamard: too many rows");
-  const size_t smem = (size_t(W) + (factor > 1 ? size_t(factor) * ((factor + 3) & ~3) : 0)) * sizeof(float);
+  const size_t smem = (size_t((W + 3) & ~3) + (factor > 1 ? size_t(factor) * ((factor + 3) & ~3) : 0)) * sizeof(float);
   const DeviceInfo& info = device_info();
   MKB_REQUIRE(smem <= size_t(info.max_smem_optin), MKB_E_UNSUPPORTED,
               "hadamard: width %d needs %zu B shared memory", W, smem);
