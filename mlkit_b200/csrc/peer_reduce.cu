@@ -82,7 +82,9 @@ __global__ void __launch_bounds__(kGatherThreads) peer_add_rmsnorm_kernel(__half
   __syncthreads();
   if (threadIdx.x < world) {
     const volatile uint32_t* flag = &mine->flags[parity][threadIdx.x];
-    const uint32_t limit = mine->poll_limit;
+    // a wait that expired once is not repeated: every later reduction of a broken exchange would
+    // otherwise add its own timeout
+    const uint32_t limit = mine->status != 0 ? 0u : mine->poll_limit;
     uint32_t polls = 0;
     while (*flag != v && polls < limit) ++polls;
     if (*flag != v) {

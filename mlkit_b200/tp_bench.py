@@ -111,6 +111,15 @@ def measure(rank: int, world: int, device: torch.device, steps: int, warmup: int
         try:
             model.enable_peer_exchange()
             results["collective"] = "peer-memory push + fused add/norm (mkb_peer_*); logits by nccl all-gather"
+            probe_tokens = torch.zeros(1, dtype=torch.int64, device=device)
+            probe_positions = torch.full((1,), CONTEXT, dtype=torch.int32, device=device)
+            model.step(probe_tokens, probe_positions)
+            torch.cuda.synchronize()
+            expired = torch.tensor([model.exchange.status()], device=device)
+            dist.all_reduce(expired, op=dist.ReduceOp.MAX)
+            if int(expired) != 0:   # a wait ran out on some rank: every rank goes back to the library collective
+                model.exchange = None
+                results["collective"] = "nccl all-reduce (a wait of the peer exchange expired)"
         except Exception as error:  # peer mapping refused on this node: stay on the library collective
             results["collective"] = f"nccl all-reduce (peer exchange unavailable: {error})"
     for batch in BATCHES:
