@@ -38,6 +38,13 @@ enum {
   MKB_GEMV_SCALAR = 1, /* word-at-a-time fp32 kernel: every layout the reference's fused kernel accepts */
   MKB_GEMV_TILED = 2,  /* 16-row x 128-code register-tiled kernel (fp16 activations) */
   MKB_GEMV_TMEM = 3,   /* tcgen05 kernel: weights through tensor memory (INT4 integer grid, fp16, needs a workspace) */
+  MKB_GEMV_GATED = 0x100, /* flag, OR-ed into a choice (mkb_gemv_ex, mkb_gemv_ws): x is [M, 2K] = gate | up of a
+                             SwiGLU MLP and the kernel forms silu(gate) * up while it loads the activations
+                             (rounded to fp16 after the activation and after the product, as separate fp16
+                             operators would); tiled kernel only (AUTO then takes it).  Every CTA redoes the
+                             activation for its share of K, so for one or two rows a separate SwiGLU kernel
+                             is as fast; it pays when the launch count matters more.  The reference leaves this
+                             product to the model code between two PackedLinear calls */
   MKB_GEMV_BULK = 4    /* TMA-fed kernel: whole 16-row units by cp.async.bulk.tensor into a shared-memory ring
                           (INT4 integer grid, fp16, K % 256 == 0; needs the workspace when K is split) */
 };

@@ -12,6 +12,7 @@ from mlkit_b200 import build as _build
 
 F16, BF16, F32 = 0, 1, 2
 GEMV_AUTO, GEMV_SCALAR, GEMV_TILED, GEMV_TMEM, GEMV_BULK = 0, 1, 2, 3, 4
+GEMV_GATED = 0x100
 
 SIGNATURES = {
     "mkb_version": (c_int, []),

@@ -46,7 +46,7 @@ int gemv_tiled_supported(int M, int K, int group, int bits, int x_dtype, int sca
 int launch_gemv_tiled(const void* x, const uint8_t* packed, const void* scales, const float* lut,
                       const void* zeros, const void* bias, void* y, int M, int N, int K, int group,
                       int bits, int lut_len, int64_t packed_row_stride, int64_t scale_row_stride,
-                      int integer_grid, float grid_minimum, cudaStream_t stream);
+                      int integer_grid, float grid_minimum, int gated, cudaStream_t stream);
 
 int gemv_umma_supported(int M, int K, int group, int bits, int x_dtype, int scale_dtype, const void* x,
                         const uint8_t* packed, int64_t packed_row_stride, const void* zeros, int integer_grid);
@@ -120,6 +120,8 @@ extern "C" int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* sca
               MKB_E_ARGUMENT, "gemv: unknown dtype");
   MKB_REQUIRE(lut_len >= 1 && lut_len <= (1 << bits), MKB_E_ARGUMENT,
               "gemv: lut_len=%d does not fit %d-bit codes", lut_len, bits);
+  const int gated = (kernel & MKB_GEMV_GATED) != 0;
+  kernel &= ~MKB_GEMV_GATED;
   MKB_REQUIRE(kernel >= MKB_GEMV_AUTO && kernel <= MKB_GEMV_BULK, MKB_E_ARGUMENT, "gemv: unknown kernel choice");
   if (N == 0) return MKB_OK;
   MKB_REQUIRE(x && packed && scales && lut && y, MKB_E_ARGUMENT, "gemv: null pointer");
@@ -135,7 +137,8 @@ extern "C" int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* sca
   if (kernel == MKB_GEMV_TMEM)
     MKB_REQUIRE(tmem_ok, MKB_E_UNSUPPORTED,
                 "gemv: the tensor-memory kernel does not cover these arguments or the workspace is too small");
-  if (kernel == MKB_GEMV_TMEM || (kernel == MKB_GEMV_AUTO && tmem_ok && mkb::prefer_tmem()))
+  MKB_REQUIRE(!(gated && kernel == MKB_GEMV_TMEM), MKB_E_UNSUPPORTED, "gemv: the tensor-memory kernel takes no gated input");
+  if (kernel == MKB_GEMV_TMEM || (!gated && kernel == MKB_GEMV_AUTO && tmem_ok && mkb::prefer_tmem()))
     return launch_gemv_umma(x, packed, scales, bias, y, workspace, M, N, K, group, packed_row_stride,
                             scale_row_stride, grid_minimum, s);
   const bool workspace_aligned = workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) % 16) == 0;
@@ -147,14 +150,16 @@ extern "C" int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* sca
   if (kernel == MKB_GEMV_BULK)
     MKB_REQUIRE(bulk_ok, MKB_E_UNSUPPORTED,
                 "gemv: the TMA-fed kernel does not cover these arguments or the workspace is too small");
-  if (kernel == MKB_GEMV_BULK || (kernel == MKB_GEMV_AUTO && bulk_ok && mkb::prefer_bulk(M, N, K)))
+  MKB_REQUIRE(!(gated && kernel == MKB_GEMV_BULK), MKB_E_UNSUPPORTED, "gemv: the TMA-fed kernel takes no gated input");
+  if (kernel == MKB_GEMV_BULK || (!gated && kernel == MKB_GEMV_AUTO && bulk_ok && mkb::prefer_bulk(M, N, K)))
     return launch_gemv_bulk(x, packed, scales, bias, y, workspace, workspace_bytes, M, N, K, group,
                             packed_row_stride, scale_row_stride, grid_minimum, s);
   if (kernel == MKB_GEMV_TILED)
     MKB_REQUIRE(tiled_ok, MKB_E_UNSUPPORTED, "gemv: the tiled kernel does not cover these arguments");
   if (kernel == MKB_GEMV_TILED || (kernel == MKB_GEMV_AUTO && tiled_ok))
     return launch_gemv_tiled(x, packed, scales, lut, zeros, bias, y, M, N, K, group, bits, lut_len,
-                             packed_row_stride, scale_row_stride, integer_grid, grid_minimum, s);
+                             packed_row_stride, scale_row_stride, integer_grid, grid_minimum, gated, s);
+  MKB_REQUIRE(!gated, MKB_E_UNSUPPORTED, "gemv: the gated input needs the tiled kernel");
   return launch_gemv_scalar(x, packed, scales, lut, zeros, bias, y, M, N, K, group, bits, lut_len, x_dtype,
                             scale_dtype, packed_row_stride, scale_row_stride, s);
 }

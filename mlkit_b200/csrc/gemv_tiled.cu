@@ -61,6 +61,7 @@ struct TiledArgs {
   int64_t packed_row_stride, scale_row_stride;
   int row_tiles, first_tile, k_tiles, k_tiles_cta, splits, mpad, group_shift;  // row tiles [first_tile, first_tile + row_tiles)
   float grid_min;
+  int gated;  // x is [M, 2K] = gate | up: the staged activation is silu(gate) * up
 };
 
 // ---- asynchronous global -> shared copies (per thread; no register scoreboard involved) ----------
@@ -344,11 +345,16 @@ __global__ void __launch_bounds__(kThreadsT, MODE == MODE_TABLE ? 2 : 3) gemv_ti
     for (int c = threadIdx.x; c < rounded; c += kThreadsT) {
       const bool live = c < chunks;
       const int tt = c & 3, kl = live ? (c >> 2) % nk_cta : 0, m = live ? (c >> 2) / nk_cta : 0;
-      const uint4* src = reinterpret_cast<const uint4*>(a.x + int64_t(m) * a.K + int64_t(kt0 + kl) * 128 + tt * 32);
+      const int64_t x_row = a.gated ? 2 * int64_t(a.K) : int64_t(a.K);
+      const uint4* src = reinterpret_cast<const uint4*>(a.x + int64_t(m) * x_row + int64_t(kt0 + kl) * 128 + tt * 32);
       uint32_t xr[16];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const uint4 v = live ? __ldg(src + q) : make_uint4(0u, 0u, 0u, 0u);
+        uint4 v = live ? __ldg(src + q) : make_uint4(0u, 0u, 0u, 0u);
+        if (a.gated && live) {
+          const uint4 up = __ldg(src + a.K / 8 + q);
+          v = make_uint4(swiglu_pair(v.x, up.x), swiglu_pair(v.y, up.y), swiglu_pair(v.z, up.z), swiglu_pair(v.w, up.w));
+        }
         xr[4 * q] = v.x; xr[4 * q + 1] = v.y; xr[4 * q + 2] = v.z; xr[4 * q + 3] = v.w;
       }
       if constexpr (RAW) {
@@ -655,8 +661,9 @@ int gemv_tiled_supported(int M, int K, int group, int bits, int x_dtype, int sca
 int launch_gemv_tiled(const void* x, const uint8_t* packed, const void* scales, const float* lut,
                       const void* zeros, const void* bias, void* y, int M, int N, int K, int group,
                       int bits, int lut_len, int64_t packed_row_stride, int64_t scale_row_stride,
-                      int integer_grid, float grid_minimum, cudaStream_t stream) {
+                      int integer_grid, float grid_minimum, int gated, cudaStream_t stream) {
   TiledArgs a{};
+  a.gated = gated;
   a.x = static_cast<const __half*>(x); a.packed = packed; a.scales = static_cast<const __half*>(scales);
   a.lut = lut; a.zeros = static_cast<const __half*>(zeros); a.bias = static_cast<const __half*>(bias);
   a.y = static_cast<__half*>(y);

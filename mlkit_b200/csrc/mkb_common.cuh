@@ -56,6 +56,17 @@ __device__ __forceinline__ void store_from_float(void* base, int64_t index, int 
   else reinterpret_cast<float*>(base)[index] = value;
 }
 
+// SwiGLU on two packed fp16 pairs, with the rounding points of separate fp16 operators: the
+// activation silu(g) is rounded to fp16, then the product with u is rounded to fp16.
+__device__ __forceinline__ uint32_t swiglu_pair(uint32_t gate_bits, uint32_t up_bits) {
+  const float2 g = __half22float2(*reinterpret_cast<const __half2*>(&gate_bits));
+  const float2 u = __half22float2(*reinterpret_cast<const __half2*>(&up_bits));
+  const float a = g.x / (1.f + __expf(-g.x)), b = g.y / (1.f + __expf(-g.y));
+  const float2 act = __half22float2(__floats2half2_rn(a, b));
+  const __half2 out = __floats2half2_rn(act.x * u.x, act.y * u.y);
+  return *reinterpret_cast<const uint32_t*>(&out);
+}
+
 __host__ __device__ inline int dtype_bytes(int dtype) { return dtype == MKB_F32 ? 4 : 2; }
 
 // The reference reconstruction: one binary32 multiply, then (with offsets) one separate binary32

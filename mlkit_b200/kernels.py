@@ -92,13 +92,18 @@ def integer_grid_of(values: Tensor) -> tuple[bool, float]:
 def packed_matvec(x: Tensor, packed: Tensor, scales: Tensor, values: Tensor, zeros: Tensor | None,
                   bias: Tensor | None, out: Tensor, *, group: int, bits: int, integer_grid: bool = False,
                   grid_minimum: float = 0.0, kernel: str = "auto", packed_row_stride: int | None = None,
-                  scale_row_stride: int | None = None, workspace: Tensor | None = None) -> Tensor:
+                  scale_row_stride: int | None = None, workspace: Tensor | None = None,
+                  gated: bool = False) -> Tensor:
     """``out[m, n] = sum_k x[m, k] * (values[code[n, k]] * scales[n, k // group] (+ zeros)) (+ bias[n])``.
 
     ``x`` is ``[M, K]`` contiguous with ``M <= 8``; ``out`` is ``[M, N]`` in the dtype of ``x``.
     """
     device = _require_cuda(x, packed, scales, values, zeros, bias, out)
     rows, width = x.shape
+    if gated:   # x is [rows, 2 * width] = gate | up; the kernel forms silu(gate) * up on load
+        if width % 2:
+            raise ValueError("a gated input has an even number of columns")
+        width //= 2
     outputs = out.shape[-1]
     if not (x.is_contiguous() and out.is_contiguous()):
         raise ValueError("packed_matvec needs contiguous activations and output")
@@ -119,8 +124,8 @@ def packed_matvec(x: Tensor, packed: Tensor, scales: Tensor, values: Tensor, zer
             x.data_ptr(), packed.data_ptr(), scales.data_ptr(), values.data_ptr(), _pointer(zeros),
             _pointer(bias), out.data_ptr(), rows, outputs, width, group, bits, values.numel(),
             _tag(x.dtype, "activation"), _tag(scales.dtype, "scale"), packed_row_stride,
-            scale_row_stride, int(integer_grid), float(grid_minimum), KERNEL_CHOICES[kernel],
-            _pointer(workspace), 0 if workspace is None else workspace.numel(), _stream(device))
+            scale_row_stride, int(integer_grid), float(grid_minimum),
+            KERNEL_CHOICES[kernel] | (_native.GEMV_GATED if gated else 0), _pointer(workspace), 0 if workspace is None else workspace.numel(), _stream(device))
     _native.check(status, "packed_matvec")
     return out
 
@@ -139,7 +144,7 @@ class MatvecPlan:
 
     def __init__(self, packed: Tensor, scales: Tensor, values: Tensor, zeros: Tensor | None, bias: Tensor | None,
                  *, outputs: int, width: int, group: int, bits: int, dtype: torch.dtype, integer_grid: bool,
-                 grid_minimum: float) -> None:
+                 grid_minimum: float, gated: bool = False) -> None:
         device = _require_cuda(packed, scales, values, zeros, bias)
         if zeros is not None and zeros.dtype != scales.dtype:
             raise ValueError("offsets must share the dtype of the scales")
@@ -150,7 +155,7 @@ class MatvecPlan:
         self.tail = (outputs, width, group, bits, values.numel(), _tag(dtype, "activation"),
                      _tag(scales.dtype, "scale"), width * bits // 8,
                      scales.stride(0) if scales.dim() == 2 else -(-width // group), int(integer_grid),
-                     float(grid_minimum), _native.GEMV_AUTO)
+                     float(grid_minimum), _native.GEMV_AUTO | (_native.GEMV_GATED if gated else 0))
         self.outputs, self.width, self.bits, self.dtype, self.device = outputs, width, bits, dtype, device
         self.integer_grid = bool(integer_grid) and dtype == torch.float16 and zeros is None
         self.workspaces: dict[tuple[int, int], tuple[int | None, int, Tensor | None]] = {}

@@ -346,6 +346,30 @@ def test_rotated_matvec_path(width, rows):
     assert matvec.relative_l2(y, plain) < 0.2
 
 
+@pytest.mark.parametrize("kernel", ["tiled", "auto"])
+@pytest.mark.parametrize("rows_in", [1, 5, 8])
+def test_matvec_gated_input_equals_swiglu_then_matvec(kernel, rows_in):
+    """MKB_GEMV_GATED: x = gate | up, the kernel forms silu(gate) * up on load with the rounding points
+    of the separate operator, so the result equals silu_mul followed by the plain matvec bit for bit."""
+    from mlkit_b200 import kernels
+
+    width, outputs = 4096, 304
+    layer = helpers.make_layer(outputs, width, 4, 128, seed=9)
+    gate_up = dev((np.random.default_rng(rows_in).standard_normal((rows_in, 2 * width)) * 1.5).astype(np.float16))
+    act = torch.empty((rows_in, width), dtype=torch.float16, device="cuda")
+    kernels.silu_mul(gate_up, act)
+    packed, scales, values = dev(layer["packed"]), dev(layer["scales16"]), dev(layer["values"])
+    plain = torch.empty((rows_in, outputs), dtype=torch.float16, device="cuda")
+    fused = torch.empty_like(plain)
+    options = dict(group=128, bits=4, integer_grid=True, grid_minimum=-8.0, kernel=kernel)
+    kernels.packed_matvec(act, packed, scales, values, None, None, plain, **dict(options, kernel="tiled"))
+    kernels.packed_matvec(gate_up, packed, scales, values, None, None, fused, gated=True, **options)
+    assert torch.equal(plain, fused)
+    with pytest.raises(ValueError, match="gated"):
+        kernels.packed_matvec(gate_up, packed, scales, values, None, None, fused, gated=True, group=128, bits=4,
+                              integer_grid=True, grid_minimum=-8.0, kernel="scalar")
+
+
 def test_zz_no_bounded_wait_expired_in_this_session():
     """The split-K kernels report an expired wait through the workspace's status word: after all the
     matvec tests of this module it must still be clear."""
