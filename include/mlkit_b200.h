@@ -212,15 +212,15 @@ int mkb_silu_mul(const void* gate_up, void* out, int M, int I, void* stream);
  * sharding of src/mlkit/inference/packed_linear.py:145-179 would call after each row-parallel layer.
  *
  * Every rank allocates one exchange buffer (mkb_peer_alloc, mkb_peer_buffer_bytes(rows, H, world)
- * bytes: a 1 KB header of arrival flags and counters, then 2 x world slots of rows x H fp16),
- * exports it (64-byte handle), and opens the buffers of all other ranks of the node.  A reduction of
- * a partial [M, H] is mkb_peer_push (copies the partial into this rank's slot on every peer with
- * plain stores over NVLink, then raises this rank's flag there) followed by mkb_peer_add_rmsnorm
- * (waits, bounded, for all flags; adds the slots in rank order in fp32, rounds to fp16;
- * residual += sum; normed = rmsnorm(residual) * weight; `reduced`, when not null, receives the sum).
- * All ranks must issue the same sequence of reductions.  `peers` is a DEVICE array of `world` buffer
- * pointers (entry `rank` is the rank's own buffer).  A wait that expires sets a status word
- * (mkb_peer_status) and lets the kernel finish; nothing hangs.
+ * bytes, rows <= 8: a 2 KB header of arrival flags and counters, then 2 x world slots of rows x H
+ * fp16), exports it (64-byte handle), and opens the buffers of all other ranks of the node.  A
+ * reduction of a partial [M, H] is ONE kernel, mkb_peer_reduce_add_rmsnorm: CTA m copies row m of the
+ * partial into this rank's slot on every rank with plain stores over NVLink and raises its flag
+ * there, waits (bounded) for the flags of all ranks, adds the slots in rank order in fp32, rounds to
+ * fp16, and then residual += sum, normed = rmsnorm(residual) * weight; `reduced`, when not null,
+ * receives the sum.  All ranks must issue the same sequence of reductions.  `peers` is a DEVICE
+ * array of `world` buffer pointers (entry `rank` is the rank's own buffer).  A wait that expires sets
+ * a status word (mkb_peer_status), later waits are skipped, the kernels finish; nothing hangs.
  */
 int64_t mkb_peer_buffer_bytes(int rows, int H, int world);
 int mkb_peer_alloc(int64_t bytes, void** buffer);
@@ -228,10 +228,9 @@ int mkb_peer_free(void* buffer);
 int mkb_peer_export(void* buffer, void* handle64);
 int mkb_peer_open(const void* handle64, void** buffer);
 int mkb_peer_close(void* buffer);
-int mkb_peer_push(const void* partial, void* const* peers, void* own, int M, int H, int rows, int world,
-                  int rank, void* stream);
-int mkb_peer_add_rmsnorm(void* residual, void* own, const void* weight, void* normed, void* reduced,
-                         int M, int H, int rows, int world, float eps, void* stream);
+int mkb_peer_reduce_add_rmsnorm(const void* partial, void* const* peers, void* own, void* residual,
+                                const void* weight, void* normed, void* reduced, int M, int H, int rows,
+                                int world, int rank, float eps, void* stream);
 int mkb_peer_status(const void* own, int* status);
 /* Polls of one flag before a wait gives up (default 60 million, of the order of half a minute;
  * ranks are separate processes and may be seconds apart).  Synchronous; call it outside captures. */

@@ -38,8 +38,7 @@ SIGNATURES = {
     "mkb_peer_export": (c_int, [c_void_p, c_void_p]),
     "mkb_peer_open": (c_int, [c_void_p, c_void_p]),
     "mkb_peer_close": (c_int, [c_void_p]),
-    "mkb_peer_push": (c_int, [c_void_p] * 3 + [c_int] * 5 + [c_void_p]),
-    "mkb_peer_add_rmsnorm": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_float, c_void_p]),
+    "mkb_peer_reduce_add_rmsnorm": (c_int, [c_void_p] * 7 + [c_int] * 5 + [c_float, c_void_p]),
     "mkb_peer_status": (c_int, [c_void_p, c_void_p]),
     "mkb_peer_set_poll_limit": (c_int, [c_void_p, c_int64]),
 }

@@ -1,33 +1,35 @@
 // One-shot all-reduce over peer memory for the row-parallel linears of the tensor-parallel decode
-// step (sm_100a, NVLink/NVSwitch), fused with the residual add and RMS norm that consume it.
+// step (sm_100a, NVLink/NVSwitch), fused with the residual add and RMS norm that consume it: ONE
+// kernel per reduction, no library collective.
 //
 // Every rank owns one exchange buffer that all ranks of the node have mapped:
-//   [ flags: 2 parities x world x uint32 | sent: world x uint32 | status | pad to 1024 B ]
+//   [ flags: 2 parities x world x 8 rows x uint32 | sent: 8 x uint32 | status | poll limit | pad to 2 KB ]
 //   [ slots: 2 parities x world x rows x H fp16 ]
-// A reduction is two kernels on each rank, no library collective:
-//   * push: CTA p copies this rank's partial [M, H] into slot[parity][rank] of peer p's buffer with
-//     plain 16-byte stores over NVLink, fences, and then writes flag[parity][rank] = v on that
-//     peer.  v counts this rank's pushes (kept per CTA in the rank's own buffer); all ranks run the
-//     same sequence of reductions, so v is the same number everywhere, and parity = v & 1 keeps a
-//     fast rank's next reduction out of the slots a slow rank is still reading;
-//   * add + norm: waits (bounded) until all `world` flags of the parity carry v, adds the slots in
-//     rank order in fp32 (every rank gets the same bits), rounds the sum to fp16 as the
-//     library all-reduce would, and goes on exactly like add_rmsnorm.
-// Waits give up after a bounded number of polls, set the status word and let the kernel finish.
+// CTA m of the kernel handles row m of the partial [M, H]:
+//   * push: it copies row m into slot[parity][rank] of every rank's buffer (its own included) with
+//     plain 16-byte stores over NVLink, fences, and raises flag[parity][rank][m] = v in each buffer.
+//     v counts the reductions this row has taken part in (kept in the rank's own buffer); all ranks
+//     run the same sequence of reductions, so v is the same number everywhere, and parity = v & 1
+//     keeps a fast rank's next reduction out of the slots a slow rank is still reading;
+//   * wait: it polls (bounded) its own buffer until the `world` flags of row m carry v.  Every CTA
+//     pushes before it waits and flags persist, so no rank can wait for a rank that waits for it;
+//   * add + norm: it adds the `world` slots in rank order in fp32 (every rank gets the same bits),
+//     rounds the sum to fp16 as the library all-reduce would, adds the residual and normalises.
+// A wait that gives up sets the status word and lets the kernel finish; later waits are skipped.
 #include "mkb_common.cuh"
 
 namespace mkb {
 namespace {
 
-constexpr int kHeaderBytes = 1024;
+constexpr int kHeaderBytes = 2048;
 constexpr int kMaxWorld = 16;
-constexpr int kPushThreads = 1024;
+constexpr int kMaxRows = 8;
 constexpr int kGatherThreads = 1024;
 constexpr uint32_t kDefaultPolls = 60000000;  // of the order of half a minute: ranks are separate processes
 
 struct Header {
-  uint32_t flags[2][kMaxWorld];   // written by the peers
-  uint32_t sent[kMaxWorld];       // pushes this rank has made toward peer p (touched by CTA p only)
+  uint32_t flags[2][kMaxWorld][kMaxRows];   // written by the peers: [parity][source rank][row]
+  uint32_t sent[kMaxRows];                  // reductions row m has taken part in (touched by CTA m only)
   uint32_t status;                // non-zero when a wait expired
   uint32_t poll_limit;            // polls of one flag before a wait gives up
 };
@@ -38,50 +40,50 @@ __device__ __forceinline__ __half* slot_of(void* buffer, int parity, int source,
          (int64_t(parity) * world + source) * slot_halves;
 }
 
-// grid = world CTAs: CTA p serves peer p
-__global__ void __launch_bounds__(kPushThreads) peer_push_kernel(const __half* __restrict__ partial, void* const* peers,
-                                                                 void* own, int M, int H, int world, int rank,
-                                                                 int64_t slot_halves) {
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  const int p = blockIdx.x;
-  Header* mine = static_cast<Header*>(own);
-  const uint32_t v = mine->sent[p] + 1;   // only this CTA touches sent[p]
-  void* peer = peers[p];
-  __half* destination = slot_of(peer, int(v & 1u), rank, world, slot_halves);
-  const int64_t vectors = int64_t(M) * H / 8;
-  const uint4* source = reinterpret_cast<const uint4*>(partial);
-  uint4* target = reinterpret_cast<uint4*>(destination);
-  for (int64_t i = threadIdx.x; i < vectors; i += kPushThreads) target[i] = source[i];
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    mine->sent[p] = v;
-    volatile uint32_t* flag = &static_cast<Header*>(peer)->flags[v & 1u][rank];
-    *flag = v;
-  }
-}
-
-// One CTA per row m: residual[m,:] += sum over ranks of slot[r][m,:]; normed = rmsnorm(residual) * weight.
+// One CTA per row m: push, wait, then residual[m,:] += sum over ranks of slot[r][m,:]; normed = rmsnorm(residual) * weight.
 // `reduced` (optional) receives the fp16 sum, for callers that need the all-reduced tensor itself.
 constexpr int kGatherPieces = 2;   // rows up to 1024 * 2 * 8 = 16384 elements stay in registers
 
-__global__ void __launch_bounds__(kGatherThreads) peer_add_rmsnorm_kernel(__half* __restrict__ residual, void* own,
-                                                                          const __half* __restrict__ weight,
-                                                                          __half* __restrict__ normed,
-                                                                          __half* __restrict__ reduced, int H, int world,
-                                                                          int64_t slot_halves, float eps) {
+__global__ void __launch_bounds__(kGatherThreads) peer_reduce_add_rmsnorm_kernel(
+    const __half* __restrict__ partial, void* const* peers, void* own, __half* __restrict__ residual,
+    const __half* __restrict__ weight, __half* __restrict__ normed, __half* __restrict__ reduced, int H, int world,
+    int rank, int64_t slot_halves, float eps) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ float part_s[kGatherThreads / 32];
   __shared__ int ready_s;
   Header* mine = static_cast<Header*>(own);
-  const uint32_t v = mine->sent[0];   // the push that precedes this kernel in the stream has set it
+  const int m = blockIdx.x;
+  const uint32_t v = mine->sent[m] + 1;   // only this CTA touches sent[m]
   const int parity = int(v & 1u);
+  {
+    // push row m of the partial into this rank's slot on every rank
+    const uint4* source = reinterpret_cast<const uint4*>(partial + int64_t(m) * H);
+    uint4 piece[kGatherPieces];
+#pragma unroll
+    for (int k = 0; k < kGatherPieces; ++k) {
+      const int i = k * kGatherThreads + threadIdx.x;
+      piece[k] = i * 8 < H ? source[i] : make_uint4(0u, 0u, 0u, 0u);
+    }
+    for (int p = 0; p < world; ++p) {
+      uint4* target = reinterpret_cast<uint4*>(slot_of(peers[p], parity, rank, world, slot_halves) + int64_t(m) * H);
+#pragma unroll
+      for (int k = 0; k < kGatherPieces; ++k) {
+        const int i = k * kGatherThreads + threadIdx.x;
+        if (i * 8 < H) target[i] = piece[k];
+      }
+    }
+  }
+  __threadfence_system();
   if (threadIdx.x == 0) ready_s = 1;
   __syncthreads();
   if (threadIdx.x < world) {
-    const volatile uint32_t* flag = &mine->flags[parity][threadIdx.x];
+    volatile uint32_t* raised = &static_cast<Header*>(peers[threadIdx.x])->flags[parity][rank][m];
+    *raised = v;
+  }
+  if (threadIdx.x == 0) mine->sent[m] = v;
+  if (threadIdx.x < world) {
+    const volatile uint32_t* flag = &mine->flags[parity][threadIdx.x][m];
     // a wait that expired once is not repeated: every later reduction of a broken exchange would
     // otherwise add its own timeout
     const uint32_t limit = mine->status != 0 ? 0u : mine->poll_limit;
@@ -185,7 +187,7 @@ cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, v
 }  // namespace mkb
 
 extern "C" int64_t mkb_peer_buffer_bytes(int rows, int H, int world) {
-  if (rows < 1 || H < 8 || world < 1 || world > mkb::kMaxWorld) return 0;
+  if (rows < 1 || rows > mkb::kMaxRows || H < 8 || world < 1 || world > mkb::kMaxWorld) return 0;
   return mkb::kHeaderBytes + int64_t(2) * world * rows * H * 2;
 }
 
@@ -241,32 +243,24 @@ extern "C" int mkb_peer_close(void* buffer) {
   return MKB_OK;
 }
 
-extern "C" int mkb_peer_push(const void* partial, void* const* peers, void* own, int M, int H, int rows, int world,
-                             int rank, void* stream) {
+extern "C" int mkb_peer_reduce_add_rmsnorm(const void* partial, void* const* peers, void* own, void* residual,
+                                           const void* weight, void* normed, void* reduced, int M, int H, int rows,
+                                           int world, int rank, float eps, void* stream) {
   using namespace mkb;
-  MKB_REQUIRE(partial && peers && own, MKB_E_ARGUMENT, "peer_push: null pointer");
-  MKB_REQUIRE(M >= 1 && M <= rows && H >= 8 && H % 8 == 0 && world >= 1 && world <= kMaxWorld && rank >= 0 && rank < world,
-              MKB_E_ARGUMENT, "peer_push: bad shape");
-  MKB_REQUIRE(reinterpret_cast<uintptr_t>(partial) % 16 == 0, MKB_E_ARGUMENT, "peer_push: partial must be 16-byte aligned");
-  const cudaError_t launched = launch_dependent(peer_push_kernel, dim3(world), dim3(kPushThreads), stream,
-                                                static_cast<const __half*>(partial), peers, own, M, H, world, rank,
-                                                int64_t(rows) * H);
-  if (launched != cudaSuccess) return cuda_fail(launched, "peer_push launch");
-  return MKB_OK;
-}
-
-extern "C" int mkb_peer_add_rmsnorm(void* residual, void* own, const void* weight, void* normed, void* reduced, int M,
-                                    int H, int rows, int world, float eps, void* stream) {
-  using namespace mkb;
-  MKB_REQUIRE(residual && own && weight && normed, MKB_E_ARGUMENT, "peer_add_rmsnorm: null pointer");
-  MKB_REQUIRE(M >= 1 && M <= rows && H % 8 == 0 && H >= 8 && H <= kGatherThreads * kGatherPieces * 8 && world >= 1 &&
-                  world <= kMaxWorld,
-              MKB_E_UNSUPPORTED, "peer_add_rmsnorm: unsupported shape");
+  MKB_REQUIRE(partial && peers && own && residual && weight && normed, MKB_E_ARGUMENT,
+              "peer_reduce_add_rmsnorm: null pointer");
+  MKB_REQUIRE(M >= 1 && M <= rows && rows <= kMaxRows && H % 8 == 0 && H >= 8 &&
+                  H <= kGatherThreads * kGatherPieces * 8 && world >= 1 && world <= kMaxWorld && rank >= 0 && rank < world,
+              MKB_E_UNSUPPORTED, "peer_reduce_add_rmsnorm: unsupported shape");
+  MKB_REQUIRE(((reinterpret_cast<uintptr_t>(partial) | reinterpret_cast<uintptr_t>(residual) |
+                reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(normed) |
+                reinterpret_cast<uintptr_t>(reduced)) & 15) == 0,
+              MKB_E_ARGUMENT, "peer_reduce_add_rmsnorm: pointers must be 16-byte aligned");
   const cudaError_t launched = launch_dependent(
-      peer_add_rmsnorm_kernel, dim3(M), dim3(kGatherThreads), stream, static_cast<__half*>(residual), own,
-      static_cast<const __half*>(weight), static_cast<__half*>(normed), static_cast<__half*>(reduced), H, world,
-      int64_t(rows) * H, eps);
-  if (launched != cudaSuccess) return cuda_fail(launched, "peer_add_rmsnorm launch");
+      peer_reduce_add_rmsnorm_kernel, dim3(M), dim3(kGatherThreads), stream, static_cast<const __half*>(partial), peers,
+      own, static_cast<__half*>(residual), static_cast<const __half*>(weight), static_cast<__half*>(normed),
+      static_cast<__half*>(reduced), H, world, rank, int64_t(rows) * H, eps);
+  if (launched != cudaSuccess) return cuda_fail(launched, "peer_reduce_add_rmsnorm launch");
   return MKB_OK;
 }
 

@@ -169,8 +169,8 @@ class PeerExchange:
     """The exchange buffers of the one-shot peer-memory all-reduce (``mkb_peer_*``).
 
     Every rank allocates one buffer, the ranks swap its 64-byte handle through the process group, and
-    each maps the others' buffers; ``push`` then writes a partial into all of them and
-    ``add_rmsnorm`` consumes the sum.  Ranks must share a node (NVLink/NVSwitch peer access).
+    each maps the others' buffers; ``reduce_add_rmsnorm`` then pushes a partial into all of them, waits for
+    the other ranks' partials and consumes the sum, in one kernel.  Ranks must share a node (NVLink/NVSwitch peer access).
     """
 
     def __init__(self, *, rank: int, world: int, rows: int, width: int, device: torch.device,
@@ -204,19 +204,15 @@ class PeerExchange:
             self.peers = torch.tensor(pointers, dtype=torch.int64, device=device)
         dist.barrier(group=group)
 
-    def push(self, partial: Tensor) -> None:
-        status = _native.library().mkb_peer_push(partial.data_ptr(), self.peers.data_ptr(), self.own, partial.shape[0],
-                                                 self.width, self.rows, self.world, self.rank,
-                                                 torch.cuda.current_stream(self.device).cuda_stream)
-        _native.check(status, "peer_push")
-
-    def add_rmsnorm(self, residual: Tensor, weight: Tensor, normed: Tensor, eps: float,
-                    reduced: Tensor | None = None) -> None:
-        status = _native.library().mkb_peer_add_rmsnorm(
-            residual.data_ptr(), self.own, weight.data_ptr(), normed.data_ptr(),
-            None if reduced is None else reduced.data_ptr(), residual.shape[0], self.width, self.rows, self.world,
-            float(eps), torch.cuda.current_stream(self.device).cuda_stream)
-        _native.check(status, "peer_add_rmsnorm")
+    def reduce_add_rmsnorm(self, partial: Tensor, residual: Tensor, weight: Tensor, normed: Tensor, eps: float,
+                           reduced: Tensor | None = None) -> None:
+        """All-reduce ``partial`` over the ranks, ``residual += sum``, ``normed = rms_norm(residual) * weight``:
+        one kernel launch."""
+        status = _native.library().mkb_peer_reduce_add_rmsnorm(
+            partial.data_ptr(), self.peers.data_ptr(), self.own, residual.data_ptr(), weight.data_ptr(),
+            normed.data_ptr(), None if reduced is None else reduced.data_ptr(), partial.shape[0], self.width,
+            self.rows, self.world, self.rank, float(eps), torch.cuda.current_stream(self.device).cuda_stream)
+        _native.check(status, "peer_reduce_add_rmsnorm")
 
     def status(self) -> int:
         """Non-zero when a bounded wait of an earlier reduction expired."""
@@ -354,7 +350,7 @@ class TensorParallelDecoder:
             attention_norm, mlp_norm = self.norms[index]
             k_cache, v_cache = self.k_cache[index], self.v_cache[index]
             if exchange is not None and delta is not None:
-                exchange.add_rmsnorm(residual, attention_norm, normed, c.eps)   # the pushed down-projection
+                exchange.reduce_add_rmsnorm(delta, residual, attention_norm, normed, c.eps)   # the down-projection shards
             else:
                 kernels.add_rmsnorm(residual, delta, attention_norm, normed, c.eps)
             block["qkv"](normed, work["qkv"])
@@ -364,21 +360,18 @@ class TensorParallelDecoder:
                                      kv_heads=local_kv, head_dim=c.head_dim)
             block["o"](work["attention"], work["o"])
             if exchange is not None:
-                exchange.push(work["o"])
-                exchange.add_rmsnorm(residual, mlp_norm, normed, c.eps)
+                exchange.reduce_add_rmsnorm(work["o"], residual, mlp_norm, normed, c.eps)
             else:
                 self._all_reduce(work["o"])
                 kernels.add_rmsnorm(residual, work["o"], mlp_norm, normed, c.eps)
             block["gate_up"](normed, work["gate_up"])
             kernels.silu_mul(work["gate_up"], work["act"])
             block["down"](work["act"], work["down"])
-            if exchange is not None:
-                exchange.push(work["down"])
-            else:
+            if exchange is None:
                 self._all_reduce(work["down"])
             delta = work["down"]
         if exchange is not None and delta is not None:
-            exchange.add_rmsnorm(residual, self.final_norm, normed, c.eps)
+            exchange.reduce_add_rmsnorm(delta, residual, self.final_norm, normed, c.eps)
         else:
             kernels.add_rmsnorm(residual, delta, self.final_norm, normed, c.eps)
         torch.matmul(normed, self.head.t(), out=work["logits"])

@@ -100,7 +100,7 @@ def measure(rank: int, world: int, device: torch.device, steps: int, warmup: int
                                                layers=layers, max_batch=max(BATCHES), capacity=CONTEXT + 64,
                                                group=group)
     model.fill_cache(CONTEXT)
-    results = {"batches": {}, "launches_per_step": len(model.blocks) * (9 if world == 1 else 11) + 3,
+    results = {"batches": {}, "launches_per_step": len(model.blocks) * 9 + 3,
                "collectives_per_step": 0 if world == 1 else 2 * len(model.blocks) + 1, "collective": "none"}
     if world > 1:
         # the library all-reduce first, as the yardstick; then the peer-memory reduction, which is the product path
@@ -110,7 +110,7 @@ def measure(rank: int, world: int, device: torch.device, steps: int, warmup: int
         results["collective"] = "nccl all-reduce"
         try:
             model.enable_peer_exchange()
-            results["collective"] = "peer-memory push + fused add/norm (mkb_peer_*); logits by nccl all-gather"
+            results["collective"] = "peer-memory all-reduce fused with add + norm, one kernel (mkb_peer_reduce_add_rmsnorm); logits by nccl all-gather"
             probe_tokens = torch.zeros(1, dtype=torch.int64, device=device)
             probe_positions = torch.full((1,), CONTEXT, dtype=torch.int32, device=device)
             model.step(probe_tokens, probe_positions)
