@@ -302,7 +302,8 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 __global__ void __launch_bounds__(kGroupThreads) attention_group_kernel(const __half* __restrict__ qkv, const int* __restrict__ positions,
                                                                  const __half* __restrict__ k_cache,
                                                                  const __half* __restrict__ v_cache, __half* __restrict__ out,
-                                                                 int q_heads, int kv_heads, int capacity, float scale) {
+                                                                 int q_heads, int kv_heads, int capacity, float scale,
+                                                                 float theta, int fuse_rope) {
   // programmatic dependent launch: let the next kernel in the stream become resident now, then wait
   // for everything this kernel reads
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -318,6 +319,29 @@ __global__ void __launch_bounds__(kGroupThreads) attention_group_kernel(const __
   const __half* values = v_cache + (int64_t(m) * kv_heads + kv) * capacity * D;
   uint8_t* k_tile = smem + warp * 2 * kTileBytes;
   uint8_t* v_tile = k_tile + kTileBytes;
+  __shared__ float cos_s[D / 2], sin_s[D / 2];
+  if (fuse_rope) {
+    // rotary embedding fused in: this CTA rotates the new key of its head and appends key and value
+    // to the caches itself (nobody else reads that slot), and rotates its query heads in registers
+    const int position = length - 1;
+    if (threadIdx.x < D / 2) {
+      const float freq = powf(theta, -2.f * float(threadIdx.x) / float(D));
+      float sine, cosine;
+      sincosf(float(position) * freq, &sine, &cosine);
+      cos_s[threadIdx.x] = cosine;
+      sin_s[threadIdx.x] = sine;
+      const __half* k = qkv + int64_t(m) * row + int64_t(q_heads + kv) * D;
+      const float a = __half2float(k[threadIdx.x]), b = __half2float(k[threadIdx.x + D / 2]);
+      __half* slot = const_cast<__half*>(keys) + int64_t(position) * D;
+      slot[threadIdx.x] = __float2half_rn(a * cosine - b * sine);
+      slot[threadIdx.x + D / 2] = __float2half_rn(b * cosine + a * sine);
+    } else if (threadIdx.x < D / 2 + D) {
+      const int i = threadIdx.x - D / 2;
+      const_cast<__half*>(values)[int64_t(position) * D + i] = qkv[int64_t(m) * row + int64_t(q_heads + kv_heads + kv) * D + i];
+    }
+    __threadfence();
+    __syncthreads();
+  }
 
   // Q fragments of this group: a[ks] = rows (g, g+8) x dims 16ks + (2t, 2t+1, 2t+8, 2t+9)
   uint32_t qa[8][4];
@@ -330,6 +354,19 @@ __global__ void __launch_bounds__(kGroupThreads) attention_group_kernel(const __
       qa[ks][1] = 0u;
       qa[ks][3] = 0u;
     }
+  }
+  if (fuse_rope) {
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+      for (int part = 0; part < 4; part += 2) {   // registers 0 and 2 of the fragment: dims 16ks + 2t and 16ks + 8 + 2t
+        const int d = 16 * ks + (part ? 8 : 0) + 2 * t;
+        const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks][part]));
+        const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&qa[ks + 4][part]));
+        const float c0 = cos_s[d], s0 = sin_s[d], c1 = cos_s[d + 1], s1 = sin_s[d + 1];
+        qa[ks][part] = pack_half2(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
+        qa[ks + 4][part] = pack_half2(hi.x * c0 + lo.x * s0, hi.y * c1 + lo.y * s1);
+      }
   }
   float o[16][2];   // row g x dims 8jn + (2t, 2t+1)
 #pragma unroll
@@ -533,7 +570,7 @@ extern "C" int mkb_attention_decode(const void* qkv, const int* positions, const
     const cudaError_t launched = launch_dependent(
         attention_group_kernel, dim3(M, kv_heads), dim3(kGroupThreads), group_smem, stream,
         static_cast<const __half*>(qkv), positions, static_cast<const __half*>(k_cache),
-        static_cast<const __half*>(v_cache), static_cast<__half*>(out), q_heads, kv_heads, capacity, scale);
+        static_cast<const __half*>(v_cache), static_cast<__half*>(out), q_heads, kv_heads, capacity, scale, 0.f, 0);
     if (launched != cudaSuccess) return cuda_fail(launched, "attention_decode launch");
     return MKB_OK;
   }
@@ -548,6 +585,31 @@ extern "C" int mkb_attention_decode(const void* qkv, const int* positions, const
       static_cast<const __half*>(k_cache), static_cast<const __half*>(v_cache), static_cast<__half*>(out), q_heads,
       kv_heads, capacity, scale);
   if (launched != cudaSuccess) return cuda_fail(launched, "attention_decode launch");
+  return MKB_OK;
+}
+
+extern "C" int mkb_rope_attention_decode(const void* qkv, const int* positions, void* k_cache, void* v_cache, void* out,
+                                         int M, int q_heads, int kv_heads, int head_dim, int capacity, float theta,
+                                         float scale, void* stream) {
+  using namespace mkb;
+  MKB_REQUIRE(head_dim == 128, MKB_E_UNSUPPORTED, "rope_attention_decode: head_dim %d (128 supported)", head_dim);
+  MKB_REQUIRE(M >= 0 && q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && capacity > 0, MKB_E_ARGUMENT,
+              "rope_attention_decode: bad shape");
+  MKB_REQUIRE(q_heads / kv_heads <= 8, MKB_E_UNSUPPORTED,
+              "rope_attention_decode: %d query heads per key-value head (at most 8)", q_heads / kv_heads);
+  if (M == 0) return MKB_OK;
+  MKB_REQUIRE(qkv && positions && k_cache && v_cache && out, MKB_E_ARGUMENT, "rope_attention_decode: null pointer");
+  const size_t group_smem = size_t(kGroupWarps) * 2 * kTileBytes;
+  static bool opted = false;
+  if (!opted) {
+    cudaFuncSetAttribute(attention_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(group_smem));
+    opted = true;
+  }
+  const cudaError_t launched = launch_dependent(
+      attention_group_kernel, dim3(M, kv_heads), dim3(kGroupThreads), group_smem, stream,
+      static_cast<const __half*>(qkv), positions, static_cast<const __half*>(k_cache),
+      static_cast<const __half*>(v_cache), static_cast<__half*>(out), q_heads, kv_heads, capacity, scale, theta, 1);
+  if (launched != cudaSuccess) return cuda_fail(launched, "rope_attention_decode launch");
   return MKB_OK;
 }
 

@@ -277,6 +277,18 @@ def attention_decode(qkv: Tensor, positions: Tensor, k_cache: Tensor, v_cache: T
     _native.check(status, "attention_decode")
 
 
+def rope_attention_decode(qkv: Tensor, positions: Tensor, k_cache: Tensor, v_cache: Tensor, out: Tensor, *,
+                          q_heads: int, kv_heads: int, head_dim: int, theta: float, scale: float | None = None) -> None:
+    """``rope_append`` and ``attention_decode`` in one launch (at most 8 query heads per key-value head);
+    ``qkv`` is left unrotated."""
+    if scale is None:
+        scale = head_dim ** -0.5
+    status = _native.library().mkb_rope_attention_decode(
+        qkv.data_ptr(), positions.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), qkv.shape[0],
+        q_heads, kv_heads, head_dim, k_cache.shape[2], theta, scale, _stream(qkv.device))
+    _native.check(status, "rope_attention_decode")
+
+
 def silu_mul(gate_up: Tensor, out: Tensor) -> None:
     """``out = silu(gate_up[:, :I]) * gate_up[:, I:]``."""
     status = _native.library().mkb_silu_mul(gate_up.data_ptr(), out.data_ptr(), gate_up.shape[0], out.shape[1],

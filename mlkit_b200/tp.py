@@ -354,10 +354,15 @@ class TensorParallelDecoder:
             else:
                 kernels.add_rmsnorm(residual, delta, attention_norm, normed, c.eps)
             block["qkv"](normed, work["qkv"])
-            kernels.rope_append(work["qkv"], positions, k_cache, v_cache, q_heads=local_q, kv_heads=local_kv,
-                                head_dim=c.head_dim, theta=c.rope_theta)
-            kernels.attention_decode(work["qkv"], positions, k_cache, v_cache, work["attention"], q_heads=local_q,
-                                     kv_heads=local_kv, head_dim=c.head_dim)
+            if local_q <= 8 * local_kv and c.head_dim == 128:   # rotary embedding, cache append and attention in one launch
+                kernels.rope_attention_decode(work["qkv"], positions, k_cache, v_cache, work["attention"],
+                                              q_heads=local_q, kv_heads=local_kv, head_dim=c.head_dim,
+                                              theta=c.rope_theta)
+            else:
+                kernels.rope_append(work["qkv"], positions, k_cache, v_cache, q_heads=local_q, kv_heads=local_kv,
+                                    head_dim=c.head_dim, theta=c.rope_theta)
+                kernels.attention_decode(work["qkv"], positions, k_cache, v_cache, work["attention"],
+                                         q_heads=local_q, kv_heads=local_kv, head_dim=c.head_dim)
             block["o"](work["attention"], work["o"])
             if exchange is not None:
                 exchange.reduce_add_rmsnorm(work["o"], residual, mlp_norm, normed, c.eps)

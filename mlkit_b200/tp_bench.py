@@ -100,7 +100,7 @@ def measure(rank: int, world: int, device: torch.device, steps: int, warmup: int
                                                layers=layers, max_batch=max(BATCHES), capacity=CONTEXT + 64,
                                                group=group)
     model.fill_cache(CONTEXT)
-    results = {"batches": {}, "launches_per_step": len(model.blocks) * 9 + 3,
+    results = {"batches": {}, "launches_per_step": len(model.blocks) * 8 + 3,
                "collectives_per_step": 0 if world == 1 else 2 * len(model.blocks) + 1, "collective": "none"}
     if world > 1:
         # the library all-reduce first, as the yardstick; then the peer-memory reduction, which is the product path

@@ -82,6 +82,30 @@ def test_rope_append_and_attention_match_torch():
         assert rel(out[m], expected) < 2e-3
 
 
+def test_fused_rope_attention_equals_the_two_kernels():
+    """rope_attention_decode: same cache contents and, up to the fp16 rounding of the rotated query,
+    the same attention output as rope_append followed by attention_decode."""
+    torch.manual_seed(4)
+    for q_heads, kv_heads in ((8, 2), (8, 1), (16, 2)):
+        batch, dim, capacity = 3, 128, 96
+        qkv = torch.randn(batch, (q_heads + 2 * kv_heads) * dim, device="cuda").half()
+        positions = torch.tensor([0, 40, 95], dtype=torch.int32, device="cuda")
+        caches = [torch.randn(batch, kv_heads, capacity, dim, device="cuda").half() for _ in range(2)]
+        k_two, v_two, k_one, v_one = caches[0].clone(), caches[1].clone(), caches[0].clone(), caches[1].clone()
+        rotated = qkv.clone()
+        kernels.rope_append(rotated, positions, k_two, v_two, q_heads=q_heads, kv_heads=kv_heads, head_dim=dim, theta=5e5)
+        expected = torch.empty(batch, q_heads * dim, device="cuda", dtype=torch.float16)
+        kernels.attention_decode(rotated, positions, k_two, v_two, expected, q_heads=q_heads, kv_heads=kv_heads, head_dim=dim)
+        untouched = qkv.clone()
+        got = torch.empty_like(expected)
+        kernels.rope_attention_decode(qkv, positions, k_one, v_one, got, q_heads=q_heads, kv_heads=kv_heads,
+                                      head_dim=dim, theta=5e5)
+        assert torch.equal(qkv, untouched)
+        assert torch.equal(v_one, v_two)
+        assert rel(k_one, k_two) < 1e-3
+        assert rel(got, expected) < 2e-3
+
+
 def test_silu_mul_matches_torch():
     torch.manual_seed(2)
     gate_up = torch.randn(5, 2 * 1024, device="cuda").half()
