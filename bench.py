@@ -42,8 +42,8 @@ METRIC = "packed_int4_g128_gemv_hbm_gbps"
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate-shape launch (4096 -> 14336) from the profiler
 # captures summarised in profiles/gemv_tiled_gate_4096x14336_M1.md and gemv_bulk_gate_4096x14336_M8.md;
 # refreshed when a kernel changes
-TILED_GATE_M1_DRAM_BYTES = 30.3145e6
-BULK_GATE_M8_DRAM_BYTES = 30.3875e6
+TILED_GATE_M1_DRAM_BYTES = 30.3293e6
+BULK_GATE_M8_DRAM_BYTES = 30.3890e6
 
 
 def gemv_bytes(out_rows: int, width: int, rows_in: int) -> int:
