@@ -193,7 +193,8 @@ int mkb_hadamard(const void* x, const int8_t* signs, const float* basis, void* y
  *     (rotate-half pairing, angle positions[m] * theta^(-2i/head_dim)) and stores k, v at
  *     cache[m, kv_head, positions[m], :]; caches are [M, kv_heads, capacity, head_dim].
  * mkb_attention_decode: out[m, head, :] = softmax(q . K[0..positions[m]] * scale) V, grouped-query,
- *     head_dim 128.
+ *     head_dim 128.  With at most 8 query heads per key-value head it runs on the tensor cores, one
+ *     CTA per (m, key-value head), the softmax weights rounded to fp16 for the second product.
  * mkb_silu_mul: out[m, i] = silu(gate_up[m, i]) * gate_up[m, I + i].
  */
 int mkb_add_rmsnorm(void* residual, const void* delta, const void* weight, void* normed,
