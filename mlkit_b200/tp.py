@@ -178,29 +178,48 @@ class PeerExchange:
         import ctypes
 
         self.rank, self.world, self.rows, self.width, self.device = rank, world, rows, width, device
+        self.own: int | None = None
+        self.opened: list[int] = []
         library = _native.library()
+
+        def agreed(problem: str | None, stage: str) -> None:
+            """Every rank learns whether every rank got through ``stage``: no rank may be left in a collective."""
+            flag = torch.tensor([0 if problem is None else 1], dtype=torch.int32, device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
+            if int(flag) != 0:
+                self.close()
+                raise RuntimeError(f"peer exchange: {stage} failed on " +
+                                   ("this rank: " + problem if problem is not None else "another rank"))
+
         with torch.cuda.device(device):
-            size = library.mkb_peer_buffer_bytes(rows, width, world)
-            if size <= 0:
-                raise ValueError(f"peer exchange does not cover rows={rows} width={width} world={world}")
-            own = ctypes.c_void_p()
-            _native.check(library.mkb_peer_alloc(size, ctypes.byref(own)), "peer_alloc")
-            self.own = own.value
-            handle = ctypes.create_string_buffer(64)
-            _native.check(library.mkb_peer_export(self.own, handle), "peer_export")
+            problem, handle = None, ctypes.create_string_buffer(64)
+            try:
+                size = library.mkb_peer_buffer_bytes(rows, width, world)
+                if size <= 0:
+                    raise ValueError(f"no layout for rows={rows} width={width} world={world}")
+                own = ctypes.c_void_p()
+                _native.check(library.mkb_peer_alloc(size, ctypes.byref(own)), "peer_alloc")
+                self.own = own.value
+                _native.check(library.mkb_peer_export(self.own, handle), "peer_export")
+            except Exception as error:  # reported to all ranks below
+                problem = repr(error)
+            agreed(problem, "allocating and exporting the buffer")
             handles: list = [None] * world
             dist.all_gather_object(handles, bytes(handle.raw), group=group)
-            self.opened: list[int] = []
             pointers = []
-            for peer, raw in enumerate(handles):
-                if peer == rank:
-                    pointers.append(self.own)
-                    continue
-                mapped = ctypes.c_void_p()
-                _native.check(library.mkb_peer_open(ctypes.create_string_buffer(raw, 64), ctypes.byref(mapped)),
-                              "peer_open")
-                self.opened.append(mapped.value)
-                pointers.append(mapped.value)
+            try:
+                for peer, raw in enumerate(handles):
+                    if peer == rank:
+                        pointers.append(self.own)
+                        continue
+                    mapped = ctypes.c_void_p()
+                    _native.check(library.mkb_peer_open(ctypes.create_string_buffer(raw, 64), ctypes.byref(mapped)),
+                                  "peer_open")
+                    self.opened.append(mapped.value)
+                    pointers.append(mapped.value)
+            except Exception as error:
+                problem = repr(error)
+            agreed(problem, "mapping the other ranks' buffers")
             self.peers = torch.tensor(pointers, dtype=torch.int64, device=device)
         dist.barrier(group=group)
 
