@@ -45,8 +45,10 @@ enum {
                              activation for its share of K, so for one or two rows a separate SwiGLU kernel
                              is as fast; it pays when the launch count matters more.  The reference leaves this
                              product to the model code between two PackedLinear calls */
-  MKB_GEMV_BULK = 4    /* TMA-fed kernel: whole 16-row units by cp.async.bulk.tensor into a shared-memory ring
+  MKB_GEMV_BULK = 4,   /* TMA-fed kernel: whole 16-row units by cp.async.bulk.tensor into a shared-memory ring
                           (INT4 integer grid, fp16, K % 256 == 0; needs the workspace when K is split) */
+  MKB_GEMV_STREAM = 5  /* streaming kernel: activations in registers, weights through per-warp cp.async rings
+                          (integer grid, fp16, group 128, K % 128 == 0); what AUTO takes when it applies */
 };
 
 int mkb_version(void);

@@ -11,7 +11,7 @@ from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 from mlkit_b200 import build as _build
 
 F16, BF16, F32 = 0, 1, 2
-GEMV_AUTO, GEMV_SCALAR, GEMV_TILED, GEMV_TMEM, GEMV_BULK = 0, 1, 2, 3, 4
+GEMV_AUTO, GEMV_SCALAR, GEMV_TILED, GEMV_TMEM, GEMV_BULK, GEMV_STREAM = 0, 1, 2, 3, 4, 5
 GEMV_GATED = 0x100
 
 SIGNATURES = {

@@ -65,7 +65,16 @@ int launch_gemv_bulk(const void* x, const uint8_t* packed, const void* scales, c
                      int64_t packed_row_stride, int64_t scale_row_stride, float grid_minimum, cudaStream_t stream);
 bool prefer_bulk(int M, int N, int K);
 
+int gemv_stream_supported(int M, int N, int K, int group, int bits, int x_dtype, int scale_dtype, const void* x,
+                          const uint8_t* packed, const void* scales, int64_t packed_row_stride,
+                          int64_t scale_row_stride, const void* zeros, int integer_grid, float grid_minimum);
+int launch_gemv_stream(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y, int M,
+                       int N, int K, int64_t packed_row_stride, int64_t scale_row_stride, float grid_minimum,
+                       cudaStream_t stream);
+
 }  // namespace mkb
+
+
 
 extern "C" int mkb_version(void) { return 102; }
 
@@ -122,13 +131,21 @@ extern "C" int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* sca
               "gemv: lut_len=%d does not fit %d-bit codes", lut_len, bits);
   const int gated = (kernel & MKB_GEMV_GATED) != 0;
   kernel &= ~MKB_GEMV_GATED;
-  MKB_REQUIRE(kernel >= MKB_GEMV_AUTO && kernel <= MKB_GEMV_BULK, MKB_E_ARGUMENT, "gemv: unknown kernel choice");
+  MKB_REQUIRE(kernel >= MKB_GEMV_AUTO && kernel <= MKB_GEMV_STREAM, MKB_E_ARGUMENT, "gemv: unknown kernel choice");
   if (N == 0) return MKB_OK;
   MKB_REQUIRE(x && packed && scales && lut && y, MKB_E_ARGUMENT, "gemv: null pointer");
   MKB_REQUIRE(gemv_scalar_supported(K, group, bits), MKB_E_UNSUPPORTED,
               "gemv: K=%d or group=%d splits a packing word of %d-bit codes", K, group, bits);
   MKB_REQUIRE(K > 0, MKB_E_UNSUPPORTED, "gemv: empty reduction");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool stream_ok = lut_len == (1 << bits) &&
+                         gemv_stream_supported(M, N, K, group, bits, x_dtype, scale_dtype, x, packed, scales,
+                                               packed_row_stride, scale_row_stride, zeros, integer_grid, grid_minimum);
+  if (kernel == MKB_GEMV_STREAM)
+    MKB_REQUIRE(stream_ok && !gated, MKB_E_UNSUPPORTED, "gemv: the streaming kernel does not cover these arguments");
+  if (kernel == MKB_GEMV_STREAM || (!gated && kernel == MKB_GEMV_AUTO && stream_ok))
+    return launch_gemv_stream(x, packed, scales, bias, y, M, N, K, packed_row_stride, scale_row_stride,
+                              grid_minimum, s);
   const bool tiled_ok = gemv_tiled_supported(M, K, group, bits, x_dtype, scale_dtype, x, packed, packed_row_stride);
   const bool tmem_ok = workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) % 16) == 0 && lut_len == 16 &&
                        gemv_umma_supported(M, K, group, bits, x_dtype, scale_dtype, x, packed, packed_row_stride, zeros,

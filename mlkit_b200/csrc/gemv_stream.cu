@@ -1,0 +1,547 @@
+// Streaming packed matvec for integer grids with one scale per 128 codes (sm_100a), M <= 8, fp16.
+//
+// The kernel is written around two budgets.  At the HBM rate an SM has about 45 cycles per KB of
+// packed weights, i.e. roughly 90 integer-pipe operations and 180 issue slots per 16-row x 128-code
+// tile; and a launch streams for only a few microseconds, so whatever happens before the first
+// tensor-core step or after the last one is paid in full.  Hence:
+//
+//   * one CTA of up to 16 warps per SM owns row tiles blockIdx.x, blockIdx.x + gridDim.x, ... ("visits").
+//     A warp owns the SAME KT k-tiles of every row tile it visits, so its activation fragments, their
+//     per-tile sums and all shared-memory offsets are loop invariants held in registers: nothing is
+//     staged per CTA and no activation byte is read from shared memory in the loop;
+//   * weights travel global -> shared by per-thread cp.async (L1 bypass) into a private ring of DV
+//     visits per warp (up to ~190 KB per SM in flight, far more than bandwidth x latency needs), so
+//     the ring fills before `griddepcontrol.wait` returns and while activations are fetched.  One copy
+//     instruction of a warp covers whole 128-byte lines; the shared layout is chosen so that both
+//     the copies and the 16-byte fragment reads are free of bank conflicts;
+//   * codes become fp16 tensor-core operands with one AND per PAIR of codes: the masked bits of a
+//     code are the fp16 subnormal c * 2^-24 (or c * 2^-20 for odd codes, which keep their own
+//     accumulator, so nothing is rounded; the two are recombined with an exact power of two).  The
+//     grid minimum enters as min * sum(x) per k-tile, preloaded as the accumulator's start value; the
+//     group scale multiplies the fp32 k-tile sum;
+//   * a visit's partial sums (one per warp) meet in shared memory; every R visits the CTA adds them in
+//     warp order and stores fp16.  When K is split over the CTAs of a thread-block cluster (large K or
+//     small N) the per-CTA sums meet once more, at the end, through distributed shared memory in a
+//     fixed order.  Results do not depend on timing.
+#include <cooperative_groups.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+#include <type_traits>
+
+#include "mkb_common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace mkb {
+namespace {
+
+constexpr int kMaxWarps = 16;
+constexpr int kMaxClusterVisits = 64;  // bound on the per-CTA sums kept for the cluster exchange
+
+struct StreamArgs {
+  const __half* x;
+  const uint8_t* packed;
+  const __half* scales;
+  const __half* bias;
+  __half* y;
+  int M, N, K;
+  int64_t packed_row_stride, scale_row_stride;
+  int row_tiles;    // ceil(N / 16)
+  int k_warps;      // K / (128 * KT): warp-sized shares of K over all slabs
+  int KW, RG;       // warps along K and row tiles per visit of one CTA (the CTA has KW * RG warps)
+  int slabs;        // CTAs of a cluster along K (gridDim.y)
+  int visits;       // visits of every CTA
+  int batch;        // visits whose partial sums shared memory holds between two reductions (a multiple of R)
+  int early;        // visits copied before the dependency wait; the rest of the ring follows the activation loads
+  int kw_inverse, rg_inverse;  // ceil(65536 / KW), ceil(65536 / RG): small quotients by multiply and shift
+  float grid_min;
+};
+
+__device__ __forceinline__ void copy16(uint32_t smem_address, const void* global) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_address), "l"(global) : "memory");
+}
+__device__ __forceinline__ void copy4(uint32_t smem_address, const void* global) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_address), "l"(global) : "memory");
+}
+// base + index * step, as one multiply-add on the fp32/integer-multiply pipe
+template <typename T>
+__device__ __forceinline__ const T* offset_pointer(const T* base, uint32_t index, uint32_t step_bytes) {
+  uint64_t out;
+  asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(out) : "r"(index), "r"(step_bytes), "l"(reinterpret_cast<uint64_t>(base)));
+  return reinterpret_cast<const T*>(out);
+}
+__device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void copy_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
+
+// d = a * b + c on the tensor cores, 16 weight rows x 16 codes times 16 codes x 8 activation rows.
+__device__ __forceinline__ void mma_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1, float c0, float c1, float c2, float c3) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(c2), "f"(c3));
+}
+__device__ __forceinline__ void mma_next(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Geometry of one visit of one warp: 16 rows x KT k-tiles of 128 codes.
+template <int BITS, int KT>
+struct Visit {
+  static constexpr int TILE_ROW_BYTES = 16 * BITS;               // 128 codes of one row
+  static constexpr int TILE_BYTES = 16 * TILE_ROW_BYTES;         // 16 rows
+  static constexpr int SEGMENT = KT * TILE_ROW_BYTES;            // contiguous bytes of one row per visit
+  static constexpr int LANES_PER_ROW = SEGMENT / 16;             // 16-byte vectors per row segment
+  static constexpr int ROWS_PER_COPY = 32 / LANES_PER_ROW;       // rows one copy instruction of a warp covers
+  static constexpr int COPIES = 16 / ROWS_PER_COPY;              // copy instructions per lane and visit
+  static constexpr int SCALE_OFFSET = KT * TILE_BYTES;            // 16 rows x 4 bytes of scales follow the codes
+  static constexpr int SLOT_BYTES = KT * TILE_BYTES + 64;
+  static constexpr int VECTORS_PER_TILE_ROW = TILE_ROW_BYTES / 16;
+  static_assert(BITS == 4, "only 4-bit codes are laid out so far");
+  static_assert(LANES_PER_ROW >= 4 && LANES_PER_ROW <= 16 && ROWS_PER_COPY % 2 == 0, "visit geometry");
+};
+
+__device__ __forceinline__ uint4 load_shared16(uint32_t address) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(address));
+  return v;
+}
+__device__ __forceinline__ uint32_t load_shared4(uint32_t address) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(address));
+  return v;
+}
+__device__ __forceinline__ void store_shared16(uint32_t address, float a, float b, float c, float d) {
+  asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(address), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+template <int BITS, int KT, int R>
+__global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const StreamArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  using V = Visit<BITS, KT>;
+  // dependents may become resident at once: they only copy constants until their own wait returns
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warps = blockDim.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int rg = (warp * a.kw_inverse) >> 16, kw = warp - rg * a.KW;   // warp / KW, warp % KW
+  const int slab = int(blockIdx.y);
+  const int k_warp = slab * a.KW + kw;           // this warp's share of K
+  const int tile0 = k_warp * KT;                 // first k-tile
+  const int visit_stride = int(gridDim.x) * a.RG;
+  const int first_row_tile = int(blockIdx.x) * a.RG + rg;
+  // visits in which this warp has a row tile: all of the CTA's, or all but the last; a warp past the
+  // end of K has none.  The last row tile of a layer may be partial: the visits before `whole_visits`
+  // have all 16 rows.
+  int my_visits = a.visits - (first_row_tile + (a.visits - 1) * visit_stride >= a.row_tiles ? 1 : 0);
+  if (k_warp >= a.k_warps) my_visits = 0;
+  const int whole_visits = (a.N & 15) ? my_visits - 1 : my_visits;
+
+  // shared memory: rings [warp][R][slot], partial sums [warp][batch][128], cluster sums [visit][RG][128]
+  const uint32_t smem_base = uint32_t(__cvta_generic_to_shared(smem));
+  const uint32_t ring_base = smem_base + warp * R * V::SLOT_BYTES;
+  float* red_s = reinterpret_cast<float*>(smem + size_t(warps) * R * V::SLOT_BYTES);
+  const uint32_t red_base = smem_base + warps * R * V::SLOT_BYTES;
+  float* acc_s = red_s + size_t(warps) * a.batch * 128;
+
+  // ---- copy side: lane -> (row within a copy, 16-byte column of the row segment) ----
+  const int copy_row = lane / V::LANES_PER_ROW, copy_column = lane % V::LANES_PER_ROW;
+  const int copy_tile = copy_column / V::VECTORS_PER_TILE_ROW, copy_vector = copy_column % V::VECTORS_PER_TILE_ROW;
+  // odd k-tiles of a visit keep rows r and r^1 swapped: the two halves of a 128-byte line then land
+  // in different banks, and a fragment read (rows g, g^1 of one tile) still covers 128 contiguous bytes
+  const uint32_t copy_to = ring_base + copy_tile * V::TILE_BYTES + ((copy_row ^ (copy_tile & 1)) * V::TILE_ROW_BYTES) +
+                           copy_vector * 16;
+  // one 64-bit source per copy of a lane; a visit adds visit * step with one multiply-add (no carries
+  // to propagate on the integer pipe, which the code expansion needs for itself)
+  const uint8_t* copy_base[V::COPIES];
+#pragma unroll
+  for (int i = 0; i < V::COPIES; ++i)
+    copy_base[i] = a.packed + int64_t(first_row_tile * 16 + i * V::ROWS_PER_COPY + copy_row) * a.packed_row_stride +
+                   int64_t(tile0) * V::TILE_ROW_BYTES + copy_column * 16;
+  const uint32_t copy_visit_step = uint32_t(visit_stride) * 16u * uint32_t(a.packed_row_stride);
+  // the scales of a visit ride in its slot: lane r < 16 copies the 4 bytes that hold row r's KT scales
+  // (for KT == 1 the aligned pair around the one scale), so they arrive as early as the weights do
+  const int64_t scale_index = int64_t(first_row_tile * 16 + (lane & 15)) * a.scale_row_stride + tile0;
+  const __half* scale_base = a.scales + (scale_index & ~int64_t(1));
+  const uint32_t scale_visit_step = uint32_t(visit_stride) * 32u * uint32_t(a.scale_row_stride);  // bytes
+  const uint32_t scale_to = ring_base + V::SCALE_OFFSET + (lane & 15) * 4;
+  const bool copies_scales = lane < 16;
+  // `exists`: the warp owns this visit.  `whole` == false: rows past N are left out (their slots keep
+  // stale bytes; the sums of such rows are never stored).
+  auto issue = [&](int visit, int slot, bool exists, bool whole) {
+    if (exists) {
+      const int first_row = whole ? 0 : (first_row_tile + visit * visit_stride) * 16;
+#pragma unroll
+      for (int i = 0; i < V::COPIES; ++i)
+        if (whole || first_row + i * V::ROWS_PER_COPY + copy_row < a.N)
+          copy16(copy_to + slot * V::SLOT_BYTES + i * V::ROWS_PER_COPY * V::TILE_ROW_BYTES,
+                 offset_pointer(copy_base[i], uint32_t(visit), copy_visit_step));
+      if (copies_scales && (whole || first_row + (lane & 15) < a.N))
+        copy4(scale_to + slot * V::SLOT_BYTES, offset_pointer(scale_base, uint32_t(visit), scale_visit_step));
+    }
+    copy_commit();  // one group per visit, empty past the end, so the pending count stays exact
+  };
+#pragma unroll
+  for (int d = 0; d < R - 1; ++d)
+    if (d < a.early) issue(d, d, d < my_visits, d < whole_visits);
+
+  // ---- activations: the B fragments of this warp's k-tiles, permuted in registers ----
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  uint32_t b[KT][4][4];   // [k-tile][word][pairs (x0,x4) (x2,x6) (x1,x5) (x3,x7)]
+  float start[KT][4];     // accumulator start: min * sum(x) * 2^-24 for activation rows 2t, 2t+1 (twice)
+  {
+    const __half* x_lane = a.x + int64_t(g) * a.K + int64_t(tile0) * 128 + t * 32;
+    const bool has_x = my_visits > 0 && g < a.M;
+    uint4 v[KT][4];
+#pragma unroll
+    for (int kk = 0; kk < KT; ++kk)
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        v[kk][w] = make_uint4(0u, 0u, 0u, 0u);
+        if (has_x) v[kk][w] = __ldg(reinterpret_cast<const uint4*>(x_lane + kk * 128 + w * 8));
+      }
+    // the rest of the ring is requested behind the activations, so these are not queued behind it
+#pragma unroll
+    for (int d = 0; d < R - 1; ++d)
+      if (d >= a.early) issue(d, d, d < my_visits, d < whole_visits);
+    const float unit = a.grid_min * 5.9604644775390625e-08f;   // min * 2^-24: the unit of the accumulators
+#pragma unroll
+    for (int kk = 0; kk < KT; ++kk) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        b[kk][w][0] = __byte_perm(v[kk][w].x, v[kk][w].z, 0x5410);
+        b[kk][w][1] = __byte_perm(v[kk][w].y, v[kk][w].w, 0x5410);
+        b[kk][w][2] = __byte_perm(v[kk][w].x, v[kk][w].z, 0x7632);
+        b[kk][w][3] = __byte_perm(v[kk][w].y, v[kk][w].w, 0x7632);
+      }
+      // sum of the k-tile's activations per activation row, on the tensor cores: a weight tile of ones
+      // gives every weight row the same sums, laid out as the accumulators want them
+      constexpr uint32_t ones = 0x3c003c00u;
+      float sums[4];
+      mma_first(sums, ones, ones, ones, ones, b[kk][0][0], b[kk][0][1], 0.f, 0.f, 0.f, 0.f);
+      mma_next(sums, ones, ones, ones, ones, b[kk][0][2], b[kk][0][3]);
+#pragma unroll
+      for (int w = 1; w < 4; ++w) {
+        mma_next(sums, ones, ones, ones, ones, b[kk][w][0], b[kk][w][1]);
+        mma_next(sums, ones, ones, ones, ones, b[kk][w][2], b[kk][w][3]);
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) start[kk][q] = sums[q] * unit;
+    }
+  }
+
+  // ---- fragment side: lane (g, t) reads 16 bytes of rows g and g + 8 of every k-tile ----
+  const uint32_t read_begin = ring_base + g * V::TILE_ROW_BYTES + t * 16;
+  const uint32_t odd_flip = (((g ^ 1) - g) * V::TILE_ROW_BYTES);  // rows g and g^1 are swapped in odd k-tiles
+  // this lane's scales: rows g and g + 8, halves kk of the 4-byte entries (KT == 1: the half the
+  // aligned pair keeps the wanted scale in; it is the same in every visit, the visit step being even)
+  const uint32_t scale_begin = ring_base + V::SCALE_OFFSET + g * 4;
+  const int64_t index_low = int64_t(first_row_tile * 16 + g) * a.scale_row_stride + tile0;
+  const int64_t index_high = index_low + 8 * a.scale_row_stride;
+  const bool high_half_0 = KT == 1 && (index_low & 1), high_half_1 = KT == 1 && (index_high & 1);
+  const uint32_t red_to = red_base + ((warp * a.batch) * 128 + lane * 4) * 4;
+
+  // One round: R visits, unrolled over the ring, so every shared-memory offset is an immediate.  With
+  // CHECKED == false the caller promises that this warp owns every visit of the round and every visit
+  // the round issues copies for, and the body has no branches.
+  auto round = [&](int visit0, uint32_t red_at, auto checked) {
+    constexpr bool CHECKED = decltype(checked)::value;
+#pragma unroll
+    for (int d = 0; d < R; ++d) {
+      const int visit = visit0 + d;
+      __syncwarp();  // every lane has read the slot that the next copies overwrite
+      issue(visit + R - 1, (d + R - 1) % R, !CHECKED || visit + R - 1 < my_visits, !CHECKED || visit + R - 1 < whole_visits);
+      copy_wait<R - 1>();
+      __syncwarp();  // the lanes' copies of this visit are visible to the whole warp
+      float y[4] = {0.f, 0.f, 0.f, 0.f};
+      if (!CHECKED || visit < my_visits) {
+        const uint32_t read_from = read_begin + d * V::SLOT_BYTES, scale_at = scale_begin + d * V::SLOT_BYTES;
+        const uint32_t scale_bits_0 = load_shared4(scale_at), scale_bits_1 = load_shared4(scale_at + 32);
+        const __half2 s0 = *reinterpret_cast<const __half2*>(&scale_bits_0);
+        const __half2 s1 = *reinterpret_cast<const __half2*>(&scale_bits_1);
+#pragma unroll
+        for (int kk = 0; kk < KT; ++kk) {
+          const uint32_t tile = read_from + kk * V::TILE_BYTES + ((kk & 1) ? odd_flip : 0u);
+          const uint4 lo = load_shared16(tile), hi = load_shared16(tile + 8 * V::TILE_ROW_BYTES);
+          const uint32_t q[4] = {lo.x, lo.y, lo.z, lo.w}, p[4] = {hi.x, hi.y, hi.z, hi.w};
+          float even[4], odd[4];
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const uint32_t q8 = q[w] >> 8, p8 = p[w] >> 8;  // codes 2, 3, 6, 7 of a word move down one byte
+            if (w == 0) {
+              mma_first(even, q[w] & 0x000f000fu, p[w] & 0x000f000fu, q8 & 0x000f000fu, p8 & 0x000f000fu,
+                        b[kk][w][0], b[kk][w][1], start[kk][0], start[kk][1], start[kk][2], start[kk][3]);
+              mma_first(odd, q[w] & 0x00f000f0u, p[w] & 0x00f000f0u, q8 & 0x00f000f0u, p8 & 0x00f000f0u,
+                        b[kk][w][2], b[kk][w][3], 0.f, 0.f, 0.f, 0.f);
+            } else {
+              mma_next(even, q[w] & 0x000f000fu, p[w] & 0x000f000fu, q8 & 0x000f000fu, p8 & 0x000f000fu,
+                       b[kk][w][0], b[kk][w][1]);
+              mma_next(odd, q[w] & 0x00f000f0u, p[w] & 0x00f000f0u, q8 & 0x00f000f0u, p8 & 0x00f000f0u,
+                       b[kk][w][2], b[kk][w][3]);
+            }
+          }
+          // odd codes were c * 2^-20, 16 times the unit: recombine exactly, then one scale per row and k-tile
+          const float f0 = (KT == 1 ? high_half_0 : (kk & 1)) ? __high2float(s0) : __low2float(s0);
+          const float f1 = (KT == 1 ? high_half_1 : (kk & 1)) ? __high2float(s1) : __low2float(s1);
+          y[0] = fmaf(f0, fmaf(odd[0], 0.0625f, even[0]), y[0]);
+          y[1] = fmaf(f0, fmaf(odd[1], 0.0625f, even[1]), y[1]);
+          y[2] = fmaf(f1, fmaf(odd[2], 0.0625f, even[2]), y[2]);
+          y[3] = fmaf(f1, fmaf(odd[3], 0.0625f, even[3]), y[3]);
+        }
+      }
+      store_shared16(red_at + d * 512, y[0], y[1], y[2], y[3]);
+    }
+  };
+
+  int batch_first = 0;   // first visit of the batch whose sums shared memory holds
+  for (int visit0 = 0; visit0 < a.visits; visit0 += R) {
+    const uint32_t red_at = red_to + (visit0 - batch_first) * 512;
+    if (visit0 + 2 * R - 2 < whole_visits) round(visit0, red_at, std::false_type{});
+    else round(visit0, red_at, std::true_type{});
+    if (visit0 + R - batch_first < a.batch && visit0 + R < a.visits) continue;
+
+    // ---- end of a batch: add the warps' partial sums in warp order, four outputs per thread ----
+    __syncthreads();
+    const int in_batch = min(a.batch, a.visits - batch_first);
+    const int quads = in_batch * a.RG * 32;
+    for (int o = threadIdx.x; o < quads; o += blockDim.x) {
+      const int source_lane = o & 31, group_index = o >> 5;
+      const int d = (group_index * a.rg_inverse) >> 16, rgi = group_index - d * a.RG;   // / RG, % RG
+      const float4* partial = reinterpret_cast<const float4*>(red_s) + (size_t(rgi) * a.KW * a.batch + d) * 32 + source_lane;
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+      for (int w = 0; w < a.KW; ++w) {
+        const float4 v = partial[w * a.batch * 32];
+        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+      }
+      const int v = batch_first + d;
+      if (a.slabs > 1) {
+        reinterpret_cast<float4*>(acc_s)[(size_t(v) * a.RG + rgi) * 32 + source_lane] = sum;
+      } else {
+        // the lane that produced this quad held weight rows g, g + 8 and activation rows 2t, 2t + 1
+        const int rt = int(blockIdx.x) * a.RG + rgi + v * visit_stride;
+        const int row = rt * 16 + (source_lane >> 2), m = (source_lane & 3) * 2;
+        if (rt < a.row_tiles) {
+          const float out[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int mq = m + (q & 1), rq = row + (q & 2) * 4;
+            if (mq < a.M && rq < a.N) {
+              float value = out[q] * 16777216.f;  // 2^24
+              if (a.bias != nullptr) value += __half2float(a.bias[rq]);
+              a.y[int64_t(mq) * a.N + rq] = __float2half_rn(value);
+            }
+          }
+        }
+      }
+    }
+    batch_first = visit0 + R;
+    if (batch_first < a.visits) __syncthreads();   // the next batch overwrites the sums
+  }
+  copy_wait<0>();
+
+  // ---- K split over the cluster: one exchange through distributed shared memory, slab order ----
+  if (a.slabs > 1) {
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();
+    const int outputs = a.visits * a.RG * 128;
+    for (int o = slab * int(blockDim.x) + threadIdx.x; o < outputs; o += a.slabs * int(blockDim.x)) {
+      float sum = 0.f;
+      for (int peer = 0; peer < a.slabs; ++peer) sum += cluster.map_shared_rank(acc_s, peer)[o];
+      const int e = o & 127, group_index = o >> 7;
+      const int v = group_index / a.RG, rgi = group_index - v * a.RG;
+      const int rt = int(blockIdx.x) * a.RG + rgi + v * visit_stride;
+      const int row = rt * 16 + (e >> 4) + ((e & 2) ? 8 : 0), m = ((e >> 2) & 3) * 2 + (e & 1);
+      if (rt < a.row_tiles && row < a.N && m < a.M) {
+        sum *= 16777216.f;
+        if (a.bias != nullptr) sum += __half2float(a.bias[row]);
+        a.y[int64_t(m) * a.N + row] = __float2half_rn(sum);
+      }
+    }
+    cluster.sync();  // no CTA leaves while a peer may still read its sums
+  }
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+template <typename Kernel>
+int opt_in_shared(Kernel kernel) {
+  static std::mutex lock;
+  static std::map<std::pair<const void*, int>, bool> done;
+  int device = 0;
+  cudaGetDevice(&device);
+  const auto key = std::make_pair(reinterpret_cast<const void*>(kernel), device);
+  std::lock_guard<std::mutex> guard(lock);
+  if (done.count(key)) return MKB_OK;
+  cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            device_info().max_smem_optin);
+  if (status != cudaSuccess) return cuda_fail(status, "gemv_stream: shared memory opt-in");
+  status = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+  if (status != cudaSuccess) return cuda_fail(status, "gemv_stream: cluster size opt-in");
+  done[key] = true;
+  return MKB_OK;
+}
+
+struct StreamPlan {
+  int KT, KW, RG, slabs, columns, visits, depth, batch, per_sm;
+  size_t smem;
+};
+
+// Chooses the decomposition: slabs of K (CTAs of a cluster), warps along K and row tiles per visit of a
+// CTA, CTAs per SM (small CTAs share an SM), ring depth (= visits per round).
+// `cluster_cap` > 0 bounds the number of clusters in flight.
+bool plan_stream(int M, int N, int K, int sm_count, int max_smem, int cluster_cap, StreamPlan& p) {
+  (void)M;
+  const int k_tiles = K / 128;
+  const int KT = k_tiles % 2 == 0 ? 2 : 1;
+  const int k_warps = k_tiles / KT;
+  const int row_tiles = (N + 15) / 16;
+  const size_t slot = size_t(KT) * 1024 + 64;
+  // fewest slabs that give every warp of a 16-warp CTA one share of K; a layer with fewer row tiles
+  // than SMs is cut further along K, in even shares, while a CTA keeps at least four warps
+  int slabs = (k_warps + kMaxWarps - 1) / kMaxWarps;
+  while (slabs < 8 && row_tiles * slabs < sm_count) {
+    int next = slabs + 1;
+    while (next <= 8 && k_warps % next != 0) ++next;
+    if (next > 8 || k_warps / next < 4) break;
+    slabs = next;
+  }
+  if (slabs > 8) return false;
+  const int KW = (k_warps + slabs - 1) / slabs;
+  int RG = kMaxWarps / KW;
+  while (RG > 1 && (row_tiles + RG - 1) / RG * slabs < sm_count) --RG;  // keep every SM busy first
+  const int warps = KW * RG;
+  const int per_sm = kMaxWarps / warps;
+  int clusters = sm_count * per_sm / slabs;
+  if (cluster_cap > 0 && clusters > cluster_cap) clusters = cluster_cap;  // what the GPU can co-schedule
+  if (clusters < 1) return false;
+  const int items = (row_tiles + RG - 1) / RG;
+  const int columns = items < clusters ? items : clusters;
+  const int visits = (items + columns - 1) / columns;
+  if (slabs > 1 && visits > kMaxClusterVisits) return false;
+  int depth = visits < 2 ? 2 : visits > 3 ? 3 : visits;
+  const size_t budget = (size_t(max_smem) + 1024) / per_sm - 1024;  // every resident CTA reserves 1 KB
+  const size_t sums = slabs > 1 ? size_t(visits) * RG * 512 : 0;
+  while (depth > 2 && size_t(depth) * warps * (slot + 512) + sums > budget) --depth;
+  if (size_t(depth) * warps * (slot + 512) + sums > budget) return false;
+  // partial sums of as many visits as fit (whole rounds), ideally all: one reduction at the end
+  const int rounds = (visits + depth - 1) / depth;
+  int batch_rounds = int((budget - sums - size_t(depth) * warps * slot) / (size_t(depth) * warps * 512));
+  if (batch_rounds > rounds) batch_rounds = rounds;
+  const int batch = batch_rounds * depth;
+  p.KT = KT; p.KW = KW; p.RG = RG; p.slabs = slabs; p.columns = columns; p.visits = visits;
+  p.depth = depth; p.batch = batch; p.per_sm = per_sm;
+  p.smem = size_t(depth) * warps * slot + size_t(batch) * warps * 512 + sums;
+  return true;
+}
+
+template <int KT, int R>
+int launch_stream(const StreamArgs& a, const StreamPlan& p, cudaStream_t stream, int* cluster_cap) {
+  auto kernel = gemv_stream_kernel<4, KT, R>;
+  int status = opt_in_shared(kernel);
+  if (status != MKB_OK) return status;
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(p.columns, p.slabs, 1);
+  config.blockDim = dim3(p.KW * p.RG * 32, 1, 1);
+  config.dynamicSmemBytes = p.smem;
+  config.stream = stream;
+  // Programmatic dependent launch: CTAs may start while the previous kernel of the stream drains; they
+  // copy weights (constants) at once and execute griddepcontrol.wait before they read activations.
+  cudaLaunchAttribute attribute[2];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  if (p.slabs > 1) {
+    attribute[1].id = cudaLaunchAttributeClusterDimension;
+    attribute[1].val.clusterDim.x = 1;
+    attribute[1].val.clusterDim.y = p.slabs;
+    attribute[1].val.clusterDim.z = 1;
+    config.numAttrs = 2;
+  }
+  if (cluster_cap != nullptr) {
+    // how many clusters of this shape the GPU holds at once (cached): a grid beyond it runs in waves
+    static std::mutex lock;
+    static std::map<std::tuple<const void*, int, size_t, int, int>, int> known;
+    int device = 0;
+    cudaGetDevice(&device);
+    const auto key = std::make_tuple(reinterpret_cast<const void*>(kernel), int(config.blockDim.x), p.smem, p.slabs, device);
+    std::lock_guard<std::mutex> guard(lock);
+    auto found = known.find(key);
+    if (found == known.end()) {
+      int clusters = 0;
+      config.gridDim = dim3(1024, p.slabs, 1);
+      const cudaError_t asked = cudaOccupancyMaxActiveClusters(&clusters, kernel, &config);
+      if (asked != cudaSuccess) return cuda_fail(asked, "gemv_stream: cluster occupancy query");
+      found = known.emplace(key, clusters).first;
+    }
+    *cluster_cap = found->second;
+    return MKB_OK;
+  }
+  const cudaError_t launched = cudaLaunchKernelEx(&config, kernel, a);
+  if (launched != cudaSuccess) return cuda_fail(launched, "gemv_stream launch");
+  return MKB_OK;
+}
+
+int dispatch_stream(const StreamArgs& a, const StreamPlan& p, cudaStream_t stream, int* cluster_cap) {
+  if (p.KT == 2) {
+    switch (p.depth) {
+      case 2: return launch_stream<2, 2>(a, p, stream, cluster_cap);
+      default: return launch_stream<2, 3>(a, p, stream, cluster_cap);
+    }
+  }
+  switch (p.depth) {
+    case 2: return launch_stream<1, 2>(a, p, stream, cluster_cap);
+    default: return launch_stream<1, 3>(a, p, stream, cluster_cap);
+  }
+}
+
+
+}  // namespace
+
+int gemv_stream_supported(int M, int N, int K, int group, int bits, int x_dtype, int scale_dtype, const void* x,
+                          const uint8_t* packed, const void* scales, int64_t packed_row_stride,
+                          int64_t scale_row_stride, const void* zeros, int integer_grid, float grid_minimum) {
+  if (x_dtype != MKB_F16 || scale_dtype != MKB_F16 || zeros != nullptr || !integer_grid) return 0;
+  if (bits != 4 || group != 128 || M < 1 || M > 8 || N < 1 || K < 128 || K % 128 != 0) return 0;
+  if (grid_minimum != float(int(grid_minimum)) || grid_minimum < -512.f || grid_minimum > 512.f) return 0;
+  if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(packed) % 16 || packed_row_stride % 16) return 0;
+  if (reinterpret_cast<uintptr_t>(scales) % 4 || ((K / 128) % 2 == 0 && scale_row_stride % 2)) return 0;
+  if ((K / 128) % 2 == 1 && (int64_t(N) * scale_row_stride) % 2) return 0;  // scales are copied in aligned pairs
+  if (int64_t(N) * packed_row_stride >= (int64_t(1) << 32) || int64_t(N) * scale_row_stride >= (int64_t(1) << 30)) return 0;
+  StreamPlan plan;
+  const DeviceInfo& info = device_info();
+  return plan_stream(M, N, K, info.sm_count, info.max_smem_optin, 0, plan) ? 1 : 0;
+}
+
+int launch_gemv_stream(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y, int M,
+                       int N, int K, int64_t packed_row_stride, int64_t scale_row_stride, float grid_minimum,
+                       cudaStream_t stream) {
+  const DeviceInfo& info = device_info();
+  StreamPlan p;
+  MKB_REQUIRE(plan_stream(M, N, K, info.sm_count, info.max_smem_optin, 0, p), MKB_E_UNSUPPORTED,
+              "gemv_stream: no decomposition for N=%d K=%d", N, K);
+  StreamArgs a{};
+  if (p.slabs > 1) {  // a grid of clusters must be resident as a whole, or it runs in waves
+    int cap = 0;
+    const int status = dispatch_stream(a, p, stream, &cap);
+    if (status != MKB_OK) return status;
+    MKB_REQUIRE(cap >= 1, MKB_E_UNSUPPORTED, "gemv_stream: no cluster of %d CTAs fits the GPU", p.slabs);
+    if (p.columns > cap)
+      MKB_REQUIRE(plan_stream(M, N, K, info.sm_count, info.max_smem_optin, cap, p),
+                  MKB_E_UNSUPPORTED, "gemv_stream: no decomposition for N=%d K=%d in %d clusters", N, K, cap);
+  }
+  a.x = static_cast<const __half*>(x); a.packed = packed; a.scales = static_cast<const __half*>(scales);
+  a.bias = static_cast<const __half*>(bias); a.y = static_cast<__half*>(y);
+  a.M = M; a.N = N; a.K = K; a.packed_row_stride = packed_row_stride; a.scale_row_stride = scale_row_stride;
+  a.row_tiles = (N + 15) / 16; a.k_warps = K / (128 * p.KT); a.KW = p.KW; a.RG = p.RG; a.slabs = p.slabs;
+  a.visits = p.visits; a.grid_min = grid_minimum; a.batch = p.batch; a.early = 1;
+  a.kw_inverse = (65536 + p.KW - 1) / p.KW; a.rg_inverse = (65536 + p.RG - 1) / p.RG;
+  return dispatch_stream(a, p, stream, nullptr);
+}
+
+}  // namespace mkb

@@ -13,7 +13,7 @@ from mlkit_b200 import _native
 
 DTYPE_TAGS = {torch.float16: _native.F16, torch.bfloat16: _native.BF16, torch.float32: _native.F32}
 KERNEL_CHOICES = {"auto": _native.GEMV_AUTO, "scalar": _native.GEMV_SCALAR, "tiled": _native.GEMV_TILED,
-                  "tmem": _native.GEMV_TMEM, "bulk": _native.GEMV_BULK}
+                  "tmem": _native.GEMV_TMEM, "bulk": _native.GEMV_BULK, "stream": _native.GEMV_STREAM}
 
 _workspaces: dict[tuple[int, int], Tensor] = {}
 

@@ -127,7 +127,7 @@ def test_matvec_matches_golden_vectors(golden_meta, golden_codecs):
 
 
 @pytest.mark.parametrize("rows_in", [1, 2, 3, 4, 5, 7, 8])
-@pytest.mark.parametrize("kernel", ["scalar", "tiled", "tmem", "bulk"])
+@pytest.mark.parametrize("kernel", ["scalar", "tiled", "tmem", "bulk", "stream"])
 def test_matvec_int4_g128_every_row_count(rows_in, kernel):
     layer = helpers.make_layer(1000, 1024, 4, 128, seed=3)   # 1000 rows: a ragged last row tile
     x = helpers.activations(rows_in, 1024, seed=rows_in)
@@ -213,6 +213,34 @@ def test_matvec_bulk_groups_bias_ragged_rows_and_splits(group, width):
         assert np.array_equal(first, run_matvec(layer, x, "bulk", bias))   # fixed summation order
 
 
+STREAM_SHAPES = [(300, 1536), (4864, 896), (272, 768), (1000, 1024), (48, 14336), (2368, 8192), (16, 128), (10, 384),
+                 (8192, 1024), (8192, 3584), (1280, 8192), (7168, 8192)]
+
+
+@pytest.mark.parametrize("rows,width", STREAM_SHAPES)
+def test_matvec_stream_shapes_bias_ragged_rows_and_splits(rows, width):
+    """The streaming kernel: one and two k-tiles per warp (odd and even K / 128), K split over one to
+    eight CTAs of a cluster, several row tiles per visit, a partial last row tile, a bias; the
+    tensor-parallel shard shapes of the 70B-shaped decoder are among them."""
+    layer = helpers.make_layer(rows, width, 4, 128, seed=rows + width)
+    bias = (np.random.default_rng(2).standard_normal(rows) * 0.1).astype(np.float16)
+    for rows_in in (1, 3, 8):
+        x = helpers.activations(rows_in, width, seed=rows_in, outliers=True)
+        expected = oracle_matvec(layer, x, bias)
+        first = run_matvec(layer, x, "stream", bias)
+        assert matvec.relative_l2(first, expected) < TOLERANCE
+        assert np.array_equal(first, run_matvec(layer, x, "stream", bias))   # fixed summation order
+
+
+def test_matvec_stream_refuses_what_it_does_not_cover():
+    layer = helpers.make_layer(64, 512, 4, 64, seed=1)    # groups narrower than 128 codes
+    with pytest.raises(ValueError, match="streaming kernel"):
+        run_matvec(layer, helpers.activations(1, 512), "stream")
+    layer = helpers.make_layer(64, 512, 8, 128, seed=1)   # 8-bit codes
+    with pytest.raises(ValueError, match="streaming kernel"):
+        run_matvec(layer, helpers.activations(1, 512), "stream")
+
+
 def test_matvec_bulk_refuses_what_it_does_not_cover():
     layer = helpers.make_layer(64, 640, 4, 128, seed=1)   # 640 codes: not a whole number of 256-code chunks
     with pytest.raises(ValueError, match="TMA-fed kernel"):
@@ -267,6 +295,9 @@ def test_matvec_llama8b_shapes_full_size(name):
         through_tmem = run_matvec(layer, x, "tmem")   # the tcgen05 kernel on the same inputs
         assert matvec.relative_l2(through_tmem, expected) < TOLERANCE
         assert np.array_equal(through_tmem, run_matvec(layer, x, "tmem"))
+        through_stream = run_matvec(layer, x, "stream")   # the streaming kernel (what "auto" takes here)
+        assert matvec.relative_l2(through_stream, expected) < TOLERANCE
+        assert np.array_equal(through_stream, run_matvec(layer, x, "stream"))
         through_bulk = run_matvec(layer, x, "bulk")   # the TMA-fed kernel on the same inputs
         assert matvec.relative_l2(through_bulk, expected) < TOLERANCE
         assert np.array_equal(through_bulk, run_matvec(layer, x, "bulk"))
