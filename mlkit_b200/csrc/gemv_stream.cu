@@ -401,15 +401,9 @@ bool plan_stream(int M, int N, int K, int sm_count, int max_smem, int cluster_ca
   const int k_warps = k_tiles / KT;
   const int row_tiles = (N + 15) / 16;
   const size_t slot = size_t(KT) * 1024 + 64;
-  // fewest slabs that give every warp of a 16-warp CTA one share of K; a layer with fewer row tiles
-  // than SMs is cut further along K, in even shares, while a CTA keeps at least four warps
-  int slabs = (k_warps + kMaxWarps - 1) / kMaxWarps;
-  while (slabs < 8 && row_tiles * slabs < sm_count) {
-    int next = slabs + 1;
-    while (next <= 8 && k_warps % next != 0) ++next;
-    if (next > 8 || k_warps / next < 4) break;
-    slabs = next;
-  }
+  // fewest slabs that give every warp of a 16-warp CTA one share of K.  The choice depends on K alone,
+  // so a layer and the same rows inside a wider (concatenated) layer are summed in the same order.
+  const int slabs = (k_warps + kMaxWarps - 1) / kMaxWarps;
   if (slabs > 8) return false;
   const int KW = (k_warps + slabs - 1) / slabs;
   int RG = kMaxWarps / KW;

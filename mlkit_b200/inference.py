@@ -151,11 +151,14 @@ class PackedLinear(nn.Module):
         self.layout = layout_for(self.code_bits, self.in_features, self.group)
         self.maximum_fused_rows = 0 if self.layout is None else MAXIMUM_FUSED_ROWS
         self._plans: dict[torch.dtype, kernels.MatvecPlan] = {}
+        self._siblings: SiblingLaunch | None = None
         preserve_input_processing(original, self)
 
     def _apply(self, fn: Callable[[Tensor], Tensor], recurse: bool = True) -> "PackedLinear":
         self._dense_weight = None
         self._plans = {}  # bound device pointers are stale once buffers move or change dtype
+        if self._siblings is not None:
+            self._siblings.dissolve()  # the members' buffers stop being views of one allocation
         return super()._apply(fn, recurse)
 
     def __deepcopy__(self, memo: dict) -> "PackedLinear":
@@ -163,7 +166,12 @@ class PackedLinear(nn.Module):
         duplicate = self.__class__.__new__(self.__class__)
         memo[id(self)] = duplicate
         for key, value in self.__dict__.items():
-            duplicate.__dict__[key] = {} if key == "_plans" else copy.deepcopy(value, memo)
+            if key == "_plans":
+                duplicate.__dict__[key] = {}
+            elif key == "_siblings":
+                duplicate.__dict__[key] = None  # a copy launches on its own until it is grouped again
+            else:
+                duplicate.__dict__[key] = copy.deepcopy(value, memo)
         return duplicate
 
     def _plan(self, dtype: torch.dtype) -> "kernels.MatvecPlan":
@@ -211,12 +219,122 @@ class PackedLinear(nn.Module):
         else:
             if inputs.dtype not in kernels.DTYPE_TAGS:
                 raise ValueError(f"activation dtype {inputs.dtype} is not supported (fp16, bf16, fp32)")
-            out = self._plan(inputs.dtype)(flat, inputs.new_empty((rows, self.out_features)))
+            siblings = self._siblings
+            if siblings is not None and flat.data_ptr() == inputs.data_ptr():
+                out = siblings.output_of(self, flat)
+            else:
+                out = self._plan(inputs.dtype)(flat, inputs.new_empty((rows, self.out_features)))
         return out.view(inputs.shape[:-1] + (self.out_features,))
 
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, bits={self.code_bits}, "
                 f"group={self.group}, fused={'yes' if self.layout is not None else 'no'}")
+
+
+class SiblingLaunch:
+    """One packed matvec for linears that read the same input (q | k | v, gate | up).
+
+    The reference launches one kernel per ``PackedLinear``
+    (``src/mlkit/inference/packed_linear.py:145-179``); a decode step of a Llama block is then seven
+    launches of which four stream less than a launch costs.  Here the members' ``packed``, ``scales``
+    (and ``zeros``, ``bias``) buffers become views of one allocation each, concatenated along the
+    output rows, so checkpoints and state dicts are unchanged while one launch computes every member.
+    The first member that is called with an input runs the launch; the others return their columns of
+    that result when they are called with the same tensor (same storage, same version) and have not
+    taken it yet.  The launch keeps a reference to its input, so a new tensor cannot reuse the address.
+    Rows of the weight are independent, so every output equals the member's own launch bit for bit.
+    """
+
+    def __init__(self, members: list["PackedLinear"]) -> None:
+        first = members[0]
+        self.members = list(members)
+        self.offsets = [0]
+        for member in members:
+            self.offsets.append(self.offsets[-1] + member.out_features)
+        self.total = self.offsets[-1]
+        self.packed = torch.cat([member.packed for member in members])
+        self.scales = torch.cat([member.scales for member in members])
+        self.zeros = None if first.zeros is None else torch.cat([member.zeros for member in members])
+        self.bias = None if first.bias is None else torch.cat([member.bias for member in members])
+        row_bytes = first.in_features * first.code_bits // 8
+        for index, member in enumerate(members):
+            low, high = self.offsets[index], self.offsets[index + 1]
+            member.packed = self.packed[low * row_bytes:high * row_bytes]
+            member.scales = self.scales[low:high]
+            if self.zeros is not None:
+                member.zeros = self.zeros[low:high]
+            if self.bias is not None:
+                member.bias = self.bias[low:high]
+            member._plans = {}
+            member._siblings = self
+        self._plans: dict[torch.dtype, kernels.MatvecPlan] = {}
+        self._input: Tensor | None = None
+        self._version = -1
+        self._output: Tensor | None = None
+        self._taken: set[int] = set()
+
+    @staticmethod
+    def compatible(members: list["PackedLinear"]) -> bool:
+        first = members[0]
+        if len(members) < 2 or any(member._siblings is not None for member in members):
+            return False
+        for member in members:
+            if (member.layout is None or member.in_features != first.in_features or member.group != first.group
+                    or member.code_bits != first.code_bits or member.scales.dtype != first.scales.dtype
+                    or member.packed.device != first.packed.device or (member.zeros is None) != (first.zeros is None)
+                    or (member.bias is None) != (first.bias is None) or member.scales.dim() != 2
+                    or member.scales.shape[1] != first.scales.shape[1] or member._forward_pre_hooks
+                    or (member.bias is not None and member.bias.dtype != first.bias.dtype)
+                    or not torch.equal(member.values, first.values)):
+                return False
+        return True
+
+    def dissolve(self) -> None:
+        for member in self.members:
+            member._siblings = None
+        self._input = self._output = None
+
+    def plan(self, dtype: torch.dtype) -> "kernels.MatvecPlan":
+        """The bound launch of the whole group: ``plan(x, out)`` with ``out`` of ``[rows, total]``."""
+        plan = self._plans.get(dtype)
+        if plan is None:
+            first = self.members[0]
+            plan = self._plans[dtype] = kernels.MatvecPlan(
+                self.packed, self.scales, first.values, self.zeros, self.bias, outputs=self.total,
+                width=first.in_features, group=first.group, bits=first.code_bits, dtype=dtype,
+                integer_grid=first.integer_grid, grid_minimum=first.grid_minimum)
+        return plan
+
+    def output_of(self, member: "PackedLinear", flat: Tensor) -> Tensor:
+        index = self.members.index(member)
+        current = self._input
+        version = 0 if flat.is_inference() else flat._version  # inference tensors carry no version counter
+        if (current is None or index in self._taken or current.data_ptr() != flat.data_ptr()
+                or current.shape != flat.shape or current.dtype != flat.dtype or self._version != version):
+            self._output = self.plan(flat.dtype)(flat, flat.new_empty((flat.shape[0], self.total)))
+            self._input, self._version = flat, version
+            self._taken = set()
+        self._taken.add(index)
+        if len(self._taken) == len(self.members):
+            self._input = None  # everybody has its columns: let the activation go
+        return self._output[:, self.offsets[index]:self.offsets[index + 1]]
+
+
+SIBLING_NAMES = (("q_proj", "k_proj", "v_proj"), ("gate_proj", "up_proj"))
+
+
+def fuse_siblings(module: nn.Module, names: tuple[tuple[str, ...], ...] = SIBLING_NAMES) -> int:
+    """Group ``PackedLinear`` children that read the same input into one launch each.  ``names`` lists
+    the attribute names of such siblings under a common parent (the Llama naming by default); groups
+    whose members differ in codec, width or input hooks are left alone.  Returns the number of groups."""
+    groups = 0
+    for parent in module.modules():
+        for group in names:
+            members = [getattr(parent, name, None) for name in group]
+            if all(isinstance(member, PackedLinear) for member in members) and SiblingLaunch.compatible(members):
+                SiblingLaunch(members)
+                groups += 1
+    return groups
 
 
 class PackedEmbedding(nn.Module):
@@ -248,9 +366,11 @@ class PackedEmbedding(nn.Module):
 
 
 def optimize(model: Model | nn.Module, backend: str = "auto", *, compile: bool = False,
-             mode: str = "reduce-overhead", cache_dense: bool = False, inplace: bool = False) -> Model:
+             mode: str = "reduce-overhead", cache_dense: bool = False, inplace: bool = False,
+             siblings: tuple[tuple[str, ...], ...] | None = SIBLING_NAMES) -> Model:
     """Choose dense or packed execution; packed swaps every compatible ``nn.Linear`` of a ``QModel``
-    for a ``PackedLinear`` and a tied embedding for a ``PackedEmbedding``."""
+    for a ``PackedLinear`` and a tied embedding for a ``PackedEmbedding``.  ``siblings`` names linears
+    under one parent that read the same input; each such group runs as one launch (``None``: never)."""
     if backend not in {"auto", "dense", "packed"}:
         raise ValueError("backend must be auto, dense, or packed")
     wrapped = model if isinstance(model, Model) else Model(model)
@@ -288,6 +408,8 @@ def optimize(model: Model | nn.Module, backend: str = "auto", *, compile: bool =
                 if isinstance(module, PackedLinear):
                     module._forward_pre_hooks = copy.deepcopy(module._forward_pre_hooks, memo)
         converted.execution_backend = f"packed:{count}"
+        if siblings and not compile:
+            fuse_siblings(converted.module, siblings)
     else:
         converted = wrapped if inplace else copy.deepcopy(wrapped)
         converted.execution_backend = "dense"

@@ -289,3 +289,58 @@ def test_benchmark_protocol():
     assert result.median_ms > 0 and result.repetitions == 3 and result.minimum_ms <= result.percentile_95_ms
     assert set(result.to_dict()) == {"median_ms", "minimum_ms", "percentile_95_ms", "repetitions", "device",
                                      "peak_memory_bytes"}
+
+
+class LlamaishBlock(nn.Module):
+    """The seven linears of a Llama block under the names the sibling grouping looks for."""
+
+    def __init__(self, hidden=512, kv=128, mlp=1024):
+        super().__init__()
+        self.q_proj = nn.Linear(hidden, hidden, bias=False, dtype=torch.float16)
+        self.k_proj = nn.Linear(hidden, kv, bias=False, dtype=torch.float16)
+        self.v_proj = nn.Linear(hidden, kv, bias=False, dtype=torch.float16)
+        self.o_proj = nn.Linear(hidden, hidden, bias=False, dtype=torch.float16)
+        self.gate_proj = nn.Linear(hidden, mlp, bias=False, dtype=torch.float16)
+        self.up_proj = nn.Linear(hidden, mlp, bias=False, dtype=torch.float16)
+        self.down_proj = nn.Linear(mlp, hidden, bias=False, dtype=torch.float16)
+
+    def forward(self, x):
+        q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
+        attended = self.o_proj(q * torch.sigmoid(k.mean(-1, keepdim=True)) + v.mean(-1, keepdim=True))
+        return self.down_proj(nn.functional.silu(self.gate_proj(attended)) * self.up_proj(attended))
+
+
+@pytest.mark.parametrize("rows", [1, 8])
+def test_sibling_projections_share_one_launch_bit_for_bit(rows):
+    converted = mk.quantize(LlamaishBlock(), mk.int(4, group=128), calib=None)
+    fused = mk.optimize(converted, backend="packed")
+    separate = mk.optimize(converted, backend="packed", siblings=None)
+    block = fused.module
+    assert block.q_proj._siblings is block.k_proj._siblings is block.v_proj._siblings is not None
+    assert block.gate_proj._siblings is block.up_proj._siblings is not None
+    assert block.o_proj._siblings is None and separate.module.q_proj._siblings is None
+    # the members' buffers are views of one allocation, so checkpoints and state dicts are unchanged
+    assert block.k_proj.packed.data_ptr() == block.q_proj.packed.data_ptr() + block.q_proj.packed.numel()
+    assert torch.equal(block.v_proj.packed, separate.module.v_proj.packed)
+    x = torch.randn(rows, 512, dtype=torch.float16)
+    with torch.inference_mode():
+        for name in ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj"):
+            assert torch.equal(getattr(block, name)(x), getattr(separate.module, name)(x)), name
+        assert torch.equal(fused(x), separate(x))
+        torch.testing.assert_close(fused(x), converted(x), rtol=0.01, atol=0.01)
+    # one launch serves each member once: a second call of the same member, a changed input and a new
+    # tensor all start a new launch and see the new values
+    y = torch.randn(rows, 512, dtype=torch.float16)
+    first = block.q_proj(y).clone()
+    assert torch.equal(block.q_proj(y), first)
+    assert torch.equal(block.k_proj(y), separate.module.k_proj(y))
+    y.mul_(2)
+    assert torch.equal(block.v_proj(y), separate.module.v_proj(y))
+    assert torch.equal(block.k_proj(y), separate.module.k_proj(y))
+    # rows beyond the fused limit take the dense route per member, as before
+    many = torch.randn(9, 512, dtype=torch.float16)
+    torch.testing.assert_close(block.k_proj(many), separate.module.k_proj(many))
+    # moving a member dissolves the group; every member then launches alone
+    block.q_proj.half()
+    assert block.k_proj._siblings is None
+    assert torch.equal(block.k_proj(x), separate.module.k_proj(x))
