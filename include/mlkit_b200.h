@@ -128,12 +128,20 @@ int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* scales, const 
  *     before any stream capture begins.
  *   - All calls on a device share the one array.  Calls that may overlap on the GPU (different
  *     streams, or two threads) race on it; order them on one stream.
+ *   - The 8 MiB become resident when the first call loads the library's tensor-memory kernel module
+ *     (CUDA loads modules lazily); that call also sets the kernel's shared-memory attribute and
+ *     queries its occupancy.  A host that has committed all device memory must make it before.
+ *   - mkb_gemv_static_status reads, and clears, the status word of the built-in scratch: non-zero
+ *     when a bounded wait inside one of the calls since the last reading expired (the results of that
+ *     call are not valid).  It synchronises with the device: call it outside stream captures.  It has
+ *     no counterpart in the reference either.
  */
 int64_t mkb_gemv_static_scratch_bytes(void);
 int mkb_gemv_static(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y,
                     int M, int N, int K, int group,
                     int64_t packed_row_stride, int64_t scale_row_stride,
                     float grid_minimum, void* stream);
+int mkb_gemv_static_status(int* status);
 
 /*
  * Unpack and dequantise a packed weight:
@@ -214,6 +222,12 @@ int mkb_rope_attention_decode(const void* qkv, const int* positions, void* k_cac
                               int M, int q_heads, int kv_heads, int head_dim, int capacity, float theta,
                               float scale, void* stream);
 int mkb_silu_mul(const void* gate_up, void* out, int M, int I, void* stream);
+/* positions[m] must lie in [0, capacity).  The kernels above never turn a position outside that range
+ * into an address: they clamp it, leave the caches untouched and raise a device-wide status word.
+ * mkb_decode_status reads and clears that word (non-zero: some launch since the last reading saw such
+ * a position and its results are not valid).  It synchronises with the device: call it outside
+ * stream captures. */
+int mkb_decode_status(int* status);
 
 /*
  * One-shot all-reduce over peer memory for the row-parallel linears (o, down) of the tensor-parallel

@@ -25,6 +25,7 @@ SIGNATURES = {
                             c_void_p]),
     "mkb_gemv_static_scratch_bytes": (c_int64, []),
     "mkb_gemv_static": (c_int, [c_void_p] * 5 + [c_int] * 4 + [c_int64, c_int64, c_float, c_void_p]),
+    "mkb_gemv_static_status": (c_int, [c_void_p]),
     "mkb_dequant": (c_int, [c_void_p] * 6 + [c_int64, c_int64] + [c_int] * 5 + [c_int64, c_void_p]),
     "mkb_dequant_rows": (c_int, [c_void_p] * 6 + [c_int64] * 3 + [c_int] * 5 + [c_int64, c_void_p]),
     "mkb_hadamard": (c_int, [c_void_p] * 4 + [c_int64] + [c_int] * 6 + [c_void_p]),
@@ -32,6 +33,7 @@ SIGNATURES = {
     "mkb_rope_append": (c_int, [c_void_p] * 4 + [c_int] * 5 + [c_float, c_void_p]),
     "mkb_attention_decode": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_float, c_void_p]),
     "mkb_rope_attention_decode": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_float, c_float, c_void_p]),
+    "mkb_decode_status": (c_int, [c_void_p]),
     "mkb_silu_mul": (c_int, [c_void_p] * 2 + [c_int, c_int, c_void_p]),
     "mkb_peer_buffer_bytes": (c_int64, [c_int] * 3),
     "mkb_peer_alloc": (c_int, [c_int64, c_void_p]),

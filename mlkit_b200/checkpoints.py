@@ -34,7 +34,8 @@ from mlkit_b200.quantization import Q, decoder, pack, registered, unpack
 FORMAT_VERSION = 1
 MANIFEST_FILE = "mlkit.json"
 WEIGHTS_FILE = "weights.safetensors"
-_HALF_STORAGE = {torch.float16, torch.bfloat16}
+# parameter tensors stored in these dtypes are widened to fp32 on load (src/mlkit/checkpoints/loading.py:33,180)
+_HALF_STORAGE = {torch.float16, torch.bfloat16, torch.float8_e4m3fn}
 _JSON_TYPES = (str, int, float, bool, list, dict, type(None))
 
 
@@ -174,6 +175,11 @@ def load_checkpoint(path: str | Path, *, model: nn.Module | Callable[[], nn.Modu
     manifest = json.loads((directory / MANIFEST_FILE).read_text())
     if manifest.get("format_version") != FORMAT_VERSION:
         raise ValueError("unsupported mlkit checkpoint format version")
+    if manifest.get("activations") or manifest.get("kv") is not None:
+        # the reference installs online activation / KV quantisers for these entries
+        # (src/mlkit/checkpoints/loading.py:86-100); loading without them would run different numerics
+        raise NotImplementedError("this checkpoint asks for online activation or KV-cache quantisation, "
+                                  "which mlkit_b200 does not implement")
     dtype = getattr(torch, manifest["dtype"])
     tokenizer = None
     if model is None:
@@ -217,8 +223,8 @@ def load_checkpoint(path: str | Path, *, model: nn.Module | Callable[[], nn.Modu
     converted.quantized = quantized
     converted.tied_weights = dict(tied)
     converted.stability_reports = manifest.get("stability_reports", {})
-    converted.activation_specs = dict(manifest.get("activations", {}))
-    converted.kv_spec = manifest.get("kv")
+    converted.activation_specs = {}
+    converted.kv_spec = None
     converted.layer_reports = [
         LayerReport(record["name"], tuple(record["shape"]), record.get("bits"), record.get("loss", 0.0),
                     record.get("seconds", 0.0))

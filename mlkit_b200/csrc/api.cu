@@ -173,9 +173,14 @@ extern "C" int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* sca
                             packed_row_stride, scale_row_stride, grid_minimum, s);
   if (kernel == MKB_GEMV_TILED)
     MKB_REQUIRE(tiled_ok, MKB_E_UNSUPPORTED, "gemv: the tiled kernel does not cover these arguments");
-  if (kernel == MKB_GEMV_TILED || (kernel == MKB_GEMV_AUTO && tiled_ok))
-    return launch_gemv_tiled(x, packed, scales, lut, zeros, bias, y, M, N, K, group, bits, lut_len,
-                             packed_row_stride, scale_row_stride, integer_grid, grid_minimum, gated, s);
+  if (kernel == MKB_GEMV_TILED || (kernel == MKB_GEMV_AUTO && tiled_ok)) {
+    const int launched = launch_gemv_tiled(x, packed, scales, lut, zeros, bias, y, M, N, K, group, bits, lut_len,
+                                           packed_row_stride, scale_row_stride, integer_grid, grid_minimum, gated, s);
+    // the tiled kernel sizes its shared memory from M, K, bits and the decode mode and refuses, before
+    // it launches anything, a combination that does not fit one SM (a 256-entry table with K = 28672
+    // at more than four rows, say): under AUTO such a call takes the scalar kernel
+    if (launched != MKB_E_UNSUPPORTED || kernel == MKB_GEMV_TILED || gated) return launched;
+  }
   MKB_REQUIRE(!gated, MKB_E_UNSUPPORTED, "gemv: the gated input needs the tiled kernel");
   return launch_gemv_scalar(x, packed, scales, lut, zeros, bias, y, M, N, K, group, bits, lut_len, x_dtype,
                             scale_dtype, packed_row_stride, scale_row_stride, s);

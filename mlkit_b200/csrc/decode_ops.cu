@@ -133,6 +133,19 @@ __global__ void __launch_bounds__(256) add_rmsnorm_generic_kernel(__half* __rest
 
 // qkv[m] = [q heads | k heads | v heads], head_dim D (even).  Rotates q and k in place (pairs (i, i + D/2),
 // angle position * theta^(-2i/D)) and writes k, v into the caches at `positions[m]`.
+// A cache position outside [0, capacity) must never become an address: the kernels clamp it, skip the
+// append, and raise this word, which mkb_decode_status reads (and clears).
+__device__ unsigned int g_decode_status = 0;
+
+__device__ __forceinline__ int checked_position(int position, int capacity, bool& valid) {
+  valid = position >= 0 && position < capacity;
+  if (!valid) {
+    if (threadIdx.x == 0) atomicOr(&g_decode_status, 1u);
+    position = position < 0 ? 0 : capacity - 1;
+  }
+  return position;
+}
+
 __global__ void rope_append_kernel(__half* __restrict__ qkv, const int* __restrict__ positions,
                                    __half* __restrict__ k_cache, __half* __restrict__ v_cache, int q_heads,
                                    int kv_heads, int D, int capacity, float theta) {
@@ -141,7 +154,8 @@ __global__ void rope_append_kernel(__half* __restrict__ qkv, const int* __restri
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   const int m = blockIdx.x, head = blockIdx.y;  // head over q_heads + kv_heads (+ kv_heads for v)
-  const int position = positions[m];
+  bool in_cache;
+  const int position = checked_position(positions[m], capacity, in_cache);
   const int row = (q_heads + 2 * kv_heads) * D;
   __half* vec = qkv + int64_t(m) * row + int64_t(head) * D;
   const int half_dim = D / 2;
@@ -155,7 +169,7 @@ __global__ void rope_append_kernel(__half* __restrict__ qkv, const int* __restri
       vec[i + half_dim] = __float2half_rn(b * c + a * s);
     }
   }
-  if (head >= q_heads) {
+  if (head >= q_heads && in_cache) {
     __syncthreads();
     const bool is_v = head >= q_heads + kv_heads;
     const int kv = head - q_heads - (is_v ? kv_heads : 0);
@@ -187,7 +201,8 @@ __global__ void __launch_bounds__(kAttentionThreads) attention_decode_kernel(
   __shared__ float part_s[kAttentionWarps];
   __shared__ float acc_s[kAttentionWarps][D];
   const int m = blockIdx.x, head = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int length = positions[m] + 1;  // the new token was appended already
+  bool in_cache;
+  const int length = checked_position(positions[m], capacity, in_cache) + 1;  // the new token was appended already
   const int kv = head / (q_heads / kv_heads);
   const int row = (q_heads + 2 * kv_heads) * D;
   if (threadIdx.x < D) q_s[threadIdx.x] = __half2float(qkv[int64_t(m) * row + int64_t(head) * D + threadIdx.x]) * scale;
@@ -313,7 +328,8 @@ __global__ void __launch_bounds__(kGroupThreads) attention_group_kernel(const __
   const int m = blockIdx.x, kv = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int G = q_heads / kv_heads;               // <= 8: rows g of the tiles; rows g + 8 are padding
-  const int length = positions[m] + 1;
+  bool in_cache;
+  const int length = checked_position(positions[m], capacity, in_cache) + 1;
   const int row = (q_heads + 2 * kv_heads) * D;
   const __half* keys = k_cache + (int64_t(m) * kv_heads + kv) * capacity * D;
   const __half* values = v_cache + (int64_t(m) * kv_heads + kv) * capacity * D;
@@ -324,7 +340,13 @@ __global__ void __launch_bounds__(kGroupThreads) attention_group_kernel(const __
     // rotary embedding fused in: this CTA rotates the new key of its head and appends key and value
     // to the caches itself (nobody else reads that slot), and rotates its query heads in registers
     const int position = length - 1;
-    if (threadIdx.x < D / 2) {
+    if (!in_cache) {
+      // nothing is appended for a position outside the cache; the rotation tables are still filled
+      if (threadIdx.x < D / 2) {
+        const float freq = powf(theta, -2.f * float(threadIdx.x) / float(D));
+        sincosf(float(position) * freq, &sin_s[threadIdx.x], &cos_s[threadIdx.x]);
+      }
+    } else if (threadIdx.x < D / 2) {
       const float freq = powf(theta, -2.f * float(threadIdx.x) / float(D));
       float sine, cosine;
       sincosf(float(position) * freq, &sine, &cosine);
@@ -610,6 +632,17 @@ extern "C" int mkb_rope_attention_decode(const void* qkv, const int* positions, 
       static_cast<const __half*>(qkv), positions, static_cast<const __half*>(k_cache),
       static_cast<const __half*>(v_cache), static_cast<__half*>(out), q_heads, kv_heads, capacity, scale, theta, 1);
   if (launched != cudaSuccess) return cuda_fail(launched, "rope_attention_decode launch");
+  return MKB_OK;
+}
+
+extern "C" int mkb_decode_status(int* status) {
+  using namespace mkb;
+  MKB_REQUIRE(status != nullptr, MKB_E_ARGUMENT, "decode_status: null pointer");
+  unsigned int value = 0, zero = 0;
+  cudaError_t done = cudaMemcpyFromSymbol(&value, g_decode_status, sizeof(value));
+  if (done == cudaSuccess && value != 0) done = cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(zero));
+  if (done != cudaSuccess) return cuda_fail(done, "decode_status");
+  *status = int(value);
   return MKB_OK;
 }
 

@@ -557,14 +557,29 @@ extern "C" int mkb_gemv_static(const void* x, const uint8_t* packed, const void*
   void* scratch = nullptr;
   const int status = static_scratch_address(&scratch);
   if (status != MKB_OK) return status;
-  // the array keeps what the previous call left: the row-block counters and the status word of this
-  // launch must start at zero
+  // the array keeps what the previous call left: the row-block counters of this launch must start at
+  // zero.  The status word is sticky (a wait that expired stays visible until mkb_gemv_static_status
+  // reads and clears it), as the status of a caller's workspace is.
   const int64_t row_blocks = (N + 127) / 128;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  cudaError_t cleared = cudaMemsetAsync(scratch, 0, size_t(row_blocks) * 4, s);
-  if (cleared == cudaSuccess) cleared = cudaMemsetAsync(static_cast<uint8_t*>(scratch) + kMaxRowBlocks * 4, 0, 4, s);
+  const cudaError_t cleared = cudaMemsetAsync(scratch, 0, size_t(row_blocks) * 4, s);
   if (cleared != cudaSuccess) return cuda_fail(cleared, "gemv_static: clearing the counters");
   return launch_gemv_umma(x, packed, scales, bias, y, scratch, M, N, K, group, packed_row_stride, scale_row_stride,
                           grid_minimum, s);
 }
 
+extern "C" int mkb_gemv_static_status(int* status) {
+  using namespace mkb;
+  MKB_REQUIRE(status != nullptr, MKB_E_ARGUMENT, "gemv_static_status: null pointer");
+  void* scratch = nullptr;
+  const int looked_up = static_scratch_address(&scratch);
+  if (looked_up != MKB_OK) return looked_up;
+  // the status word follows the row-block counters; read it, then clear it for the calls to come
+  uint8_t* word = static_cast<uint8_t*>(scratch) + kMaxRowBlocks * 4;
+  int value = 0;
+  cudaError_t done = cudaMemcpy(&value, word, sizeof(value), cudaMemcpyDeviceToHost);
+  if (done == cudaSuccess && value != 0) done = cudaMemset(word, 0, sizeof(value));
+  if (done != cudaSuccess) return cuda_fail(done, "gemv_static_status");
+  *status = value;
+  return MKB_OK;
+}

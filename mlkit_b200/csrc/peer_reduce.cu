@@ -78,6 +78,9 @@ __global__ void __launch_bounds__(kGatherThreads) peer_reduce_add_rmsnorm_kernel
   if (threadIdx.x == 0) ready_s = 1;
   __syncthreads();
   if (threadIdx.x < world) {
+    // release: the barrier above ordered every thread's stores before this point for this thread;
+    // the fence makes them visible system-wide before the flag that announces them
+    __threadfence_system();
     volatile uint32_t* raised = &static_cast<Header*>(peers[threadIdx.x])->flags[parity][rank][m];
     *raised = v;
   }

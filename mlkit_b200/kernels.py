@@ -294,3 +294,13 @@ def silu_mul(gate_up: Tensor, out: Tensor) -> None:
     status = _native.library().mkb_silu_mul(gate_up.data_ptr(), out.data_ptr(), gate_up.shape[0], out.shape[1],
                                             _stream(gate_up.device))
     _native.check(status, "silu_mul")
+
+
+def decode_status() -> int:
+    """Non-zero when a decode operator since the last call saw a cache position outside ``[0, capacity)``
+    (it clamped the position and skipped the append; that step's results are not valid).  Synchronises."""
+    import ctypes
+
+    value = ctypes.c_int(0)
+    _native.check(_native.library().mkb_decode_status(ctypes.byref(value)), "decode_status")
+    return value.value

@@ -359,6 +359,13 @@ class TensorParallelDecoder:
         batch = tokens.shape[0]
         if batch > self.max_batch:
             raise ValueError(f"batch {batch} exceeds max_batch {self.max_batch}")
+        if not torch.cuda.is_current_stream_capturing():
+            # an eager step checks its cache slots on the host (one small synchronisation).  A captured
+            # step cannot: its caller keeps positions below the capacity; the kernels clamp a position
+            # that is not and report it through kernels.decode_status()
+            low, high = int(positions.min()), int(positions.max())
+            if low < 0 or high >= self.capacity:
+                raise ValueError(f"positions {low}..{high} leave the cache of {self.capacity} slots")
         work = self._buffers(batch)
         local_q, local_kv = c.q_heads // w, c.kv_heads // w
         residual, normed = work["residual"], work["normed"]

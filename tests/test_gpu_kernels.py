@@ -271,6 +271,47 @@ def test_matvec_rejects_bad_arguments():
                               bits=3)
 
 
+FULL_SIZE_CODECS = [("int", 2, 128), ("int", 3, 128), ("int", 8, 128), ("nf4", 4, 64), ("codebook3", 3, 64)]
+
+
+@pytest.mark.parametrize("kind,bits,group", FULL_SIZE_CODECS)
+def test_matvec_codec_sweep_full_size(kind, bits, group):
+    """The codec sweep of the baseline at its own size, one 4096 -> 14336 linear, one and eight rows:
+    bit-exact dequantisation and the matvec within 2e-3 of reconstruct-then-matmul.  (Scales by absolute
+    maximum here; the MSE-fitted codebook scales are covered at a smaller size, the search being slow
+    on the host and the kernels blind to how a scale was chosen.)"""
+    from mlkit_b200 import kernels
+
+    rows, width = 14336, 4096
+    layer = helpers.make_layer(rows, width, bits, group, kind, seed=bits + group)
+    dense, codes = kernels.dequantize(dev(layer["packed"]), dev(layer["scales16"]), dev(layer["values"]), None,
+                                      shape=(rows, width), group=group, bits=bits, codes=True)
+    assert np.array_equal(codes.cpu().numpy(), layer["codes"])
+    reference = codec.reconstruct_weight(layer["codes"], layer["scales16"], layer["values"], group)
+    assert np.array_equal(dense.cpu().numpy(), reference)
+    for rows_in in (1, 8):
+        x = helpers.activations(rows_in, width, seed=rows_in)
+        expected = x.astype(np.float32) @ reference.astype(np.float32).T
+        y = run_matvec(layer, x, "auto")
+        assert matvec.relative_l2(y, expected) < TOLERANCE
+        assert np.array_equal(y, run_matvec(layer, x, "auto"))
+
+
+def test_matvec_codebook_with_fitted_scales():
+    layer = helpers.make_layer(512, 4096, 3, 64, "codebook3", seed=9, scale="mse")
+    for rows_in in (1, 8):
+        x = helpers.activations(rows_in, 4096, seed=rows_in)
+        assert matvec.relative_l2(run_matvec(layer, x, "auto"), oracle_matvec(layer, x)) < TOLERANCE
+
+
+def test_matvec_auto_falls_back_when_the_tiled_kernel_does_not_fit():
+    """A 256-entry table codec at K = 28672 and eight rows needs more shared memory than an SM has in
+    the tiled kernel: AUTO must take the scalar kernel instead of refusing the call."""
+    layer = helpers.random_layer(64, 28672, 8, 128, seed=2)
+    x = helpers.activations(8, 28672, seed=3)
+    assert matvec.relative_l2(run_matvec(layer, x, "auto"), oracle_matvec(layer, x)) < TOLERANCE
+
+
 LLAMA8B = {"q": (4096, 4096), "k": (1024, 4096), "o": (4096, 4096), "gate": (14336, 4096), "down": (4096, 14336)}
 
 

@@ -197,6 +197,17 @@ def test_decoder_matches_dense_reference_and_graph_replay():
     assert model.weight_bytes > 0
 
 
+def test_decoder_refuses_positions_outside_the_cache():
+    """The host check of an eager step; no out-of-range position ever reaches a kernel here."""
+    config = SMALL
+    model = tp.TensorParallelDecoder(config, rank=0, world=1, device=torch.device("cuda"), max_batch=2, capacity=16)
+    tokens = torch.tensor([1, 2], device="cuda")
+    for bad in ([0, 16], [-1, 3]):
+        with pytest.raises(ValueError, match="leave the cache"):
+            model.step(tokens, torch.tensor(bad, dtype=torch.int32, device="cuda"))
+    assert kernels.decode_status() == 0
+
+
 @pytest.mark.parametrize("world", [2, 4])
 def test_shards_sum_to_the_full_projection(world):
     config = tp.DecoderConfig(layers=1, hidden=512, q_heads=8, kv_heads=4, head_dim=128, intermediate=1024, vocab=512)
@@ -225,6 +236,148 @@ def test_shards_sum_to_the_full_projection(world):
         o_sum += shards["o"](wide_q[:, rank * share_q:(rank + 1) * share_q].contiguous(), out(shards["o"])).float()
         down_sum += shards["down"](wide_i[:, rank * share_i:(rank + 1) * share_i].contiguous(), out(shards["down"])).float()
     assert rel(o_sum, o_full) < 2e-3 and rel(down_sum, down_full) < 2e-3
+
+
+# ---------------------------------------------------------------- the peer-memory reduction on one GPU
+class LocalExchange:
+    """``world`` exchange buffers on one device, as the ranks of one node would map them."""
+
+    def __init__(self, world, rows, width):
+        import ctypes
+
+        from mlkit_b200 import _native
+
+        self.lib, self.world, self.rows, self.width = _native.library(), world, rows, width
+        size = self.lib.mkb_peer_buffer_bytes(rows, width, world)
+        self.buffers = []
+        for _ in range(world):
+            pointer = ctypes.c_void_p()
+            _native.check(self.lib.mkb_peer_alloc(size, ctypes.byref(pointer)), "peer_alloc")
+            self.buffers.append(pointer.value)
+        self.peers = torch.tensor(self.buffers, dtype=torch.int64, device="cuda")
+
+    def reduce(self, rank, partial, residual, weight, eps=1e-5):
+        """One reduction as rank ``rank`` issues it; returns (reduced, normed); ``residual`` is updated."""
+        from mlkit_b200 import _native
+
+        normed, reduced = torch.empty_like(partial), torch.empty_like(partial)
+        _native.check(self.lib.mkb_peer_reduce_add_rmsnorm(
+            partial.data_ptr(), self.peers.data_ptr(), self.buffers[rank], residual.data_ptr(), weight.data_ptr(),
+            normed.data_ptr(), reduced.data_ptr(), partial.shape[0], self.width, self.rows, self.world, rank, eps,
+            torch.cuda.current_stream().cuda_stream), "peer_reduce_add_rmsnorm")
+        return reduced, normed
+
+    def status(self, rank):
+        import ctypes
+
+        from mlkit_b200 import _native
+
+        value = ctypes.c_int(-1)
+        _native.check(self.lib.mkb_peer_status(self.buffers[rank], ctypes.byref(value)), "peer_status")
+        return value.value
+
+    def limit(self, rank, polls):
+        from mlkit_b200 import _native
+
+        _native.check(self.lib.mkb_peer_set_poll_limit(self.buffers[rank], polls), "peer_set_poll_limit")
+
+    def close(self):
+        torch.cuda.synchronize()
+        for buffer in self.buffers:
+            self.lib.mkb_peer_free(buffer)
+
+
+def reference_add_rmsnorm(total16, residual, weight, eps=1e-5):
+    """fp16 sum added to the residual (one rounding), then the norm with the operator's rounding points."""
+    updated = (residual.float() + total16.float()).half()
+    inverse = torch.rsqrt(updated.float().pow(2).mean(-1, keepdim=True) + eps)
+    return updated, ((updated.float() * inverse).half().float() * weight.float()).half()
+
+
+@pytest.mark.parametrize("rows_in", [1, 8])
+def test_peer_reduction_of_one_rank_equals_add_rmsnorm(rows_in):
+    """world = 1: the kernel pushes to and waits on its own buffer only.  Five reductions, eager and
+    replayed from a CUDA graph, walk both slot parities and the persistent per-row counters; sum,
+    residual and norm must equal ``mkb_add_rmsnorm`` on the same data bit for bit."""
+    torch.manual_seed(rows_in)
+    width = 1024
+    exchange = LocalExchange(1, 8, width)
+    weight = (torch.rand(width, device="cuda") + 0.5).half()
+    residual, expected_residual = torch.zeros(rows_in, width, device="cuda").half(), torch.zeros(rows_in, width, device="cuda").half()
+    for _ in range(3):
+        partial = torch.randn(rows_in, width, device="cuda").half()
+        reduced, normed = exchange.reduce(0, partial, residual, weight)
+        expected_normed = torch.empty_like(partial)
+        kernels.add_rmsnorm(expected_residual, partial, weight, expected_normed, 1e-5)
+        assert torch.equal(reduced, partial) and torch.equal(residual, expected_residual)
+        assert torch.equal(normed, expected_normed)
+    partial = torch.randn(rows_in, width, device="cuda").half()
+    graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            reduced, normed = exchange.reduce(0, partial, residual, weight)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(2):
+        graph.replay()
+        expected_normed = torch.empty_like(partial)
+        kernels.add_rmsnorm(expected_residual, partial, weight, expected_normed, 1e-5)
+        torch.cuda.synchronize()
+        assert torch.equal(reduced, partial) and torch.equal(residual, expected_residual)
+        assert torch.equal(normed, expected_normed)
+    assert exchange.status(0) == 0
+    exchange.close()
+
+
+@pytest.mark.parametrize("rows_in", [1, 8])
+def test_peer_reduction_of_two_ranks_in_turn(rows_in):
+    """Two ranks' buffers on one GPU, the ranks' kernels issued one after the other (kernels that wait
+    on one another must not share a GPU).  Rank 1 goes first with a poll limit of a thousand: it
+    delivers its partial to both buffers, its own wait for rank 0 runs out and its result is void.
+    Rank 0 then finds both partials and must produce the fp16 sum in rank order, the updated residual
+    and the norm.  Three rounds use both slot parities."""
+    torch.manual_seed(10 + rows_in)
+    width = 2048
+    exchange = LocalExchange(2, 8, width)
+    exchange.limit(1, 1000)
+    weight = (torch.rand(width, device="cuda") + 0.5).half()
+    residual = torch.randn(rows_in, width, device="cuda").half()
+    expected_residual = residual.clone()
+    scratch_residual = torch.zeros_like(residual)
+    for _ in range(3):
+        partials = [torch.randn(rows_in, width, device="cuda").half() for _ in range(2)]
+        exchange.reduce(1, partials[1], scratch_residual, weight)
+        reduced, normed = exchange.reduce(0, partials[0], residual, weight)
+        total16 = (partials[0].float() + partials[1].float()).half()
+        expected_residual, expected_normed = reference_add_rmsnorm(total16, expected_residual, weight)
+        assert torch.equal(reduced, total16)
+        assert torch.equal(residual, expected_residual)
+        assert rel(normed, expected_normed) < 1e-3 and (normed.float() - expected_normed.float()).abs().max() < 0.02
+    assert exchange.status(0) == 0 and exchange.status(1) == 1
+    exchange.close()
+
+
+def test_peer_reduction_wait_runs_out_without_hanging():
+    """A flag that nothing sets: with a poll limit of a thousand the kernel gives up, sets the status
+    word and finishes; the next call skips its wait altogether."""
+    width = 512
+    exchange = LocalExchange(2, 8, width)
+    exchange.limit(0, 1000)
+    weight = torch.ones(width, device="cuda").half()
+    partial = torch.ones(2, width, device="cuda").half()
+    residual = torch.zeros(2, width, device="cuda").half()
+    assert exchange.status(0) == 0
+    exchange.reduce(0, partial, residual, weight)
+    torch.cuda.synchronize()
+    assert exchange.status(0) == 1
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    exchange.limit(0, 20_000_000)   # would be seconds of polling if the wait were not skipped
+    start.record()
+    exchange.reduce(0, partial, residual, weight)
+    stop.record()
+    torch.cuda.synchronize()
+    assert start.elapsed_time(stop) < 50 and exchange.status(0) == 1
+    exchange.close()
 
 
 def _free_port():

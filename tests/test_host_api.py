@@ -140,6 +140,40 @@ def test_factor_bases_match_reference(golden_meta, golden_transforms):
         mk.hadamard(torch.randn(3, 12))
 
 
+def test_restore_layer_widens_fp8_scales_and_refuses_online_quantisers(tmp_path):
+    """A layer as the reference's ``save`` writes it with ``scale_fmt="fp8"`` (scales stored as
+    float8_e4m3fn, src/mlkit/checkpoints/saving.py:60-69): the loader widens them to fp32 and the
+    reconstruction equals the oracle's.  A manifest that asks for online activation or KV-cache
+    quantisation is refused instead of being loaded without its quantisers."""
+    import json
+
+    from mlkit_b200 import checkpoints
+    from oracle import bitstream, codec
+
+    rng = np.random.default_rng(4)
+    rows, width, group, bits = 6, 64, 32, 4
+    codes = rng.integers(0, 16, size=(rows, width), dtype=np.uint8)
+    scales8 = torch.from_numpy((rng.random((rows, width // group), dtype=np.float32) * 0.05 + 0.01)).to(torch.float8_e4m3fn)
+    values = codec.int_values(bits)
+    tensors = {"layer.codes": torch.from_numpy(bitstream.pack(codes, bits)), "layer.params.scales": scales8,
+               "layer.params.values": torch.from_numpy(values)}
+    layer = {"codec": "scaled", "shape": [rows, width], "code_bits": bits, "bits": 4.5,
+             "params": {"scales": {"tensor": "layer.params.scales", "encoding": None},
+                        "values": {"tensor": "layer.params.values", "encoding": None}, "group": {"value": group},
+                        "offset": {"value": 0}},
+             "metadata": {"scale_fmt": "fp8"}}
+    restored = checkpoints.restore_layer(tensors, "layer", layer)
+    assert restored.params["scales"].dtype == torch.float32
+    expected = codec.decode_scaled(codes, scales8.float().numpy(), values, group)
+    assert np.array_equal(restored.w.numpy(), expected)
+
+    manifest = {"format_version": 1, "name": "m", "architecture": "external", "dtype": "float16", "layers": {},
+                "activations": {"layer": {"bits": 8}}, "kv": None}
+    (tmp_path / "mlkit.json").write_text(json.dumps(manifest))
+    with pytest.raises(NotImplementedError, match="online activation"):
+        checkpoints.load_checkpoint(tmp_path, model=torch.nn.Linear(4, 4))
+
+
 def test_hot_path_refuses_cpu_tensors():
     linear = torch.nn.Linear(64, 8)
     q = mk.int(4, group=32)(linear.weight.detach())

@@ -50,6 +50,11 @@ def _run_both(layer, x, bias=None):
         _native.check(status, "mkb_gemv_static")
         results.append(out)
     torch.cuda.synchronize()
+    import ctypes
+
+    expired = ctypes.c_int(-1)   # no bounded wait ran out in the calls above
+    _native.check(lib.mkb_gemv_static_status(ctypes.byref(expired)), "mkb_gemv_static_status")
+    assert expired.value == 0
     return expected.cpu().numpy(), [r.cpu().numpy() for r in results]
 
 
@@ -65,6 +70,32 @@ def test_static_scratch_entry_matches_the_workspace_entry(shape, rows_in):
     reference = matvec.reconstruct_then_matmul(x, layer["packed"], layer["scales16"], layer["values"], 128, 4, shape,
                                                bias=bias)
     assert matvec.relative_l2(results[1], reference) < TOLERANCE
+
+
+def test_static_scratch_entry_at_the_limit_of_the_scratch():
+    """254 row blocks x 8 slabs x 8 rows need exactly the 8 MiB the library holds; one row block more is
+    refused.  Random codes (the arithmetic is value-blind); the yardstick is the workspace entry.  On
+    a machine with a second GPU the same call runs there too: every device has its own array."""
+    from mlkit_b200 import _native
+    from oracle import bitstream
+
+    rows, width = 254 * 128, 4096
+    rng = np.random.default_rng(8)
+    layer = {"rows": rows, "group": 128, "values": np.arange(-8, 8, dtype=np.float32),
+             "packed": rng.integers(0, 256, size=rows * width // 2, dtype=np.uint8),
+             "scales16": (rng.random((rows, width // 128), dtype=np.float32) * 0.01 + 0.001).astype(np.float16)}
+    x = helpers.activations(8, width, seed=4)
+    assert _native.library().mkb_gemv_workspace_bytes(8, rows, width, 4) >= 8 << 20
+    for device in range(min(2, torch.cuda.device_count())):
+        with torch.cuda.device(device):
+            expected, results = _run_both(layer, x)
+            for got in results:
+                assert np.array_equal(got, expected)
+    lib = _native.library()
+    big = torch.zeros(8, width, dtype=torch.float16, device="cuda")
+    status = lib.mkb_gemv_static(big.data_ptr(), big.data_ptr(), big.data_ptr(), None, big.data_ptr(), 8, rows + 128,
+                                 width, 128, width // 2, width // 128, -8.0, torch.cuda.current_stream().cuda_stream)
+    assert status == -2 and b"built-in scratch holds" in lib.mkb_last_error()
 
 
 def test_static_scratch_entry_refuses_what_does_not_fit():
