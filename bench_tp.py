@@ -168,7 +168,7 @@ def run(args, rank: int, world: int, device: torch.device, peak_info: tuple[floa
         "clocks": sampler.summary,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_kind": peak_kind,
-                     "kernel": f"gemv_tiled_kernel<4, raw> on the gate|up shard {results['kernel']['shape']}, M=1, rank 0",
+                     "kernel": f"the matvec kernel AUTO takes (gemv_stream_kernel) on the gate|up shard {results['kernel']['shape']}, M=1, rank 0",
                      "bytes_per_launch": results["kernel"]["bytes"], "us_per_launch": results["kernel"]["us"]},
         "decode": {
             "tokens_per_s": {"batch1": one["tokens_per_s"], "batch8": eight["tokens_per_s"]},

@@ -41,10 +41,10 @@ enum {
   MKB_GEMV_GATED = 0x100, /* flag, OR-ed into a choice (mkb_gemv_ex, mkb_gemv_ws): x is [M, 2K] = gate | up of a
                              SwiGLU MLP and the kernel forms silu(gate) * up while it loads the activations
                              (rounded to fp16 after the activation and after the product, as separate fp16
-                             operators would); tiled kernel only (AUTO then takes it).  Every CTA redoes the
-                             activation for its share of K, so for one or two rows a separate SwiGLU kernel
-                             is as fast; it pays when the launch count matters more.  The reference leaves this
-                             product to the model code between two PackedLinear calls */
+                             operators would); tiled and streaming kernels (AUTO takes one of them).  In the
+                             streaming kernel every warp forms the activation of its own share of K once, so
+                             the cost is M * K activations per CTA; it replaces a launch.  The reference leaves
+                             this product to the model code between two PackedLinear calls */
   MKB_GEMV_BULK = 4,   /* TMA-fed kernel: whole 16-row units by cp.async.bulk.tensor into a shared-memory ring
                           (INT4 integer grid, fp16, K % 256 == 0; needs the workspace when K is split) */
   MKB_GEMV_STREAM = 5  /* streaming kernel: activations in registers, weights through per-warp cp.async rings

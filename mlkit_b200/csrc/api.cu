@@ -70,7 +70,7 @@ int gemv_stream_supported(int M, int N, int K, int group, int bits, int x_dtype,
                           int64_t scale_row_stride, const void* zeros, int integer_grid, float grid_minimum);
 int launch_gemv_stream(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y, int M,
                        int N, int K, int64_t packed_row_stride, int64_t scale_row_stride, float grid_minimum,
-                       cudaStream_t stream);
+                       int gated, cudaStream_t stream);
 
 }  // namespace mkb
 
@@ -142,10 +142,10 @@ extern "C" int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* sca
                          gemv_stream_supported(M, N, K, group, bits, x_dtype, scale_dtype, x, packed, scales,
                                                packed_row_stride, scale_row_stride, zeros, integer_grid, grid_minimum);
   if (kernel == MKB_GEMV_STREAM)
-    MKB_REQUIRE(stream_ok && !gated, MKB_E_UNSUPPORTED, "gemv: the streaming kernel does not cover these arguments");
-  if (kernel == MKB_GEMV_STREAM || (!gated && kernel == MKB_GEMV_AUTO && stream_ok))
+    MKB_REQUIRE(stream_ok, MKB_E_UNSUPPORTED, "gemv: the streaming kernel does not cover these arguments");
+  if (kernel == MKB_GEMV_STREAM || (kernel == MKB_GEMV_AUTO && stream_ok))
     return launch_gemv_stream(x, packed, scales, bias, y, M, N, K, packed_row_stride, scale_row_stride,
-                              grid_minimum, s);
+                              grid_minimum, gated, s);
   const bool tiled_ok = gemv_tiled_supported(M, K, group, bits, x_dtype, scale_dtype, x, packed, packed_row_stride);
   const bool tmem_ok = workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) % 16) == 0 && lut_len == 16 &&
                        gemv_umma_supported(M, K, group, bits, x_dtype, scale_dtype, x, packed, packed_row_stride, zeros,

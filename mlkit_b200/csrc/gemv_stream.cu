@@ -54,6 +54,7 @@ struct StreamArgs {
   int slabs;        // CTAs of a cluster along K (gridDim.y)
   int visits;       // visits of every CTA
   int batch;        // visits whose partial sums shared memory holds between two reductions (a multiple of R)
+  int gated;        // x is [M, 2K] = gate | up of a SwiGLU MLP: the activation is silu(gate) * up, formed on load
   int early;        // visits copied before the dependency wait; the rest of the ring follows the activation loads
   int kw_inverse, rg_inverse;  // ceil(65536 / KW), ceil(65536 / RG): small quotients by multiply and shift
   float grid_min;
@@ -195,7 +196,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
   uint32_t b[KT][4][4];   // [k-tile][word][pairs (x0,x4) (x2,x6) (x1,x5) (x3,x7)]
   float start[KT][4];     // accumulator start: min * sum(x) * 2^-24 for activation rows 2t, 2t+1 (twice)
   {
-    const __half* x_lane = a.x + int64_t(g) * a.K + int64_t(tile0) * 128 + t * 32;
+    const __half* x_lane = a.x + int64_t(g) * (a.gated ? 2 * a.K : a.K) + int64_t(tile0) * 128 + t * 32;
     const bool has_x = my_visits > 0 && g < a.M;
     uint4 v[KT][4];
 #pragma unroll
@@ -205,6 +206,17 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
         v[kk][w] = make_uint4(0u, 0u, 0u, 0u);
         if (has_x) v[kk][w] = __ldg(reinterpret_cast<const uint4*>(x_lane + kk * 128 + w * 8));
       }
+    if (a.gated) {  // the up half sits K elements further in the same row
+#pragma unroll
+      for (int kk = 0; kk < KT; ++kk)
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          uint4 up = make_uint4(0u, 0u, 0u, 0u);
+          if (has_x) up = __ldg(reinterpret_cast<const uint4*>(x_lane + a.K + kk * 128 + w * 8));
+          v[kk][w] = make_uint4(swiglu_pair(v[kk][w].x, up.x), swiglu_pair(v[kk][w].y, up.y),
+                                swiglu_pair(v[kk][w].z, up.z), swiglu_pair(v[kk][w].w, up.w));
+        }
+    }
     // the rest of the ring is requested behind the activations, so these are not queued behind it
 #pragma unroll
     for (int d = 0; d < R - 1; ++d)
@@ -514,7 +526,7 @@ int gemv_stream_supported(int M, int N, int K, int group, int bits, int x_dtype,
 
 int launch_gemv_stream(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y, int M,
                        int N, int K, int64_t packed_row_stride, int64_t scale_row_stride, float grid_minimum,
-                       cudaStream_t stream) {
+                       int gated, cudaStream_t stream) {
   const DeviceInfo& info = device_info();
   StreamPlan p;
   MKB_REQUIRE(plan_stream(M, N, K, info.sm_count, info.max_smem_optin, 0, p), MKB_E_UNSUPPORTED,
@@ -533,7 +545,7 @@ int launch_gemv_stream(const void* x, const uint8_t* packed, const void* scales,
   a.bias = static_cast<const __half*>(bias); a.y = static_cast<__half*>(y);
   a.M = M; a.N = N; a.K = K; a.packed_row_stride = packed_row_stride; a.scale_row_stride = scale_row_stride;
   a.row_tiles = (N + 15) / 16; a.k_warps = K / (128 * p.KT); a.KW = p.KW; a.RG = p.RG; a.slabs = p.slabs;
-  a.visits = p.visits; a.grid_min = grid_minimum; a.batch = p.batch; a.early = 1;
+  a.visits = p.visits; a.grid_min = grid_minimum; a.batch = p.batch; a.early = 1; a.gated = gated;
   a.kw_inverse = (65536 + p.KW - 1) / p.KW; a.rg_inverse = (65536 + p.RG - 1) / p.RG;
   return dispatch_stream(a, p, stream, nullptr);
 }

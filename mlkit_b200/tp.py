@@ -92,6 +92,10 @@ class PackedShard:
         self.plan = kernels.MatvecPlan(packed, scales, values, None, None, outputs=out_rows, width=width,
                                        group=group, bits=bits, dtype=torch.float16, integer_grid=integer,
                                        grid_minimum=low)
+        # the same launch reading gate | up and forming SwiGLU on the way (the down projection of an MLP)
+        self.gated_plan = kernels.MatvecPlan(packed, scales, values, None, None, outputs=out_rows, width=width,
+                                             group=group, bits=bits, dtype=torch.float16, integer_grid=integer,
+                                             grid_minimum=low, gated=True) if integer else None
 
     def __call__(self, x: Tensor, out: Tensor) -> Tensor:
         return self.plan(x, out)
@@ -396,8 +400,11 @@ class TensorParallelDecoder:
                 self._all_reduce(work["o"])
                 kernels.add_rmsnorm(residual, work["o"], mlp_norm, normed, c.eps)
             block["gate_up"](normed, work["gate_up"])
-            kernels.silu_mul(work["gate_up"], work["act"])
-            block["down"](work["act"], work["down"])
+            if block["down"].gated_plan is not None:   # SwiGLU formed while the down projection loads its input
+                block["down"].gated_plan(work["gate_up"], work["down"])
+            else:
+                kernels.silu_mul(work["gate_up"], work["act"])
+                block["down"](work["act"], work["down"])
             if exchange is None:
                 self._all_reduce(work["down"])
             delta = work["down"]

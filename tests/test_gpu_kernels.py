@@ -418,7 +418,7 @@ def test_rotated_matvec_path(width, rows):
     assert matvec.relative_l2(y, plain) < 0.2
 
 
-@pytest.mark.parametrize("kernel", ["tiled", "auto"])
+@pytest.mark.parametrize("kernel", ["tiled", "stream", "auto"])
 @pytest.mark.parametrize("rows_in", [1, 5, 8])
 def test_matvec_gated_input_equals_swiglu_then_matvec(kernel, rows_in):
     """MKB_GEMV_GATED: x = gate | up, the kernel forms silu(gate) * up on load with the rounding points
@@ -434,7 +434,7 @@ def test_matvec_gated_input_equals_swiglu_then_matvec(kernel, rows_in):
     plain = torch.empty((rows_in, outputs), dtype=torch.float16, device="cuda")
     fused = torch.empty_like(plain)
     options = dict(group=128, bits=4, integer_grid=True, grid_minimum=-8.0, kernel=kernel)
-    kernels.packed_matvec(act, packed, scales, values, None, None, plain, **dict(options, kernel="tiled"))
+    kernels.packed_matvec(act, packed, scales, values, None, None, plain, **options)
     kernels.packed_matvec(gate_up, packed, scales, values, None, None, fused, gated=True, **options)
     assert torch.equal(plain, fused)
     with pytest.raises(ValueError, match="gated"):

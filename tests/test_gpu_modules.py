@@ -344,3 +344,87 @@ def test_sibling_projections_share_one_launch_bit_for_bit(rows):
     block.q_proj.half()
     assert block.k_proj._siblings is None
     assert torch.equal(block.k_proj(x), separate.module.k_proj(x))
+
+
+# ---------------------------------------------------------------- a checkpoint written by the reference
+GOLDEN_CHECKPOINTS = __import__("pathlib").Path(__file__).resolve().parent / "golden" / "ckpt"
+
+
+class TiedLanguageModel(nn.Module):
+    """The model of the reference's checkpoint test (tests/checkpoints/test_checkpoints.py:60-80)."""
+
+    def __init__(self):
+        super().__init__()
+        self.embedding = nn.Embedding(32, 16)
+        self.projections = nn.Sequential(nn.Linear(16, 16), nn.Linear(16, 16))
+        self.lm_head = nn.Linear(16, 32, bias=False)
+        self.lm_head.weight = self.embedding.weight
+
+    def forward(self, tokens):
+        return self.lm_head(self.projections(self.embedding(tokens)))
+
+
+def _stored_tensors(directory):
+    from safetensors import safe_open
+
+    with safe_open(str(directory / "weights.safetensors"), "pt") as handle:
+        return {key: handle.get_tensor(key) for key in handle.keys()}
+
+
+def test_checkpoint_written_by_the_reference_loads_runs_and_saves_back(tmp_path):
+    """``tests/golden/ckpt/tied`` was written by the reference's own ``save`` (see make_checkpoint.py
+    beside it).  It must load unchanged, reproduce the reference's outputs, run packed, and a re-save
+    must give the same manifest entries and the same tensors, key for key and byte for byte."""
+    import json
+
+    source = GOLDEN_CHECKPOINTS / "tied"
+    stored = np.load(GOLDEN_CHECKPOINTS / "tied_io.npz")
+    tokens, expected = torch.from_numpy(stored["tokens"]).cuda(), torch.from_numpy(stored["logits"]).cuda()
+    restored = mk.load(source, model=TiedLanguageModel)
+    assert restored.module.embedding.weight is restored.module.lm_head.weight
+    with torch.inference_mode():
+        torch.testing.assert_close(restored(tokens), expected, rtol=1e-5, atol=1e-6)
+        packed = mk.optimize(restored)
+        assert packed.execution_backend == "packed:2"
+        assert matvec.relative_l2(packed(tokens).float().cpu().numpy(), stored["logits"]) < 2e-3
+    restored.save(tmp_path / "again")
+    first, second = json.loads((source / "mlkit.json").read_text()), json.loads((tmp_path / "again" / "mlkit.json").read_text())
+    for key in ("format_version", "name", "architecture", "dtype", "layers", "logical_bpw", "model_bpw",
+                "parameter_accounting", "transforms", "activations", "kv", "state_aliases", "tied_weights", "tensor_bytes"):
+        assert first[key] == second[key], key
+    before, after = _stored_tensors(source), _stored_tensors(tmp_path / "again")
+    assert set(before) == set(after)
+    for key, value in before.items():
+        assert value.dtype == after[key].dtype and torch.equal(value, after[key]), key
+
+
+def test_reference_checkpoint_with_a_rotation_installs_the_hook(tmp_path):
+    """``tests/golden/ckpt/rotated``: the manifest carries the rotation descriptor the reference
+    recorded; loading installs the input hook and a re-save keeps descriptor and tensors."""
+    import json
+
+    class Attention(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.o_proj = nn.Linear(64, 24, bias=False)
+
+        def forward(self, x):
+            return self.o_proj(x)
+
+    source = GOLDEN_CHECKPOINTS / "rotated"
+    seed = json.loads((GOLDEN_CHECKPOINTS / "fixture.json").read_text())["rotated"]["seed"]
+    restored = mk.load(source, model=Attention)
+    assert len(restored.module.o_proj._forward_pre_hooks) == 1
+    assert restored.module._mlkit_transforms == [{"kind": "rotation", "name": "o_proj", "seed": seed}]
+    x = torch.randn(3, 64)
+    packed = mk.optimize(restored)
+    with torch.inference_mode():
+        # the hook rotates with this device's sign vector, in the dense and in the packed model alike
+        expected = torch.nn.functional.linear(mk.rht(x, seed=seed), restored.module.o_proj.weight)
+        torch.testing.assert_close(restored(x), expected, rtol=1e-5, atol=1e-5)
+        torch.testing.assert_close(packed(x), expected, rtol=2e-3, atol=2e-3)
+    restored.save(tmp_path / "again")
+    again = json.loads((tmp_path / "again" / "mlkit.json").read_text())
+    assert again["transforms"] == json.loads((source / "mlkit.json").read_text())["transforms"]
+    before, after = _stored_tensors(source), _stored_tensors(tmp_path / "again")
+    assert set(before) == set(after) and all(torch.equal(before[key], after[key]) for key in before)
