@@ -174,6 +174,25 @@ int mkb_dequant_rows(const uint8_t* packed, const void* scales, const float* lut
                      int scale_dtype, int out_dtype, int64_t scale_row_stride, void* stream);
 
 /*
+ * Round-to-nearest encoding with one fp16 scale per row group (absolute maximum, symmetric), and
+ * packing, in one launch:
+ *   scale[n,j] = fp16(max(max_k |w[n,k]| over group j, 1e-12) * reciprocal)   (clamped to [2^-24, 65504])
+ *   code[n,k]  = round_half_even(w / scale) clamped to [grid_low, grid_high], minus grid_low    (integer_grid)
+ *              = index of the nearest level, a tie taking the lower one                        (otherwise)
+ *   packed     = the little-endian bit stream of the codes (bit_packing.py:13-77)
+ * `reciprocal` is fp32(1) / fp32(max |level|); the division w / scale is IEEE binary32.  codes_out
+ * (uint8 [N,K]) may be null.  A trailing partial group gets its own scale.  group * bits and K * bits
+ * must be multiples of 8 (groups and rows end on bytes).  weight_dtype is MKB_F16/BF16/F32.
+ *
+ * Replaces the fused encode the reference runs on CUDA (src/mlkit/kernels/scalar_encode.py:65-146)
+ * and the tensor route it must equal (src/mlkit/quantization/formats/grouped_scaling.py:288-392,
+ * scale_storage.py:11-26), followed by `pack` (src/mlkit/quantization/operations/bit_packing.py:13-77).
+ */
+int mkb_rtn_encode(const void* weight, const float* levels, uint8_t* packed, void* scales, uint8_t* codes_out,
+                   int64_t N, int K, int group, int bits, int level_count, int integer_grid,
+                   float grid_low, float grid_high, float reciprocal, int weight_dtype, void* stream);
+
+/*
  * Structured orthogonal transform of activation rows, fused:
  *   y[m,:] = (B kron H_pow2)(x[m,:] * signs), W = factor * pow2,
  * H the Sylvester-ordered Walsh-Hadamard butterflies in ascending stride in fp32, scaled by

@@ -28,6 +28,7 @@ SIGNATURES = {
     "mkb_gemv_static_status": (c_int, [c_void_p]),
     "mkb_dequant": (c_int, [c_void_p] * 6 + [c_int64, c_int64] + [c_int] * 5 + [c_int64, c_void_p]),
     "mkb_dequant_rows": (c_int, [c_void_p] * 6 + [c_int64] * 3 + [c_int] * 5 + [c_int64, c_void_p]),
+    "mkb_rtn_encode": (c_int, [c_void_p] * 5 + [c_int64] + [c_int] * 5 + [c_float] * 3 + [c_int, c_void_p]),
     "mkb_hadamard": (c_int, [c_void_p] * 4 + [c_int64] + [c_int] * 6 + [c_void_p]),
     "mkb_add_rmsnorm": (c_int, [c_void_p] * 4 + [c_int, c_int, c_float, c_void_p]),
     "mkb_rope_append": (c_int, [c_void_p] * 4 + [c_int] * 5 + [c_float, c_void_p]),

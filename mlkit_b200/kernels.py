@@ -206,6 +206,27 @@ def dequantize(packed: Tensor, scales: Tensor | None, values: Tensor | None, zer
     return weight, unpacked
 
 
+def rtn_encode(weight: Tensor, levels: Tensor, *, group: int, bits: int, integer_grid: bool, low: float, high: float,
+               reciprocal: float, codes: bool = False) -> tuple[Tensor, Tensor, Tensor | None]:
+    """Round-to-nearest encode and pack on the device: returns ``(packed uint8, scales fp16 [N, groups],
+    codes uint8 [N, K] or None)``.  Raises ``ValueError`` for layouts whose groups or rows do not end
+    on a byte (the caller then takes the tensor route)."""
+    device = _require_cuda(weight, levels)
+    rows, width = weight.shape
+    source = weight if weight.is_contiguous() else weight.contiguous()
+    group = min(group, width)
+    packed = torch.empty(rows * width * bits // 8, dtype=torch.uint8, device=device)
+    scales = torch.empty((rows, -(-width // group)), dtype=torch.float16, device=device)
+    unpacked = torch.empty((rows, width), dtype=torch.uint8, device=device) if codes else None
+    with torch.cuda.device(device):
+        status = _native.library().mkb_rtn_encode(
+            source.data_ptr(), levels.data_ptr(), packed.data_ptr(), scales.data_ptr(), _pointer(unpacked), rows, width,
+            group, bits, levels.numel(), int(integer_grid), float(low), float(high), float(reciprocal),
+            _tag(source.dtype, "weight"), _stream(device))
+    _native.check(status, "rtn_encode")
+    return packed, scales, unpacked
+
+
 def dequantize_rows(packed: Tensor, scales: Tensor, values: Tensor, zeros: Tensor | None, rows: Tensor, *,
                     shape: tuple[int, int], group: int, bits: int, dtype: torch.dtype) -> Tensor:
     """Reconstruct the listed rows only: ``out[i] = weight[rows[i]]``."""

@@ -410,6 +410,23 @@ class Scaled:
         rows, width = weight.shape
         group = width if self.group is None else min(self.group, width)
         levels = self.grid.values.to(weight.device).contiguous()
+        bits = self.grid.bits
+        if (weight.is_cuda and self.scale == "absmax" and not self.asym and self.scale_fmt == "fp16" and bits <= 8
+                and group <= 1024 and (group * bits) % 8 == 0 and (width * bits) % 8 == 0 and rows > 0):
+            # one launch on the device: the same arithmetic, operation for operation (mkb_rtn_encode)
+            from mlkit_b200 import kernels
+
+            if not torch.isfinite(weight).all():
+                raise ValueError("scaled requires a finite floating-point weight matrix")
+            _, scales16, codes = kernels.rtn_encode(weight, levels, group=group, bits=bits, integer_grid=self.grid.integer,
+                                                    low=self._low, high=self._high, reciprocal=self._reciprocal, codes=True)
+            scales = scales16.float()
+            return Q(
+                bits=bits * weight.numel() + scales.numel() * 16, codes=codes,
+                params={"scales": scales, "values": levels, "group": group, "offset": 0, "zero": None},
+                decode=decode_scaled, codec="scaled",
+                metadata={"code_bits": bits, "scale_fmt": self.scale_fmt, "trainable": ["scales"]},
+            )
         low, high = _group_range(weight, group)
         if not (torch.isfinite(low).all() and torch.isfinite(high).all()):
             raise ValueError("scaled requires a finite floating-point weight matrix")

@@ -111,6 +111,55 @@ def test_dequant_rows_gathers_like_an_embedding():
         assert np.array_equal(out.cpu().numpy(), dense[rows])
 
 
+# ---------------------------------------------------------------- encoding on the device (bit-exact)
+def test_device_rtn_encode_matches_the_reference_vectors(golden_meta, golden_codecs):
+    """``mkb_rtn_encode`` through the format objects: codes, scales and the packed stream of every
+    symmetric absolute-maximum case of the golden set equal what the reference produced."""
+    import mlkit_b200 as mk
+    from tests.test_host_api import build_format
+
+    checked = 0
+    for name, info in golden_meta["codecs"].items():
+        if info["asym"] or info["scale"] != "absmax":
+            continue
+        if name.startswith("e4m3"):
+            fmt = mk.scaled(mk.grid.fp("e4m3"), group=info["group"])
+        else:
+            fmt = build_format(name, info, golden_codecs[f"{name}.values"])
+        weight = torch.from_numpy(golden_codecs[f"{name}.weight"]).cuda()
+        q = fmt(weight.float(), mk.Ctx(name, device="cuda"))
+        assert q.codes.is_cuda and q.codes.dtype == torch.uint8
+        assert np.array_equal(q.codes.cpu().numpy(), golden_codecs[f"{name}.codes"]), name
+        assert np.array_equal(q.params["scales"].cpu().numpy(), golden_codecs[f"{name}.scales"]), name
+        assert np.array_equal(mk.pack(q.codes, info["bits"]).cpu().numpy(), golden_codecs[f"{name}.packed"]), name
+        checked += 1
+    assert checked >= 8
+
+
+@pytest.mark.parametrize("kind,bits,group,width", [("int", 4, 128, 4096), ("int", 3, 128, 1024), ("int", 8, 128, 512),
+                                                    ("int", 2, 64, 320), ("nf4", 4, 64, 4096), ("codebook3", 3, 64, 1000),
+                                                    ("int", 4, 128, 200), ("int", 5, 64, 256)])
+def test_device_rtn_encode_equals_the_tensor_route(kind, bits, group, width):
+    """The kernel against the torch-op route of the same format on the same device: codes, scales and
+    the packed stream, including a trailing partial group (1000 = 15 x 64 + 40, 200 = 128 + 72)."""
+    import mlkit_b200 as mk
+    from mlkit_b200 import kernels
+
+    values, integer = helpers.grid_values(kind, bits)
+    grid = mk.grid.int(bits) if integer else mk.grid.values(torch.from_numpy(values), bits=bits)
+    fmt = mk.scaled(grid, group=group)
+    weight = (torch.randn(300, width, device="cuda") * 0.02).half()
+    weight[5, :group] = 0                       # an all-zero group: the scale floor
+    weight[7, 3] = 30.0                         # a large outlier
+    levels = grid.values.cuda()
+    packed, scales16, codes = kernels.rtn_encode(weight, levels, group=group, bits=bits, integer_grid=integer,
+                                                 low=fmt._low, high=fmt._high, reciprocal=fmt._reciprocal, codes=True)
+    expected = fmt(weight.float().cpu())        # the tensor route (CPU tensors never take the kernel)
+    assert torch.equal(codes.cpu(), expected.codes)
+    assert torch.equal(scales16.float().cpu(), expected.params["scales"])
+    assert torch.equal(packed.cpu(), mk.pack(expected.codes, bits))
+
+
 # ---------------------------------------------------------------- matvec (<= 2e-3 relative L2)
 def test_matvec_matches_golden_vectors(golden_meta, golden_codecs):
     for name, info in golden_meta["codecs"].items():
