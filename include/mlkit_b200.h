@@ -241,6 +241,12 @@ int mkb_rope_attention_decode(const void* qkv, const int* positions, void* k_cac
                               int M, int q_heads, int kv_heads, int head_dim, int capacity, float theta,
                               float scale, void* stream);
 int mkb_silu_mul(const void* gate_up, void* out, int M, int I, void* stream);
+/* Greedy pick over a shard of the vocabulary: best[m] (uint64) = key(max_i logits[m, i]) << 32 |
+ * (0xffffffff - (argmax index + offset)), key a monotone map of the fp16 value to an unsigned word, so
+ * that the unsigned maximum of the ranks' words is the global pick and, on a tie, the smallest token.
+ * Ranks exchange these 8 bytes per sequence instead of their logits.  logits are fp16 [M, width] with
+ * row stride row_stride.  No counterpart in the reference, which leaves sampling to `transformers`. */
+int mkb_argmax(const void* logits, void* best, int M, int64_t width, int64_t row_stride, int64_t offset, void* stream);
 /* positions[m] must lie in [0, capacity).  The kernels above never turn a position outside that range
  * into an address: they clamp it, leave the caches untouched and raise a device-wide status word.
  * mkb_decode_status reads and clears that word (non-zero: some launch since the last reading saw such

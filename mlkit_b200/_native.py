@@ -34,6 +34,7 @@ SIGNATURES = {
     "mkb_rope_append": (c_int, [c_void_p] * 4 + [c_int] * 5 + [c_float, c_void_p]),
     "mkb_attention_decode": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_float, c_void_p]),
     "mkb_rope_attention_decode": (c_int, [c_void_p] * 5 + [c_int] * 5 + [c_float, c_float, c_void_p]),
+    "mkb_argmax": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p]),
     "mkb_decode_status": (c_int, [c_void_p]),
     "mkb_silu_mul": (c_int, [c_void_p] * 2 + [c_int, c_int, c_void_p]),
     "mkb_peer_buffer_bytes": (c_int64, [c_int] * 3),

@@ -635,6 +635,60 @@ extern "C" int mkb_rope_attention_decode(const void* qkv, const int* positions, 
   return MKB_OK;
 }
 
+namespace mkb {
+namespace {
+// best[m] = (max over i of logits[m, i], smallest such i + offset), one CTA of 1024 threads per row.
+// The pair is packed so that an integer maximum orders it: the fp16 value mapped to a sortable key in
+// the high word, the complement of the index in the low word (a tie keeps the smallest index).
+__global__ void __launch_bounds__(1024) argmax_kernel(const __half* __restrict__ logits, int64_t width, int64_t row_stride,
+                                                      int64_t offset, unsigned long long* __restrict__ best) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  __shared__ unsigned long long part_s[32];
+  const __half* row = logits + int64_t(blockIdx.x) * row_stride;
+  unsigned long long top = 0;
+  for (int64_t i = threadIdx.x; i < width; i += blockDim.x) {
+    const unsigned short bits = __half_as_ushort(row[i]);
+    // monotone map of fp16 to unsigned: flip all bits of negatives, the sign bit of the others (NaN ranks lowest)
+    unsigned int key = (bits & 0x8000u) ? (~bits & 0xffffu) : (bits | 0x8000u);
+    if ((bits & 0x7fffu) > 0x7c00u) key = 0;
+    const unsigned long long candidate = (static_cast<unsigned long long>(key) << 32) | (0xffffffffu - static_cast<unsigned int>(i + offset));
+    top = candidate > top ? candidate : top;
+  }
+#pragma unroll
+  for (int step = 16; step; step >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, top, step);
+    top = other > top ? other : top;
+  }
+  if ((threadIdx.x & 31) == 0) part_s[threadIdx.x >> 5] = top;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    top = part_s[threadIdx.x];
+#pragma unroll
+    for (int step = 16; step; step >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, top, step);
+      top = other > top ? other : top;
+    }
+    if (threadIdx.x == 0) best[blockIdx.x] = top;
+  }
+}
+}  // namespace
+}  // namespace mkb
+
+extern "C" int mkb_argmax(const void* logits, void* best, int M, int64_t width, int64_t row_stride, int64_t offset,
+                          void* stream) {
+  using namespace mkb;
+  MKB_REQUIRE(M >= 0 && width >= 1 && row_stride >= width && offset >= 0 && offset + width <= 0xffffffffLL, MKB_E_ARGUMENT,
+              "argmax: bad shape");
+  if (M == 0) return MKB_OK;
+  MKB_REQUIRE(logits && best, MKB_E_ARGUMENT, "argmax: null pointer");
+  const cudaError_t launched = launch_dependent(argmax_kernel, dim3(M), dim3(1024), 0, stream,
+                                                static_cast<const __half*>(logits), width, row_stride, offset,
+                                                static_cast<unsigned long long*>(best));
+  if (launched != cudaSuccess) return cuda_fail(launched, "argmax launch");
+  return MKB_OK;
+}
+
 extern "C" int mkb_decode_status(int* status) {
   using namespace mkb;
   MKB_REQUIRE(status != nullptr, MKB_E_ARGUMENT, "decode_status: null pointer");

@@ -38,7 +38,7 @@ namespace mkb {
 namespace {
 
 constexpr int kMaxWarps = 16;
-constexpr int kMaxClusterVisits = 64;  // bound on the per-CTA sums kept for the cluster exchange
+constexpr int kMaxClusterVisits = 128;  // bound on the per-CTA sums kept for the cluster exchange
 
 struct StreamArgs {
   const __half* x;

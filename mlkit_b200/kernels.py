@@ -317,6 +317,20 @@ def silu_mul(gate_up: Tensor, out: Tensor) -> None:
     _native.check(status, "silu_mul")
 
 
+def argmax_keys(logits: Tensor, best: Tensor, offset: int = 0) -> Tensor:
+    """``best[m]`` (int64 storage of an unsigned word) = sortable key of the row maximum of ``logits``
+    ([M, width] fp16) in the high half, ``0xffffffff - (argmax + offset)`` in the low half."""
+    status = _native.library().mkb_argmax(logits.data_ptr(), best.data_ptr(), logits.shape[0], logits.shape[1],
+                                          logits.stride(0), offset, _stream(logits.device))
+    _native.check(status, "argmax")
+    return best
+
+
+def tokens_of_keys(keys: Tensor) -> Tensor:
+    """The token ids inside ``argmax_keys`` words."""
+    return 0xFFFFFFFF - (keys & 0xFFFFFFFF)
+
+
 def decode_status() -> int:
     """Non-zero when a decode operator since the last call saw a cache position outside ``[0, capacity)``
     (it clamped the position and skipped the append; that step's results are not valid).  Synchronises."""

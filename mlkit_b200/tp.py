@@ -59,6 +59,13 @@ LLAMA3_8B = DecoderConfig(layers=32, hidden=4096, q_heads=32, kv_heads=8, head_d
 # ---------------------------------------------------------------------------------- sharding
 
 
+def best_keys(all_keys: Tensor) -> Tensor:
+    """The unsigned maximum over axis 0 of ``argmax_keys`` words kept in int64 storage: flipping the top
+    bit turns unsigned order into signed order and back."""
+    top = -(1 << 63)
+    return (all_keys ^ top).amax(0) ^ top
+
+
 def rows_of(rank: int, world: int, total: int) -> slice:
     """Rows ``[rank * total / world, (rank + 1) * total / world)`` of a column-parallel projection."""
     share = total // world
@@ -279,6 +286,7 @@ class TensorParallelDecoder:
         self.embedding: Tensor | None = None
         self.final_norm: Tensor | None = None
         self.head: Tensor | None = None
+        self.packed_head: PackedShard | None = None
         self.k_cache: list[Tensor] = []
         self.v_cache: list[Tensor] = []
         self._work: dict[int, dict[str, Tensor]] = {}
@@ -300,11 +308,23 @@ class TensorParallelDecoder:
         self.k_cache.append(torch.zeros(shape, dtype=torch.float16, device=self.device))
         self.v_cache.append(torch.zeros(shape, dtype=torch.float16, device=self.device))
 
-    def set_head(self, embedding: Tensor, final_norm: Tensor, head: Tensor) -> None:
-        """``embedding`` [vocab, hidden] replicated; ``head`` [vocab, hidden] is sharded by rows here."""
+    def set_head(self, embedding: Tensor, final_norm: Tensor, head: "Tensor | Q") -> None:
+        """``embedding`` [vocab, hidden] replicated; ``head`` [vocab, hidden] is sharded by rows here.  A
+        quantised head (a ``Q`` of a scalar codec, as head-quantised checkpoints carry) stays packed:
+        this rank's rows of its code stream feed the packed matvec
+        (``src/mlkit/inference/packed_linear.py:248-287`` runs such a head through ``PackedLinear``)."""
         self.embedding = embedding.to(self.device).half().contiguous()
         self.final_norm = final_norm.to(self.device).half().contiguous()
-        self.head = head[rows_of(self.rank, self.world, head.shape[0])].to(self.device).half().contiguous()
+        if isinstance(head, Q):
+            packed, scales, values, bits, group = _packed_parts(head, self.device)
+            vocab, width = head.codes.shape
+            rows = rows_of(self.rank, self.world, vocab)
+            shard_packed, shard_scales = shard_rows(packed, scales, rows, width, bits)
+            self.packed_head = PackedShard(shard_packed, shard_scales, values, out_rows=vocab // self.world, width=width,
+                                           bits=bits, group=group)
+            self.head = None
+        else:
+            self.head = head[rows_of(self.rank, self.world, head.shape[0])].to(self.device).half().contiguous()
 
     @staticmethod
     def synthetic(config: DecoderConfig, *, rank: int = 0, world: int = 1, device: torch.device | str = "cuda",
@@ -333,6 +353,8 @@ class TensorParallelDecoder:
     def weight_bytes(self) -> int:
         """Bytes this rank streams per decode step: packed codes, scales and its share of the head."""
         total = sum(shard.nbytes for block in self.blocks for shard in block.values())
+        if self.packed_head is not None:
+            total += self.packed_head.nbytes
         return total + (0 if self.head is None else self.head.numel() * 2)
 
     # -- one decode step --
@@ -348,6 +370,8 @@ class TensorParallelDecoder:
                 "o": half(batch, c.hidden), "gate_up": half(batch, 2 * c.intermediate // w),
                 "act": half(batch, c.intermediate // w), "down": half(batch, c.hidden),
                 "logits": half(batch, c.vocab // w),
+                "keys": torch.empty(batch, dtype=torch.int64, device=self.device),
+                "all_keys": torch.empty(w, batch, dtype=torch.int64, device=self.device),
                 "gathered": half(w, batch, c.vocab // w),
             }
         return work
@@ -356,9 +380,11 @@ class TensorParallelDecoder:
         if self.world > 1:
             dist.all_reduce(tensor, group=self.group)
 
-    def step(self, tokens: Tensor, positions: Tensor) -> Tensor:
+    def step(self, tokens: Tensor, positions: Tensor, greedy: bool = False) -> Tensor:
         """Decode one token per sequence: ``tokens`` int64 [batch], ``positions`` int32 [batch] (the
-        cache slot each new token takes).  Returns this step's logits [batch, vocab] in fp16."""
+        cache slot each new token takes).  Returns this step's logits [batch, vocab] in fp16, or, with
+        ``greedy``, the next tokens int64 [batch]: every rank picks the best token of its vocabulary
+        shard and the ranks exchange 8 bytes per sequence instead of their logits."""
         c, w = self.config, self.world
         batch = tokens.shape[0]
         if batch > self.max_batch:
@@ -412,7 +438,17 @@ class TensorParallelDecoder:
             exchange.reduce_add_rmsnorm(delta, residual, self.final_norm, normed, c.eps)
         else:
             kernels.add_rmsnorm(residual, delta, self.final_norm, normed, c.eps)
-        torch.matmul(normed, self.head.t(), out=work["logits"])
+        if self.packed_head is not None:   # a head-quantised checkpoint: the head is one more packed matvec
+            self.packed_head(normed, work["logits"])
+        else:
+            torch.matmul(normed, self.head.t(), out=work["logits"])
+        if greedy:
+            share = work["logits"].shape[1]
+            keys = kernels.argmax_keys(work["logits"], work["keys"], offset=self.rank * share)
+            if w > 1:
+                dist.all_gather_into_tensor(work["all_keys"], keys, group=self.group)
+                keys = best_keys(work["all_keys"])
+            return kernels.tokens_of_keys(keys)
         if w == 1:
             return work["logits"]
         dist.all_gather_into_tensor(work["gathered"], work["logits"], group=self.group)

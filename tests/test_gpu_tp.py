@@ -197,6 +197,33 @@ def test_decoder_matches_dense_reference_and_graph_replay():
     assert model.weight_bytes > 0
 
 
+def test_packed_head_and_greedy_pick():
+    """A head-quantised model: the head is one more packed matvec over this rank's rows of the code
+    stream; the greedy step returns the arg-max of those logits (smallest token on a tie)."""
+    torch.manual_seed(4)
+    config = SMALL
+    blocks = [quantised_block(config, 20 + i) for i in range(config.layers)]
+    embedding = torch.randn(config.vocab, config.hidden, device="cuda").half()
+    final_norm = (torch.rand(config.hidden, device="cuda") + 0.5).half()
+    head_weight = (torch.randn(config.vocab, config.hidden, device="cuda") * 0.05).half()
+    head_q = mk.int(4, group=128)(head_weight.float())
+    dense = build_model(config, blocks, embedding, final_norm, head_q.w.half())
+    packed = build_model(config, blocks, embedding, final_norm, head_q)
+    assert packed.packed_head is not None and packed.head is None
+    tokens = torch.tensor([3, 500, 77, 9], device="cuda")
+    positions = torch.zeros(4, dtype=torch.int32, device="cuda")
+    expected = dense.step(tokens, positions).float()
+    logits = packed.step(tokens, positions).float()
+    assert rel(logits, expected) < 2e-3
+    picked = packed.step(tokens, positions, greedy=True)
+    assert picked.dtype == torch.int64 and torch.equal(picked, logits.argmax(-1))
+    # the key orders like the fp16 value, negative maxima included; a tie keeps the smallest index
+    rows = torch.tensor([[-3.0, -1.5, -7.0, -1.5], [0.0, -0.0, -2.0, -1.0], [5.0, 65504.0, 2.0, 65504.0]], device="cuda").half()
+    keys = kernels.argmax_keys(rows, torch.empty(3, dtype=torch.int64, device="cuda"), offset=10)
+    assert kernels.tokens_of_keys(keys).tolist() == [11, 10, 11]
+    assert (keys[2] ^ (1 << 63)) > (keys[1] ^ (1 << 63)) > (keys[0] ^ (1 << 63))
+
+
 def test_decoder_refuses_positions_outside_the_cache():
     """The host check of an eager step; no out-of-range position ever reaches a kernel here."""
     config = SMALL

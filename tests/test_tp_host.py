@@ -51,6 +51,20 @@ def _worker(rank: int, world: int, port: int, failures) -> None:
         dist.all_gather(pieces, torch.from_numpy(mine.astype(np.float32)))
         assert matvec.relative_l2(torch.cat(pieces, 1).numpy(), full) < 1e-6
 
+        # greedy pick over vocabulary shards: every rank contributes 8 bytes per sequence (the sortable
+        # key of its best logit and the complement of its token id); the unsigned maximum wins
+        logits = torch.tensor([[0.5, -2.0, 3.0, 3.0, -1.0, 2.5, 3.0, 0.0], [-4.0, -1.0, -3.0, -2.0, -1.0, -6.0, -7.0, -8.0]])
+        share = logits.shape[1] // world
+        local = logits[:, rank * share:(rank + 1) * share].half()
+        bits = local.view(torch.int16).to(torch.int64) & 0xFFFF
+        key = torch.where(bits >= 0x8000, ~bits & 0xFFFF, bits | 0x8000)          # the kernel's map of fp16 to unsigned
+        words = (key << 32) | (0xFFFFFFFF - (torch.arange(share) + rank * share))
+        best = tp.best_keys(words.t())   # this rank's best word per sequence
+        gathered = [torch.empty_like(best) for _ in range(world)]
+        dist.all_gather(gathered, best)
+        winners = 0xFFFFFFFF - (tp.best_keys(torch.stack(gathered)) & 0xFFFFFFFF)
+        assert winners.tolist() == [2, 1]   # ties keep the smallest token; negative maxima order correctly
+
         # a rank that fails between steps is seen by the others through the store, not through a hang
         store = dist.distributed_c10d._get_default_store()
         store.set(f"alive{rank}", "1")
