@@ -65,12 +65,12 @@ int launch_gemv_bulk(const void* x, const uint8_t* packed, const void* scales, c
                      int64_t packed_row_stride, int64_t scale_row_stride, float grid_minimum, cudaStream_t stream);
 bool prefer_bulk(int M, int N, int K);
 
-int gemv_stream_supported(int M, int N, int K, int group, int bits, int x_dtype, int scale_dtype, const void* x,
-                          const uint8_t* packed, const void* scales, int64_t packed_row_stride,
+int gemv_stream_supported(int M, int N, int K, int group, int bits, int lut_len, int x_dtype, int scale_dtype,
+                          const void* x, const uint8_t* packed, const void* scales, int64_t packed_row_stride,
                           int64_t scale_row_stride, const void* zeros, int integer_grid, float grid_minimum);
-int launch_gemv_stream(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y, int M,
-                       int N, int K, int64_t packed_row_stride, int64_t scale_row_stride, float grid_minimum,
-                       int gated, cudaStream_t stream);
+int launch_gemv_stream(const void* x, const uint8_t* packed, const void* scales, const float* lut, const void* bias,
+                       void* y, int M, int N, int K, int group, int bits, int lut_len, int64_t packed_row_stride,
+                       int64_t scale_row_stride, int integer_grid, float grid_minimum, int gated, cudaStream_t stream);
 
 }  // namespace mkb
 
@@ -138,14 +138,13 @@ extern "C" int mkb_gemv_ws(const void* x, const uint8_t* packed, const void* sca
               "gemv: K=%d or group=%d splits a packing word of %d-bit codes", K, group, bits);
   MKB_REQUIRE(K > 0, MKB_E_UNSUPPORTED, "gemv: empty reduction");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool stream_ok = lut_len == (1 << bits) &&
-                         gemv_stream_supported(M, N, K, group, bits, x_dtype, scale_dtype, x, packed, scales,
+  const bool stream_ok = gemv_stream_supported(M, N, K, group, bits, lut_len, x_dtype, scale_dtype, x, packed, scales,
                                                packed_row_stride, scale_row_stride, zeros, integer_grid, grid_minimum);
   if (kernel == MKB_GEMV_STREAM)
     MKB_REQUIRE(stream_ok, MKB_E_UNSUPPORTED, "gemv: the streaming kernel does not cover these arguments");
   if (kernel == MKB_GEMV_STREAM || (kernel == MKB_GEMV_AUTO && stream_ok))
-    return launch_gemv_stream(x, packed, scales, bias, y, M, N, K, packed_row_stride, scale_row_stride,
-                              grid_minimum, gated, s);
+    return launch_gemv_stream(x, packed, scales, lut, bias, y, M, N, K, group, bits, lut_len, packed_row_stride,
+                              scale_row_stride, integer_grid, grid_minimum, gated, s);
   const bool tiled_ok = gemv_tiled_supported(M, K, group, bits, x_dtype, scale_dtype, x, packed, packed_row_stride);
   const bool tmem_ok = workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) % 16) == 0 && lut_len == 16 &&
                        gemv_umma_supported(M, K, group, bits, x_dtype, scale_dtype, x, packed, packed_row_stride, zeros,

@@ -45,6 +45,8 @@ struct StreamArgs {
   const uint8_t* packed;
   const __half* scales;
   const __half* bias;
+  const float* lut;   // table codecs: the levels
+  int lut_len;
   __half* y;
   int M, N, K;
   int64_t packed_row_stride, scale_row_stride;
@@ -91,20 +93,36 @@ __device__ __forceinline__ void mma_next(float (&d)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Geometry of one visit of one warp: 16 rows x KT k-tiles of 128 codes.
-template <int BITS, int KT>
+// How codes become tensor-core operands.
+//   RAW   integer grids (lut[c] = min + c) of 2, 4 or 8 bits with one scale per 128 codes: masked bits
+//         used as fp16 subnormals (see the head of this file); the scale multiplies the k-tile sum.
+//   TABLE any table of at most 16 levels with 3- or 4-bit codes and one scale per 64 or 128 codes: a
+//         pair of neighbouring codes indexes a shared-memory table of fp16 pairs (one copy per lane,
+//         so the gather has no bank conflicts), the pair is multiplied by the fp16 scale of its row
+//         group, and the products accumulate directly.  The table holds fp16(lut[c]): the matvec is
+//         within the 2e-3 bound of reconstruct-then-matmul, not bit-equal to it (the dequantisation
+//         kernel is the bit-exact route).
+enum { MODE_RAW = 0, MODE_TABLE = 1 };
+
+// Geometry of one visit of one warp: 16 rows x KT k-tiles of 128 codes.  GPT = scale groups per k-tile.
+template <int BITS, int MODE, int GPT, int KT>
 struct Visit {
   static constexpr int TILE_ROW_BYTES = 16 * BITS;               // 128 codes of one row
+  static constexpr int LANE_BYTES = 4 * BITS;                    // a lane's 32 codes of one row
   static constexpr int TILE_BYTES = 16 * TILE_ROW_BYTES;         // 16 rows
   static constexpr int SEGMENT = KT * TILE_ROW_BYTES;            // contiguous bytes of one row per visit
-  static constexpr int LANES_PER_ROW = SEGMENT / 16;             // 16-byte vectors per row segment
-  static constexpr int ROWS_PER_COPY = 32 / LANES_PER_ROW;       // rows one copy instruction of a warp covers
-  static constexpr int COPIES = 16 / ROWS_PER_COPY;              // copy instructions per lane and visit
-  static constexpr int SCALE_OFFSET = KT * TILE_BYTES;            // 16 rows x 4 bytes of scales follow the codes
-  static constexpr int SLOT_BYTES = KT * TILE_BYTES + 64;
+  static constexpr int VECTORS_PER_ROW = SEGMENT / 16;           // 16-byte vectors per row segment
   static constexpr int VECTORS_PER_TILE_ROW = TILE_ROW_BYTES / 16;
-  static_assert(BITS == 4, "only 4-bit codes are laid out so far");
-  static_assert(LANES_PER_ROW >= 4 && LANES_PER_ROW <= 16 && ROWS_PER_COPY % 2 == 0, "visit geometry");
+  static constexpr int VECTORS = 16 * VECTORS_PER_ROW;           // per visit and warp
+  static constexpr int COPIES = (VECTORS + 31) / 32;             // copy instructions per lane and visit
+  // the scales of a visit follow its codes: 16 rows x SCALE_ROW_BYTES (at least one 4-byte copy)
+  static constexpr int SCALE_ROW_BYTES = KT * GPT * 2 < 4 ? 4 : KT * GPT * 2;
+  static constexpr int SCALE_OFFSET = KT * TILE_BYTES;
+  static constexpr int SLOT_BYTES = KT * TILE_BYTES + 16 * SCALE_ROW_BYTES;
+  [[maybe_unused]] static constexpr int CLASSES = MODE == MODE_RAW ? (BITS == 4 ? 2 : BITS == 2 ? 4 : 1) : 1;
+  [[maybe_unused]] static constexpr int TABLE_ENTRIES = MODE == MODE_TABLE ? (1 << (2 * BITS)) : 0;   // pairs of codes
+  static_assert(SEGMENT % 16 == 0 && SLOT_BYTES % 16 == 0, "visit geometry");
+  static_assert(MODE == MODE_TABLE ? (BITS == 3 || BITS == 4) : (BITS == 2 || BITS == 4 || BITS == 8), "codec");
 };
 
 __device__ __forceinline__ uint4 load_shared16(uint32_t address) {
@@ -117,14 +135,39 @@ __device__ __forceinline__ uint32_t load_shared4(uint32_t address) {
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(address));
   return v;
 }
+__device__ __forceinline__ uint2 load_shared8(uint32_t address) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(address));
+  return v;
+}
+__device__ __forceinline__ uint32_t load_shared2(uint32_t address) {
+  uint32_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(address));
+  return v;
+}
+__device__ __forceinline__ void copy8(uint32_t smem_address, const void* global) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_address), "l"(global) : "memory");
+}
 __device__ __forceinline__ void store_shared16(uint32_t address, float a, float b, float c, float d) {
   asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(address), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-template <int BITS, int KT, int R>
+// Position of 16-byte vector `vector` of row `row` inside k-tile `tile` of a slot.  The layouts keep
+// the copies (a warp writes whole 128-byte lines) and the fragment reads (a lane reads its 32 codes
+// of rows g and g + 8) free of bank conflicts: 4-bit rows of odd k-tiles swap with their neighbour,
+// 8-bit rows keep their vectors swapped in pairs on odd rows.
+template <int BITS>
+__host__ __device__ constexpr uint32_t tile_offset(int tile, int row, int vector) {
+  if (BITS == 4) return uint32_t(tile) * 1024u + uint32_t(row ^ (tile & 1)) * 64u + uint32_t(vector) * 16u;
+  if (BITS == 8) return uint32_t(tile) * 2048u + uint32_t(row) * 128u + uint32_t(vector ^ (row & 1)) * 16u;
+  return uint32_t(tile) * (256u * BITS) + uint32_t(row) * (16u * BITS) + uint32_t(vector) * 16u;
+}
+
+template <int BITS, int MODE, int GPT, int KT, int R>
 __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const StreamArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
-  using V = Visit<BITS, KT>;
+  using V = Visit<BITS, MODE, GPT, KT>;
+  constexpr bool RAW = MODE == MODE_RAW;
   // dependents may become resident at once: they only copy constants until their own wait returns
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -143,34 +186,37 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
   if (k_warp >= a.k_warps) my_visits = 0;
   const int whole_visits = (a.N & 15) ? my_visits - 1 : my_visits;
 
-  // shared memory: rings [warp][R][slot], partial sums [warp][batch][128], cluster sums [visit][RG][128]
+  // shared memory: rings [warp][R][slot], partial sums [warp][batch][128], cluster sums [visit][RG][128],
+  // then the pair table [entry][lane] of the table codecs
   const uint32_t smem_base = uint32_t(__cvta_generic_to_shared(smem));
   const uint32_t ring_base = smem_base + warp * R * V::SLOT_BYTES;
   float* red_s = reinterpret_cast<float*>(smem + size_t(warps) * R * V::SLOT_BYTES);
   const uint32_t red_base = smem_base + warps * R * V::SLOT_BYTES;
   float* acc_s = red_s + size_t(warps) * a.batch * 128;
+  const uint32_t table_base = red_base + (warps * a.batch + (a.slabs > 1 ? a.visits * a.RG : 0)) * 512;
 
-  // ---- copy side: lane -> (row within a copy, 16-byte column of the row segment) ----
-  const int copy_row = lane / V::LANES_PER_ROW, copy_column = lane % V::LANES_PER_ROW;
-  const int copy_tile = copy_column / V::VECTORS_PER_TILE_ROW, copy_vector = copy_column % V::VECTORS_PER_TILE_ROW;
-  // odd k-tiles of a visit keep rows r and r^1 swapped: the two halves of a 128-byte line then land
-  // in different banks, and a fragment read (rows g, g^1 of one tile) still covers 128 contiguous bytes
-  const uint32_t copy_to = ring_base + copy_tile * V::TILE_BYTES + ((copy_row ^ (copy_tile & 1)) * V::TILE_ROW_BYTES) +
-                           copy_vector * 16;
+  // ---- copy side: vector v = i * 32 + lane of the visit's 16 x SEGMENT bytes -> (row, column) ----
   // one 64-bit source per copy of a lane; a visit adds visit * step with one multiply-add (no carries
   // to propagate on the integer pipe, which the code expansion needs for itself)
   const uint8_t* copy_base[V::COPIES];
+  uint32_t copy_to[V::COPIES];
+  uint32_t copy_rows = 0;   // row of copy i in bits [4i, 4i + 4)
 #pragma unroll
-  for (int i = 0; i < V::COPIES; ++i)
-    copy_base[i] = a.packed + int64_t(first_row_tile * 16 + i * V::ROWS_PER_COPY + copy_row) * a.packed_row_stride +
-                   int64_t(tile0) * V::TILE_ROW_BYTES + copy_column * 16;
+  for (int i = 0; i < V::COPIES; ++i) {
+    const int vector = i * 32 + lane, row = vector / V::VECTORS_PER_ROW, column = vector % V::VECTORS_PER_ROW;
+    copy_base[i] = a.packed + int64_t(first_row_tile * 16 + row) * a.packed_row_stride +
+                   int64_t(tile0) * V::TILE_ROW_BYTES + column * 16;
+    copy_to[i] = ring_base + tile_offset<BITS>(column / V::VECTORS_PER_TILE_ROW, row, column % V::VECTORS_PER_TILE_ROW);
+    copy_rows |= uint32_t(row) << (4 * i);
+  }
   const uint32_t copy_visit_step = uint32_t(visit_stride) * 16u * uint32_t(a.packed_row_stride);
-  // the scales of a visit ride in its slot: lane r < 16 copies the 4 bytes that hold row r's KT scales
-  // (for KT == 1 the aligned pair around the one scale), so they arrive as early as the weights do
-  const int64_t scale_index = int64_t(first_row_tile * 16 + (lane & 15)) * a.scale_row_stride + tile0;
-  const __half* scale_base = a.scales + (scale_index & ~int64_t(1));
+  // the scales of a visit ride in its slot: lane r < 16 copies the SCALE_ROW_BYTES that hold row r's
+  // scales of the visit (for a single scale the aligned pair around it), so they arrive with the weights
+  constexpr int SCALES = KT * GPT;   // scales per row and visit
+  const int64_t scale_index = int64_t(first_row_tile * 16 + (lane & 15)) * a.scale_row_stride + int64_t(tile0) * GPT;
+  const __half* scale_base = a.scales + (SCALES == 1 ? scale_index & ~int64_t(1) : scale_index);
   const uint32_t scale_visit_step = uint32_t(visit_stride) * 32u * uint32_t(a.scale_row_stride);  // bytes
-  const uint32_t scale_to = ring_base + V::SCALE_OFFSET + (lane & 15) * 4;
+  const uint32_t scale_to = ring_base + V::SCALE_OFFSET + (lane & 15) * V::SCALE_ROW_BYTES;
   const bool copies_scales = lane < 16;
   // `exists`: the warp owns this visit.  `whole` == false: rows past N are left out (their slots keep
   // stale bytes; the sums of such rows are never stored).
@@ -179,11 +225,15 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
       const int first_row = whole ? 0 : (first_row_tile + visit * visit_stride) * 16;
 #pragma unroll
       for (int i = 0; i < V::COPIES; ++i)
-        if (whole || first_row + i * V::ROWS_PER_COPY + copy_row < a.N)
-          copy16(copy_to + slot * V::SLOT_BYTES + i * V::ROWS_PER_COPY * V::TILE_ROW_BYTES,
-                 offset_pointer(copy_base[i], uint32_t(visit), copy_visit_step));
-      if (copies_scales && (whole || first_row + (lane & 15) < a.N))
-        copy4(scale_to + slot * V::SLOT_BYTES, offset_pointer(scale_base, uint32_t(visit), scale_visit_step));
+        if ((V::VECTORS % 32 == 0 || i * 32 + lane < V::VECTORS) &&
+            (whole || first_row + int((copy_rows >> (4 * i)) & 15u) < a.N))
+          copy16(copy_to[i] + slot * V::SLOT_BYTES, offset_pointer(copy_base[i], uint32_t(visit), copy_visit_step));
+      if (copies_scales && (whole || first_row + (lane & 15) < a.N)) {
+        const __half* from = offset_pointer(scale_base, uint32_t(visit), scale_visit_step);
+        if constexpr (V::SCALE_ROW_BYTES == 4) copy4(scale_to + slot * V::SLOT_BYTES, from);
+        else if constexpr (V::SCALE_ROW_BYTES == 8) copy8(scale_to + slot * V::SLOT_BYTES, from);
+        else copy16(scale_to + slot * V::SLOT_BYTES, from);
+      }
     }
     copy_commit();  // one group per visit, empty past the end, so the pending count stays exact
   };
@@ -191,10 +241,20 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
   for (int d = 0; d < R - 1; ++d)
     if (d < a.early) issue(d, d, d < my_visits, d < whole_visits);
 
+  // ---- the pair table of the table codecs: entry (lo | hi << BITS) = fp16 (lut[lo], lut[hi]) ----
+  if constexpr (!RAW) {
+    __half2* table = reinterpret_cast<__half2*>(smem + (table_base - smem_base));
+    for (int index = threadIdx.x; index < V::TABLE_ENTRIES * 32; index += blockDim.x) {
+      const int entry = index >> 5, lo = entry & ((1 << BITS) - 1), hi = entry >> BITS;
+      table[index] = __floats2half2_rn(lo < a.lut_len ? a.lut[lo] : 0.f, hi < a.lut_len ? a.lut[hi] : 0.f);
+    }
+    __syncthreads();
+  }
+
   // ---- activations: the B fragments of this warp's k-tiles, permuted in registers ----
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  uint32_t b[KT][4][4];   // [k-tile][word][pairs (x0,x4) (x2,x6) (x1,x5) (x3,x7)]
-  float start[KT][4];     // accumulator start: min * sum(x) * 2^-24 for activation rows 2t, 2t+1 (twice)
+  uint32_t b[KT][16];     // tensor-core step s of a k-tile multiplies by b[2s], b[2s + 1]
+  float start[KT][4];     // RAW: accumulator start, min * sum(x) * 2^-24 for activation rows 2t, 2t+1 (twice)
   {
     const __half* x_lane = a.x + int64_t(g) * (a.gated ? 2 * a.K : a.K) + int64_t(tile0) * 128 + t * 32;
     const bool has_x = my_visits > 0 && g < a.M;
@@ -224,39 +284,164 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
     const float unit = a.grid_min * 5.9604644775390625e-08f;   // min * 2^-24: the unit of the accumulators
 #pragma unroll
     for (int kk = 0; kk < KT; ++kk) {
+      const uint32_t r[16] = {v[kk][0].x, v[kk][0].y, v[kk][0].z, v[kk][0].w, v[kk][1].x, v[kk][1].y, v[kk][1].z, v[kk][1].w,
+                              v[kk][2].x, v[kk][2].y, v[kk][2].z, v[kk][2].w, v[kk][3].x, v[kk][3].y, v[kk][3].z, v[kk][3].w};
+      if constexpr (RAW && BITS == 4) {
+        // a mask keeps codes (c, c + 4) of a word of 8: pairs (x0,x4) (x2,x6) for the even codes, (x1,x5) (x3,x7) for the odd
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        b[kk][w][0] = __byte_perm(v[kk][w].x, v[kk][w].z, 0x5410);
-        b[kk][w][1] = __byte_perm(v[kk][w].y, v[kk][w].w, 0x5410);
-        b[kk][w][2] = __byte_perm(v[kk][w].x, v[kk][w].z, 0x7632);
-        b[kk][w][3] = __byte_perm(v[kk][w].y, v[kk][w].w, 0x7632);
+        for (int w = 0; w < 4; ++w) {
+          b[kk][4 * w + 0] = __byte_perm(r[4 * w], r[4 * w + 2], 0x5410);
+          b[kk][4 * w + 1] = __byte_perm(r[4 * w + 1], r[4 * w + 3], 0x5410);
+          b[kk][4 * w + 2] = __byte_perm(r[4 * w], r[4 * w + 2], 0x7632);
+          b[kk][4 * w + 3] = __byte_perm(r[4 * w + 1], r[4 * w + 3], 0x7632);
+        }
+      } else if constexpr (RAW && BITS == 2) {
+        // a mask keeps codes (i, i + 8) of a word of 16; step 4 * word + i also takes (i + 4, i + 12)
+#pragma unroll
+        for (int word = 0; word < 2; ++word)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t selector = (i & 1) ? 0x7632 : 0x5410;
+            b[kk][2 * (4 * word + i) + 0] = __byte_perm(r[8 * word + i / 2], r[8 * word + i / 2 + 4], selector);
+            b[kk][2 * (4 * word + i) + 1] = __byte_perm(r[8 * word + i / 2 + 2], r[8 * word + i / 2 + 6], selector);
+          }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) b[kk][j] = r[j];   // neighbouring codes pair up: the natural order
       }
-      // sum of the k-tile's activations per activation row, on the tensor cores: a weight tile of ones
-      // gives every weight row the same sums, laid out as the accumulators want them
-      constexpr uint32_t ones = 0x3c003c00u;
-      float sums[4];
-      mma_first(sums, ones, ones, ones, ones, b[kk][0][0], b[kk][0][1], 0.f, 0.f, 0.f, 0.f);
-      mma_next(sums, ones, ones, ones, ones, b[kk][0][2], b[kk][0][3]);
+      if constexpr (RAW) {
+        // sum of the k-tile's activations per activation row, on the tensor cores: a weight tile of ones
+        // gives every weight row the same sums, laid out as the accumulators want them
+        constexpr uint32_t ones = 0x3c003c00u;
+        float sums[4];
+        mma_first(sums, ones, ones, ones, ones, b[kk][0], b[kk][1], 0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int w = 1; w < 4; ++w) {
-        mma_next(sums, ones, ones, ones, ones, b[kk][w][0], b[kk][w][1]);
-        mma_next(sums, ones, ones, ones, ones, b[kk][w][2], b[kk][w][3]);
+        for (int step = 1; step < 8; ++step) mma_next(sums, ones, ones, ones, ones, b[kk][2 * step], b[kk][2 * step + 1]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) start[kk][q] = sums[q] * unit;
       }
-#pragma unroll
-      for (int q = 0; q < 4; ++q) start[kk][q] = sums[q] * unit;
     }
   }
 
-  // ---- fragment side: lane (g, t) reads 16 bytes of rows g and g + 8 of every k-tile ----
-  const uint32_t read_begin = ring_base + g * V::TILE_ROW_BYTES + t * 16;
-  const uint32_t odd_flip = (((g ^ 1) - g) * V::TILE_ROW_BYTES);  // rows g and g^1 are swapped in odd k-tiles
-  // this lane's scales: rows g and g + 8, halves kk of the 4-byte entries (KT == 1: the half the
-  // aligned pair keeps the wanted scale in; it is the same in every visit, the visit step being even)
-  const uint32_t scale_begin = ring_base + V::SCALE_OFFSET + g * 4;
-  const int64_t index_low = int64_t(first_row_tile * 16 + g) * a.scale_row_stride + tile0;
+  // ---- fragment side: lane (g, t) reads its 32 codes of rows g and g + 8 of every k-tile ----
+  const uint32_t table_lane = table_base + lane * 4;
+  // scales of rows g and g + 8 in the slot; a single scale per row and visit sits in the half of an
+  // aligned pair that the parity of its index says (the same in every visit, the visit step being even)
+  const uint32_t scale_begin = ring_base + V::SCALE_OFFSET + g * V::SCALE_ROW_BYTES;
+  const int64_t index_low = int64_t(first_row_tile * 16 + g) * a.scale_row_stride + int64_t(tile0) * GPT;
   const int64_t index_high = index_low + 8 * a.scale_row_stride;
-  const bool high_half_0 = KT == 1 && (index_low & 1), high_half_1 = KT == 1 && (index_high & 1);
+  const uint32_t odd_scale_0 = SCALES == 1 && (index_low & 1) ? 2u : 0u, odd_scale_1 = SCALES == 1 && (index_high & 1) ? 2u : 0u;
   const uint32_t red_to = red_base + ((warp * a.batch) * 128 + lane * 4) * 4;
+
+  // One k-tile of one visit: `slot_at` is the shared address of the visit's slot.
+  auto tile_product = [&](uint32_t slot_at, int kk, float (&y)[4]) {
+    const uint32_t scales_at = slot_at + (scale_begin - ring_base);
+    if constexpr (RAW) {
+      const float f0 = __half2float(__ushort_as_half((unsigned short)load_shared2(scales_at + kk * 2 + odd_scale_0)));
+      const float f1 = __half2float(__ushort_as_half((unsigned short)load_shared2(scales_at + 8 * V::SCALE_ROW_BYTES + kk * 2 + odd_scale_1)));
+      float acc[V::CLASSES][4];
+      if constexpr (BITS == 4) {
+        const uint4 lo = load_shared16(slot_at + tile_offset<4>(kk, g, t)), hi = load_shared16(slot_at + tile_offset<4>(kk, g + 8, t));
+        const uint32_t q[4] = {lo.x, lo.y, lo.z, lo.w}, p[4] = {hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const uint32_t q8 = q[w] >> 8, p8 = p[w] >> 8;  // codes 2, 3, 6, 7 of a word move down one byte
+          if (w == 0) {
+            mma_first(acc[0], q[w] & 0x000f000fu, p[w] & 0x000f000fu, q8 & 0x000f000fu, p8 & 0x000f000fu,
+                      b[kk][0], b[kk][1], start[kk][0], start[kk][1], start[kk][2], start[kk][3]);
+            mma_first(acc[1], q[w] & 0x00f000f0u, p[w] & 0x00f000f0u, q8 & 0x00f000f0u, p8 & 0x00f000f0u,
+                      b[kk][2], b[kk][3], 0.f, 0.f, 0.f, 0.f);
+          } else {
+            mma_next(acc[0], q[w] & 0x000f000fu, p[w] & 0x000f000fu, q8 & 0x000f000fu, p8 & 0x000f000fu,
+                     b[kk][4 * w], b[kk][4 * w + 1]);
+            mma_next(acc[1], q[w] & 0x00f000f0u, p[w] & 0x00f000f0u, q8 & 0x00f000f0u, p8 & 0x00f000f0u,
+                     b[kk][4 * w + 2], b[kk][4 * w + 3]);
+          }
+        }
+      } else if constexpr (BITS == 8) {
+        // a byte is the fp16 subnormal c * 2^-24 once it sits in the low byte of a 16-bit lane
+        const uint4 lo0 = load_shared16(slot_at + tile_offset<8>(kk, g, 2 * t)), lo1 = load_shared16(slot_at + tile_offset<8>(kk, g, 2 * t + 1));
+        const uint4 hi0 = load_shared16(slot_at + tile_offset<8>(kk, g + 8, 2 * t)), hi1 = load_shared16(slot_at + tile_offset<8>(kk, g + 8, 2 * t + 1));
+        const uint32_t q[8] = {lo0.x, lo0.y, lo0.z, lo0.w, lo1.x, lo1.y, lo1.z, lo1.w};
+        const uint32_t p[8] = {hi0.x, hi0.y, hi0.z, hi0.w, hi1.x, hi1.y, hi1.z, hi1.w};
+#pragma unroll
+        for (int step = 0; step < 8; ++step) {
+          const uint32_t a0 = __byte_perm(q[step], 0u, 0x4140), a1 = __byte_perm(p[step], 0u, 0x4140);
+          const uint32_t a2 = __byte_perm(q[step], 0u, 0x4342), a3 = __byte_perm(p[step], 0u, 0x4342);
+          if (step == 0) mma_first(acc[0], a0, a1, a2, a3, b[kk][0], b[kk][1], start[kk][0], start[kk][1], start[kk][2], start[kk][3]);
+          else mma_next(acc[0], a0, a1, a2, a3, b[kk][2 * step], b[kk][2 * step + 1]);
+        }
+      } else {  // BITS == 2: codes of equal position in their byte share a lift of 4^i and an accumulator
+        const uint2 lo = load_shared8(slot_at + tile_offset<2>(kk, g, 0) + t * 8), hi = load_shared8(slot_at + tile_offset<2>(kk, g + 8, 0) + t * 8);
+        const uint32_t q[2] = {lo.x, lo.y}, p[2] = {hi.x, hi.y};
+#pragma unroll
+        for (int word = 0; word < 2; ++word) {
+          const uint32_t q8 = q[word] >> 8, p8 = p[word] >> 8;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t mask = 0x00030003u << (2 * i);
+            const int step = 4 * word + i;
+            if (word == 0 && i == 0)
+              mma_first(acc[0], q[word] & mask, p[word] & mask, q8 & mask, p8 & mask, b[kk][0], b[kk][1],
+                        start[kk][0], start[kk][1], start[kk][2], start[kk][3]);
+            else if (word == 0)
+              mma_first(acc[i], q[word] & mask, p[word] & mask, q8 & mask, p8 & mask, b[kk][2 * step], b[kk][2 * step + 1],
+                        0.f, 0.f, 0.f, 0.f);
+            else
+              mma_next(acc[i], q[word] & mask, p[word] & mask, q8 & mask, p8 & mask, b[kk][2 * step], b[kk][2 * step + 1]);
+          }
+        }
+      }
+      // classes of higher lift were c * 2^-24 times a power of two: recombine exactly (Horner), then one
+      // scale per row and k-tile
+      constexpr float down = BITS == 4 ? 0.0625f : 0.25f;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float total = acc[V::CLASSES - 1][q];
+#pragma unroll
+        for (int c = V::CLASSES - 2; c >= 0; --c) total = fmaf(total, down, acc[c][q]);
+        y[q] = fmaf(q < 2 ? f0 : f1, total, y[q]);
+      }
+    } else {
+      // table codecs: a pair of codes -> fp16 pair from the lane's copy of the table, times the scale of
+      // the lane's row group; the products accumulate directly
+      const uint32_t group_of_lane = (t * GPT) >> 2;   // scale group of codes 32t .. 32t+31 inside the k-tile
+      const uint32_t s0 = load_shared2(scales_at + (kk * GPT + group_of_lane) * 2 + odd_scale_0);
+      const uint32_t s1 = load_shared2(scales_at + 8 * V::SCALE_ROW_BYTES + (kk * GPT + group_of_lane) * 2 + odd_scale_1);
+      const uint32_t scale_0 = s0 | (s0 << 16), scale_1 = s1 | (s1 << 16);
+      const __half2 f0 = *reinterpret_cast<const __half2*>(&scale_0), f1 = *reinterpret_cast<const __half2*>(&scale_1);
+      auto weight_pair = [&](uint32_t entry, __half2 scale) -> uint32_t {
+        const uint32_t bits = load_shared4(table_lane + entry * 128u);
+        const __half2 scaled = __hmul2(*reinterpret_cast<const __half2*>(&bits), scale);
+        return *reinterpret_cast<const uint32_t*>(&scaled);
+      };
+      if constexpr (BITS == 4) {
+        const uint4 lo = load_shared16(slot_at + tile_offset<4>(kk, g, t)), hi = load_shared16(slot_at + tile_offset<4>(kk, g + 8, t));
+        const uint32_t q[4] = {lo.x, lo.y, lo.z, lo.w}, p[4] = {hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+        for (int step = 0; step < 8; ++step) {   // bytes 2 * step and 2 * step + 1 of the lane's 16
+          const int w = step >> 1, low = (step & 1) ? 0x4442 : 0x4440, high = (step & 1) ? 0x4443 : 0x4441;
+          mma_next(y, weight_pair(__byte_perm(q[w], 0u, low), f0), weight_pair(__byte_perm(p[w], 0u, low), f1),
+                   weight_pair(__byte_perm(q[w], 0u, high), f0), weight_pair(__byte_perm(p[w], 0u, high), f1),
+                   b[kk][2 * step], b[kk][2 * step + 1]);
+        }
+      } else {  // BITS == 3: 32 codes are 96 bits; pair j is the 6-bit field at bit 6 j
+        const uint32_t at0 = slot_at + tile_offset<3>(kk, g, 0) + t * 12, at1 = slot_at + tile_offset<3>(kk, g + 8, 0) + t * 12;
+        const uint32_t q[3] = {load_shared4(at0), load_shared4(at0 + 4), load_shared4(at0 + 8)};
+        const uint32_t p[3] = {load_shared4(at1), load_shared4(at1 + 4), load_shared4(at1 + 8)};
+        auto field = [](const uint32_t (&w)[3], int j) -> uint32_t {
+          const int bit = 6 * j, word = bit >> 5, shift = bit & 31;
+          const uint32_t value = shift + 6 <= 32 ? w[word] >> shift : __funnelshift_r(w[word], w[word + 1], shift);
+          return value & 63u;
+        };
+#pragma unroll
+        for (int step = 0; step < 8; ++step)
+          mma_next(y, weight_pair(field(q, 2 * step), f0), weight_pair(field(p, 2 * step), f1),
+                   weight_pair(field(q, 2 * step + 1), f0), weight_pair(field(p, 2 * step + 1), f1),
+                   b[kk][2 * step], b[kk][2 * step + 1]);
+      }
+    }
+  };
 
   // One round: R visits, unrolled over the ring, so every shared-memory offset is an immediate.  With
   // CHECKED == false the caller promises that this warp owns every visit of the round and every visit
@@ -272,39 +457,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
       __syncwarp();  // the lanes' copies of this visit are visible to the whole warp
       float y[4] = {0.f, 0.f, 0.f, 0.f};
       if (!CHECKED || visit < my_visits) {
-        const uint32_t read_from = read_begin + d * V::SLOT_BYTES, scale_at = scale_begin + d * V::SLOT_BYTES;
-        const uint32_t scale_bits_0 = load_shared4(scale_at), scale_bits_1 = load_shared4(scale_at + 32);
-        const __half2 s0 = *reinterpret_cast<const __half2*>(&scale_bits_0);
-        const __half2 s1 = *reinterpret_cast<const __half2*>(&scale_bits_1);
 #pragma unroll
-        for (int kk = 0; kk < KT; ++kk) {
-          const uint32_t tile = read_from + kk * V::TILE_BYTES + ((kk & 1) ? odd_flip : 0u);
-          const uint4 lo = load_shared16(tile), hi = load_shared16(tile + 8 * V::TILE_ROW_BYTES);
-          const uint32_t q[4] = {lo.x, lo.y, lo.z, lo.w}, p[4] = {hi.x, hi.y, hi.z, hi.w};
-          float even[4], odd[4];
-#pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            const uint32_t q8 = q[w] >> 8, p8 = p[w] >> 8;  // codes 2, 3, 6, 7 of a word move down one byte
-            if (w == 0) {
-              mma_first(even, q[w] & 0x000f000fu, p[w] & 0x000f000fu, q8 & 0x000f000fu, p8 & 0x000f000fu,
-                        b[kk][w][0], b[kk][w][1], start[kk][0], start[kk][1], start[kk][2], start[kk][3]);
-              mma_first(odd, q[w] & 0x00f000f0u, p[w] & 0x00f000f0u, q8 & 0x00f000f0u, p8 & 0x00f000f0u,
-                        b[kk][w][2], b[kk][w][3], 0.f, 0.f, 0.f, 0.f);
-            } else {
-              mma_next(even, q[w] & 0x000f000fu, p[w] & 0x000f000fu, q8 & 0x000f000fu, p8 & 0x000f000fu,
-                       b[kk][w][0], b[kk][w][1]);
-              mma_next(odd, q[w] & 0x00f000f0u, p[w] & 0x00f000f0u, q8 & 0x00f000f0u, p8 & 0x00f000f0u,
-                       b[kk][w][2], b[kk][w][3]);
-            }
-          }
-          // odd codes were c * 2^-20, 16 times the unit: recombine exactly, then one scale per row and k-tile
-          const float f0 = (KT == 1 ? high_half_0 : (kk & 1)) ? __high2float(s0) : __low2float(s0);
-          const float f1 = (KT == 1 ? high_half_1 : (kk & 1)) ? __high2float(s1) : __low2float(s1);
-          y[0] = fmaf(f0, fmaf(odd[0], 0.0625f, even[0]), y[0]);
-          y[1] = fmaf(f0, fmaf(odd[1], 0.0625f, even[1]), y[1]);
-          y[2] = fmaf(f1, fmaf(odd[2], 0.0625f, even[2]), y[2]);
-          y[3] = fmaf(f1, fmaf(odd[3], 0.0625f, even[3]), y[3]);
-        }
+        for (int kk = 0; kk < KT; ++kk) tile_product(ring_base + d * V::SLOT_BYTES, kk, y);
       }
       store_shared16(red_at + d * 512, y[0], y[1], y[2], y[3]);
     }
@@ -344,7 +498,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
           for (int q = 0; q < 4; ++q) {
             const int mq = m + (q & 1), rq = row + (q & 2) * 4;
             if (mq < a.M && rq < a.N) {
-              float value = out[q] * 16777216.f;  // 2^24
+              float value = RAW ? out[q] * 16777216.f : out[q];  // RAW sums are in units of 2^-24
               if (a.bias != nullptr) value += __half2float(a.bias[rq]);
               a.y[int64_t(mq) * a.N + rq] = __float2half_rn(value);
             }
@@ -370,7 +524,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
       const int rt = int(blockIdx.x) * a.RG + rgi + v * visit_stride;
       const int row = rt * 16 + (e >> 4) + ((e & 2) ? 8 : 0), m = ((e >> 2) & 3) * 2 + (e & 1);
       if (rt < a.row_tiles && row < a.N && m < a.M) {
-        sum *= 16777216.f;
+        if (RAW) sum *= 16777216.f;
         if (a.bias != nullptr) sum += __half2float(a.bias[row]);
         a.y[int64_t(m) * a.N + row] = __float2half_rn(sum);
       }
@@ -399,20 +553,23 @@ int opt_in_shared(Kernel kernel) {
 }
 
 struct StreamPlan {
+  int bits, mode, gpt;   // the codec: code width, MODE_*, scale groups per k-tile
   int KT, KW, RG, slabs, columns, visits, depth, batch, per_sm;
   size_t smem;
 };
 
 // Chooses the decomposition: slabs of K (CTAs of a cluster), warps along K and row tiles per visit of a
 // CTA, CTAs per SM (small CTAs share an SM), ring depth (= visits per round).
-// `cluster_cap` > 0 bounds the number of clusters in flight.
+// `cluster_cap` > 0 bounds the number of clusters in flight.  bits, mode, gpt are inputs.
 bool plan_stream(int M, int N, int K, int sm_count, int max_smem, int cluster_cap, StreamPlan& p) {
   (void)M;
   const int k_tiles = K / 128;
   const int KT = k_tiles % 2 == 0 ? 2 : 1;
   const int k_warps = k_tiles / KT;
   const int row_tiles = (N + 15) / 16;
-  const size_t slot = size_t(KT) * 1024 + 64;
+  const int scale_row_bytes = KT * p.gpt * 2 < 4 ? 4 : KT * p.gpt * 2;
+  const size_t slot = size_t(KT) * 256 * p.bits + 16 * scale_row_bytes;
+  const size_t table = p.mode == MODE_TABLE ? (size_t(128) << (2 * p.bits)) : 0;
   // fewest slabs that give every warp of a 16-warp CTA one share of K.  The choice depends on K alone,
   // so a layer and the same rows inside a wider (concatenated) layer are summed in the same order.
   const int slabs = (k_warps + kMaxWarps - 1) / kMaxWarps;
@@ -421,7 +578,7 @@ bool plan_stream(int M, int N, int K, int sm_count, int max_smem, int cluster_ca
   int RG = kMaxWarps / KW;
   while (RG > 1 && (row_tiles + RG - 1) / RG * slabs < sm_count) --RG;  // keep every SM busy first
   const int warps = KW * RG;
-  const int per_sm = kMaxWarps / warps;
+  const int per_sm = table ? 1 : kMaxWarps / warps;
   int clusters = sm_count * per_sm / slabs;
   if (cluster_cap > 0 && clusters > cluster_cap) clusters = cluster_cap;  // what the GPU can co-schedule
   if (clusters < 1) return false;
@@ -431,7 +588,7 @@ bool plan_stream(int M, int N, int K, int sm_count, int max_smem, int cluster_ca
   if (slabs > 1 && visits > kMaxClusterVisits) return false;
   int depth = visits < 2 ? 2 : visits > 3 ? 3 : visits;
   const size_t budget = (size_t(max_smem) + 1024) / per_sm - 1024;  // every resident CTA reserves 1 KB
-  const size_t sums = slabs > 1 ? size_t(visits) * RG * 512 : 0;
+  const size_t sums = (slabs > 1 ? size_t(visits) * RG * 512 : 0) + table;
   while (depth > 2 && size_t(depth) * warps * (slot + 512) + sums > budget) --depth;
   if (size_t(depth) * warps * (slot + 512) + sums > budget) return false;
   // partial sums of as many visits as fit (whole rounds), ideally all: one reduction at the end
@@ -445,9 +602,9 @@ bool plan_stream(int M, int N, int K, int sm_count, int max_smem, int cluster_ca
   return true;
 }
 
-template <int KT, int R>
+template <int BITS, int MODE, int GPT, int KT, int R>
 int launch_stream(const StreamArgs& a, const StreamPlan& p, cudaStream_t stream, int* cluster_cap) {
-  auto kernel = gemv_stream_kernel<4, KT, R>;
+  auto kernel = gemv_stream_kernel<BITS, MODE, GPT, KT, R>;
   int status = opt_in_shared(kernel);
   if (status != MKB_OK) return status;
   cudaLaunchConfig_t config{};
@@ -493,44 +650,74 @@ int launch_stream(const StreamArgs& a, const StreamPlan& p, cudaStream_t stream,
   return MKB_OK;
 }
 
-int dispatch_stream(const StreamArgs& a, const StreamPlan& p, cudaStream_t stream, int* cluster_cap) {
+template <int BITS, int MODE, int GPT>
+int dispatch_shape(const StreamArgs& a, const StreamPlan& p, cudaStream_t stream, int* cluster_cap) {
   if (p.KT == 2) {
-    switch (p.depth) {
-      case 2: return launch_stream<2, 2>(a, p, stream, cluster_cap);
-      default: return launch_stream<2, 3>(a, p, stream, cluster_cap);
-    }
+    if (p.depth == 2) return launch_stream<BITS, MODE, GPT, 2, 2>(a, p, stream, cluster_cap);
+    return launch_stream<BITS, MODE, GPT, 2, 3>(a, p, stream, cluster_cap);
   }
-  switch (p.depth) {
-    case 2: return launch_stream<1, 2>(a, p, stream, cluster_cap);
-    default: return launch_stream<1, 3>(a, p, stream, cluster_cap);
-  }
+  if (p.depth == 2) return launch_stream<BITS, MODE, GPT, 1, 2>(a, p, stream, cluster_cap);
+  return launch_stream<BITS, MODE, GPT, 1, 3>(a, p, stream, cluster_cap);
 }
 
+int dispatch_stream(const StreamArgs& a, const StreamPlan& p, cudaStream_t stream, int* cluster_cap) {
+  if (p.mode == MODE_RAW) {
+    if (p.bits == 4) return dispatch_shape<4, MODE_RAW, 1>(a, p, stream, cluster_cap);
+    if (p.bits == 2) return dispatch_shape<2, MODE_RAW, 1>(a, p, stream, cluster_cap);
+    return dispatch_shape<8, MODE_RAW, 1>(a, p, stream, cluster_cap);
+  }
+  if (p.bits == 4) return p.gpt == 1 ? dispatch_shape<4, MODE_TABLE, 1>(a, p, stream, cluster_cap)
+                                     : dispatch_shape<4, MODE_TABLE, 2>(a, p, stream, cluster_cap);
+  return p.gpt == 1 ? dispatch_shape<3, MODE_TABLE, 1>(a, p, stream, cluster_cap)
+                    : dispatch_shape<3, MODE_TABLE, 2>(a, p, stream, cluster_cap);
+}
+
+// The codec a call maps to: false when the streaming kernel does not cover it.
+bool codec_of(int group, int bits, int lut_len, const void* zeros, int integer_grid, float grid_minimum, StreamPlan& p) {
+  if (zeros != nullptr || lut_len < 1 || lut_len > (1 << bits)) return false;
+  const bool ramp = integer_grid && lut_len == (1 << bits) && grid_minimum == float(int(grid_minimum)) &&
+                    grid_minimum >= -512.f && grid_minimum <= 512.f;
+  if (ramp && group == 128 && (bits == 2 || bits == 4 || bits == 8)) {
+    p.bits = bits; p.mode = MODE_RAW; p.gpt = 1;
+    return true;
+  }
+  if ((bits == 3 || bits == 4) && (group == 64 || group == 128)) {
+    p.bits = bits; p.mode = MODE_TABLE; p.gpt = 128 / group;
+    return true;
+  }
+  return false;
+}
 
 }  // namespace
 
-int gemv_stream_supported(int M, int N, int K, int group, int bits, int x_dtype, int scale_dtype, const void* x,
-                          const uint8_t* packed, const void* scales, int64_t packed_row_stride,
+int gemv_stream_supported(int M, int N, int K, int group, int bits, int lut_len, int x_dtype, int scale_dtype,
+                          const void* x, const uint8_t* packed, const void* scales, int64_t packed_row_stride,
                           int64_t scale_row_stride, const void* zeros, int integer_grid, float grid_minimum) {
-  if (x_dtype != MKB_F16 || scale_dtype != MKB_F16 || zeros != nullptr || !integer_grid) return 0;
-  if (bits != 4 || group != 128 || M < 1 || M > 8 || N < 1 || K < 128 || K % 128 != 0) return 0;
-  if (grid_minimum != float(int(grid_minimum)) || grid_minimum < -512.f || grid_minimum > 512.f) return 0;
+  if (x_dtype != MKB_F16 || scale_dtype != MKB_F16) return 0;
+  if (M < 1 || M > 8 || N < 1 || K < 128 || K % 128 != 0) return 0;
+  StreamPlan plan{};
+  if (!codec_of(group, bits, lut_len, zeros, integer_grid, grid_minimum, plan)) return 0;
   if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(packed) % 16 || packed_row_stride % 16) return 0;
-  if (reinterpret_cast<uintptr_t>(scales) % 4 || ((K / 128) % 2 == 0 && scale_row_stride % 2)) return 0;
-  if ((K / 128) % 2 == 1 && (int64_t(N) * scale_row_stride) % 2) return 0;  // scales are copied in aligned pairs
+  // the scales of a row and visit are copied as one aligned piece of 4, 8 or 16 bytes
+  const int scales_per_visit = ((K / 128) % 2 == 0 ? 2 : 1) * plan.gpt;
+  if (scales_per_visit == 1) {
+    if (reinterpret_cast<uintptr_t>(scales) % 4 || (int64_t(N) * scale_row_stride) % 2) return 0;  // aligned pairs
+  } else if (reinterpret_cast<uintptr_t>(scales) % (scales_per_visit * 2) || scale_row_stride % scales_per_visit) {
+    return 0;
+  }
   if (int64_t(N) * packed_row_stride >= (int64_t(1) << 32) || int64_t(N) * scale_row_stride >= (int64_t(1) << 30)) return 0;
-  StreamPlan plan;
   const DeviceInfo& info = device_info();
   return plan_stream(M, N, K, info.sm_count, info.max_smem_optin, 0, plan) ? 1 : 0;
 }
 
-int launch_gemv_stream(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y, int M,
-                       int N, int K, int64_t packed_row_stride, int64_t scale_row_stride, float grid_minimum,
-                       int gated, cudaStream_t stream) {
+int launch_gemv_stream(const void* x, const uint8_t* packed, const void* scales, const float* lut, const void* bias,
+                       void* y, int M, int N, int K, int group, int bits, int lut_len, int64_t packed_row_stride,
+                       int64_t scale_row_stride, int integer_grid, float grid_minimum, int gated, cudaStream_t stream) {
   const DeviceInfo& info = device_info();
-  StreamPlan p;
-  MKB_REQUIRE(plan_stream(M, N, K, info.sm_count, info.max_smem_optin, 0, p), MKB_E_UNSUPPORTED,
-              "gemv_stream: no decomposition for N=%d K=%d", N, K);
+  StreamPlan p{};
+  MKB_REQUIRE(codec_of(group, bits, lut_len, nullptr, integer_grid, grid_minimum, p) &&
+                  plan_stream(M, N, K, info.sm_count, info.max_smem_optin, 0, p),
+              MKB_E_UNSUPPORTED, "gemv_stream: no decomposition for N=%d K=%d bits=%d group=%d", N, K, bits, group);
   StreamArgs a{};
   if (p.slabs > 1) {  // a grid of clusters must be resident as a whole, or it runs in waves
     int cap = 0;
@@ -542,10 +729,10 @@ int launch_gemv_stream(const void* x, const uint8_t* packed, const void* scales,
                   MKB_E_UNSUPPORTED, "gemv_stream: no decomposition for N=%d K=%d in %d clusters", N, K, cap);
   }
   a.x = static_cast<const __half*>(x); a.packed = packed; a.scales = static_cast<const __half*>(scales);
-  a.bias = static_cast<const __half*>(bias); a.y = static_cast<__half*>(y);
+  a.bias = static_cast<const __half*>(bias); a.y = static_cast<__half*>(y); a.lut = lut; a.lut_len = lut_len;
   a.M = M; a.N = N; a.K = K; a.packed_row_stride = packed_row_stride; a.scale_row_stride = scale_row_stride;
   a.row_tiles = (N + 15) / 16; a.k_warps = K / (128 * p.KT); a.KW = p.KW; a.RG = p.RG; a.slabs = p.slabs;
-  a.visits = p.visits; a.grid_min = grid_minimum; a.batch = p.batch; a.early = 1; a.gated = gated;
+  a.visits = p.visits; a.grid_min = p.mode == MODE_RAW ? grid_minimum : 0.f; a.batch = p.batch; a.early = 1; a.gated = gated;
   a.kw_inverse = (65536 + p.KW - 1) / p.KW; a.rg_inverse = (65536 + p.RG - 1) / p.RG;
   return dispatch_stream(a, p, stream, nullptr);
 }

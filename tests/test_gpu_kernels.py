@@ -205,6 +205,16 @@ def test_matvec_tiled_every_codec(kind, bits, group, rows_in, asym):
     expected = oracle_matvec(layer, x)
     for kernel in ("tiled", "scalar"):
         assert matvec.relative_l2(run_matvec(layer, x, kernel), expected) < TOLERANCE, kernel
+    # the streaming kernel: integer grids of 2, 4, 8 bits with groups of 128; tables of 3- and 4-bit
+    # codes with groups of 64 or 128; nothing with offsets
+    streams = not asym and ((kind == "int" and bits in (2, 4, 8) and group == 128) or (bits in (3, 4) and group in (64, 128)))
+    if streams:
+        got = run_matvec(layer, x, "stream")
+        assert matvec.relative_l2(got, expected) < TOLERANCE
+        assert np.array_equal(got, run_matvec(layer, x, "stream"))
+    else:
+        with pytest.raises(ValueError, match="streaming kernel"):
+            run_matvec(layer, x, "stream")
 
 
 @pytest.mark.parametrize("bits,width,group", [(1, 64, 16), (3, 40, 8), (5, 72, 24), (7, 64, 64), (4, 130, 32),
@@ -281,11 +291,27 @@ def test_matvec_stream_shapes_bias_ragged_rows_and_splits(rows, width):
         assert np.array_equal(first, run_matvec(layer, x, "stream", bias))   # fixed summation order
 
 
+@pytest.mark.parametrize("kind,bits,group", [("int", 2, 128), ("int", 8, 128), ("int", 3, 128), ("nf4", 4, 64),
+                                             ("nf4", 4, 128), ("codebook3", 3, 64), ("int", 4, 64)])
+@pytest.mark.parametrize("rows,width", [(300, 1536), (4864, 896), (48, 8192), (1000, 1024)])
+def test_matvec_stream_every_codec_bias_ragged_rows_and_splits(kind, bits, group, rows, width):
+    """Every codec of the streaming kernel on shapes with one and two k-tiles per warp, K split over a
+    cluster, a partial last row tile and a bias."""
+    layer = helpers.make_layer(rows, width, bits, group, kind, seed=bits + group + rows)
+    bias = (np.random.default_rng(2).standard_normal(rows) * 0.1).astype(np.float16)
+    for rows_in in (1, 8):
+        x = helpers.activations(rows_in, width, seed=rows_in, outliers=True)
+        expected = oracle_matvec(layer, x, bias)
+        first = run_matvec(layer, x, "stream", bias)
+        assert matvec.relative_l2(first, expected) < TOLERANCE
+        assert np.array_equal(first, run_matvec(layer, x, "stream", bias))
+
+
 def test_matvec_stream_refuses_what_it_does_not_cover():
-    layer = helpers.make_layer(64, 512, 4, 64, seed=1)    # groups narrower than 128 codes
+    layer = helpers.make_layer(64, 512, 4, 32, seed=1)    # groups narrower than 64 codes
     with pytest.raises(ValueError, match="streaming kernel"):
         run_matvec(layer, helpers.activations(1, 512), "stream")
-    layer = helpers.make_layer(64, 512, 8, 128, seed=1)   # 8-bit codes
+    layer = helpers.make_layer(64, 512, 4, 128, seed=1, asym=True)   # offsets
     with pytest.raises(ValueError, match="streaming kernel"):
         run_matvec(layer, helpers.activations(1, 512), "stream")
 
