@@ -1,12 +1,22 @@
 // Fused structured orthogonal transform of activation rows:  y = (B kron H_P)(x * signs).
 //
-// One CTA owns one row.  The row lives in shared memory as fp32 for the whole transform: sign
-// flip on load, Walsh-Hadamard butterflies in ascending stride with three stages per pass (the
-// same pairing and order as a stage-by-stage transform, so sums and differences round
-// identically), the 1/sqrt(P) scale folded into the last pass as one multiply, the dense
-// factor-by-factor mix across the blocks, and one rounding to the activation dtype on store.
-// The reference needs ceil(log2(P)/3) global round trips plus casts, a sign multiply, two
-// transposes and a small library matmul for the same result.
+// Three kernels, all with fp32 arithmetic and one rounding to the activation dtype on store.
+//  * warp kernel (power-of-two widths that are multiples of 512): a warp owns 512 consecutive values,
+//    sixteen per lane.  Strides 1..8 are butterflies between a lane's own registers, strides 16..256
+//    are exchanges between lanes (shfl.xor), so nine stages need no shared memory and no barrier; a
+//    width of 512 or less goes from global memory to global memory in one sweep.  Wider rows finish
+//    the remaining stages in shared memory, three per pass.
+//  * row kernel: any other power-of-two width, the whole row in shared memory, three stages per pass.
+//  * factor kernel (width = F * P with a dense F x F basis): the transform is a Kronecker product, so
+//    the F-point mix and the P-point butterflies commute.  A CTA owns four output blocks of one row:
+//    it mixes the F input blocks into its four (reading the row straight from global memory), then
+//    runs the butterflies on those 4 * P values.  A row is spread over ceil(F / 4) CTAs with no
+//    exchange between them.
+// The butterflies pair i with i ^ stride in ascending stride and form (a + b, a - b), the pairing and
+// order of a stage-by-stage transform, so power-of-two widths round identically to one; the 1/sqrt(P)
+// scale is one multiply after the last stage.
+// The reference needs ceil(log2(P)/3) global round trips plus casts, a sign multiply, two transposes
+// and a small library matmul for the same result.
 #include "mkb_common.cuh"
 
 namespace mkb {
@@ -18,7 +28,7 @@ struct HadamardArgs {
   const float* basis;
   void* y;
   int64_t M;
-  int W, factor, pow2, log2p, dtype, inverse, vector_io;
+  int W, factor, pow2, log2p, dtype, inverse;
   float scale;  // fp32(1) / fp32(sqrt(pow2)), or 1
 };
 
@@ -61,122 +71,221 @@ __device__ __forceinline__ void butterfly_pass(float* buf, int groups, int strid
   }
 }
 
-__global__ void hadamard_kernel(HadamardArgs a) {
-  extern __shared__ __align__(16) float smem_f[];
-  float* buf = smem_f;               // [W]
-  float* basis_s = smem_f + ((a.W + 3) & ~3);   // [factor][factor padded to 4] when factor > 1; 16-byte aligned
-  const int64_t row = blockIdx.x;
-  const int64_t offset = row * a.W;
+__device__ __forceinline__ void depend_on_previous_grid() {
+  // programmatic dependent launch: the kernel that follows in the stream (a packed matvec prefetching
+  // its weights) may become resident now; this one waits for the producer of its input
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
-  if (a.vector_io) {
-    // 16-bit activations, eight per 16-byte access
-    const uint4* source = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(a.x) + offset);
-    for (int i = threadIdx.x; i < a.W / 8; i += blockDim.x) {
-      const uint4 raw = __ldg(source + i);
-      const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
-      float v[8];
+template <int COUNT>
+__device__ __forceinline__ void load_run(const void* x, int64_t index, int dtype, float* v) {
+  // COUNT (8 or 16) consecutive activations starting at a 16-byte boundary
+  if (dtype == MKB_F32) {
+    const float4* source = reinterpret_cast<const float4*>(static_cast<const float*>(x) + index);
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float2 pair = a.dtype == MKB_F16 ? __half22float2(*reinterpret_cast<const __half2*>(&words[q]))
-                                               : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&words[q]));
-        v[2 * q] = pair.x;
-        v[2 * q + 1] = pair.y;
-      }
-      if (a.signs != nullptr && !a.inverse) {
-        const uint2 flips = *reinterpret_cast<const uint2*>(a.signs + 8 * i);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const uint32_t word = q < 4 ? flips.x : flips.y;
-          v[q] = __fmul_rn(v[q], float(int8_t((word >> (8 * (q & 3))) & 0xffu)));
-        }
-      }
-      *reinterpret_cast<float4*>(buf + 8 * i) = make_float4(v[0], v[1], v[2], v[3]);
-      *reinterpret_cast<float4*>(buf + 8 * i + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    for (int q = 0; q < COUNT / 4; ++q) {
+      const float4 four = __ldg(source + q);
+      v[4 * q] = four.x; v[4 * q + 1] = four.y; v[4 * q + 2] = four.z; v[4 * q + 3] = four.w;
     }
-  } else {
-    for (int i = threadIdx.x; i < a.W; i += blockDim.x) {
-      float v = load_as_float(a.x, offset + i, a.dtype);
-      if (a.signs != nullptr && !a.inverse) v = __fmul_rn(v, float(a.signs[i]));
-      buf[i] = v;
+    return;
+  }
+  const uint4* source = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + index);
+#pragma unroll
+  for (int q = 0; q < COUNT / 8; ++q) {
+    const uint4 raw = __ldg(source + q);
+    const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float2 pair = dtype == MKB_F16 ? __half22float2(*reinterpret_cast<const __half2*>(&words[w]))
+                                           : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&words[w]));
+      v[8 * q + 2 * w] = pair.x;
+      v[8 * q + 2 * w + 1] = pair.y;
     }
   }
-  // the factor mix, laid out [f][f' padded to 4]: mix[f][f'] multiplies h[f, :] into y[f', :]
-  const int F4 = (a.factor + 3) & ~3;
-  if (a.factor > 1)
-    for (int i = threadIdx.x; i < a.factor * F4; i += blockDim.x) {
-      const int f = i / F4, fo = i - f * F4;
-      basis_s[i] = fo < a.factor ? (a.inverse ? a.basis[f * a.factor + fo] : a.basis[fo * a.factor + f]) : 0.f;
-    }
-  __syncthreads();
+}
 
-  int remaining = a.log2p, stride_bits = 0;
+template <int COUNT>
+__device__ __forceinline__ void store_run(void* y, int64_t index, int dtype, const float* v) {
+  if (dtype == MKB_F32) {
+    float4* target = reinterpret_cast<float4*>(static_cast<float*>(y) + index);
+#pragma unroll
+    for (int q = 0; q < COUNT / 4; ++q) target[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    return;
+  }
+  uint4* target = reinterpret_cast<uint4*>(static_cast<uint16_t*>(y) + index);
+#pragma unroll
+  for (int q = 0; q < COUNT / 8; ++q) {
+    uint32_t words[4];
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      if (dtype == MKB_F16) {
+        const __half2 pair = __floats2half2_rn(v[8 * q + 2 * w], v[8 * q + 2 * w + 1]);
+        words[w] = *reinterpret_cast<const uint32_t*>(&pair);
+      } else {
+        const __nv_bfloat162 pair = __floats2bfloat162_rn(v[8 * q + 2 * w], v[8 * q + 2 * w + 1]);
+        words[w] = *reinterpret_cast<const uint32_t*>(&pair);
+      }
+    }
+    target[q] = make_uint4(words[0], words[1], words[2], words[3]);
+  }
+}
+
+template <int COUNT>
+__device__ __forceinline__ void flip_run(const int8_t* signs, int index, float* v) {
+  // multiply by COUNT consecutive +-1 signs (the run starts on a COUNT-byte boundary)
+  const uint2* source = reinterpret_cast<const uint2*>(signs + index);
+#pragma unroll
+  for (int q = 0; q < COUNT / 8; ++q) {
+    const uint2 flips = source[q];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t word = j < 4 ? flips.x : flips.y;
+      v[8 * q + j] = __fmul_rn(v[8 * q + j], float(int8_t((word >> (8 * (j & 3))) & 0xffu)));
+    }
+  }
+}
+
+// the stages that are left after `done_bits` of them, on `count` values in shared memory
+__device__ __forceinline__ void remaining_passes(float* buf, int count, int log2p, int done_bits, float last_scale) {
+  int remaining = log2p - done_bits, stride_bits = done_bits;
   while (remaining > 0) {
     const int stages = remaining >= 3 ? 3 : remaining;
     remaining -= stages;
-    const float scale = remaining == 0 ? a.scale : 1.0f;
-    const int groups = a.W >> stages;
+    const float scale = remaining == 0 ? last_scale : 1.0f;
+    const int groups = count >> stages;
     if (stages == 3) butterfly_pass<3>(buf, groups, 1 << stride_bits, stride_bits, scale);
     else if (stages == 2) butterfly_pass<2>(buf, groups, 1 << stride_bits, stride_bits, scale);
     else butterfly_pass<1>(buf, groups, 1 << stride_bits, stride_bits, scale);
     stride_bits += stages;
     __syncthreads();
   }
+}
 
-  if (a.factor == 1) {
-    if (a.vector_io) {
-      uint4* target = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.y) + offset);
-      for (int i = threadIdx.x; i < a.W / 8; i += blockDim.x) {
-        const float4 lo = *reinterpret_cast<const float4*>(buf + 8 * i), hi = *reinterpret_cast<const float4*>(buf + 8 * i + 4);
-        float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-        if (a.signs != nullptr && a.inverse) {
+constexpr int kWarpRun = 16;                 // values per lane in the warp kernel
+constexpr int kWarpSpan = 32 * kWarpRun;     // values per warp: nine stages without shared memory
+constexpr int kWarpBits = 9;
+
+__global__ void __launch_bounds__(1024) hadamard_warp_kernel(HadamardArgs a) {
+  extern __shared__ __align__(16) float smem_f[];
+  depend_on_previous_grid();
+  float* buf = smem_f;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int64_t offset = int64_t(blockIdx.x) * a.W;
+  const int front = a.log2p < kWarpBits ? a.log2p : kWarpBits;   // at least 4: the block is 16 wide or wider
+  const bool direct = a.log2p <= kWarpBits;
+  for (int chunk = warp; chunk < a.W / kWarpSpan; chunk += warps) {
+    const int first = chunk * kWarpSpan + lane * kWarpRun;
+    float v[kWarpRun];
+    load_run<kWarpRun>(a.x, offset + first, a.dtype, v);
+    if (a.signs != nullptr && !a.inverse) flip_run<kWarpRun>(a.signs, first, v);
 #pragma unroll
-          for (int q = 0; q < 8; ++q) v[q] = __fmul_rn(v[q], float(a.signs[8 * i + q]));
-        }
-        uint32_t words[4];
+    for (int s = 0; s < 4; ++s) {
+      const int span = 1 << s;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          if (a.dtype == MKB_F16) {
-            const __half2 pair = __floats2half2_rn(v[2 * q], v[2 * q + 1]);
-            words[q] = *reinterpret_cast<const uint32_t*>(&pair);
-          } else {
-            const __nv_bfloat162 pair = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
-            words[q] = *reinterpret_cast<const uint32_t*>(&pair);
-          }
+      for (int j = 0; j < kWarpRun; ++j) {
+        if ((j & span) == 0) {
+          const float low = v[j], high = v[j + span];
+          v[j] = __fadd_rn(low, high);
+          v[j + span] = __fsub_rn(low, high);
         }
-        target[i] = make_uint4(words[0], words[1], words[2], words[3]);
       }
-      return;
     }
-    for (int i = threadIdx.x; i < a.W; i += blockDim.x) {
-      float v = buf[i];
-      if (a.signs != nullptr && a.inverse) v = __fmul_rn(v, float(a.signs[i]));
-      store_from_float(a.y, offset + i, a.dtype, v);
+#pragma unroll
+    for (int s = 4; s < kWarpBits; ++s) {
+      if (s < front) {
+        const int mask = 1 << (s - 4);
+        // the lane with the bit clear keeps low + high, its partner low - high: one rounding of
+        // (+-own + other), the same value as the add or the subtract
+        const float sign = (lane & mask) ? -1.0f : 1.0f;
+#pragma unroll
+        for (int j = 0; j < kWarpRun; ++j) v[j] = __fmaf_rn(v[j], sign, __shfl_xor_sync(0xffffffffu, v[j], mask));
+      }
     }
-    return;
+    if (direct) {
+#pragma unroll
+      for (int j = 0; j < kWarpRun; ++j) v[j] = __fmul_rn(v[j], a.scale);
+      if (a.signs != nullptr && a.inverse) flip_run<kWarpRun>(a.signs, first, v);
+      store_run<kWarpRun>(a.y, offset + first, a.dtype, v);
+    } else {
+#pragma unroll
+      for (int q = 0; q < kWarpRun / 4; ++q)
+        *reinterpret_cast<float4*>(buf + first + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    }
   }
-  // y[f', p] = sum_f mix[f][f'] h[f, p]: a thread forms four f' for one p, so one 16-byte broadcast
-  // read of the mix and one read of h feed four multiply-adds; f runs in ascending order
+  if (direct) return;
+  __syncthreads();
+  remaining_passes(buf, a.W, a.log2p, kWarpBits, a.scale);
+  for (int i = threadIdx.x; i < a.W / 8; i += blockDim.x) {
+    const float4 lo = *reinterpret_cast<const float4*>(buf + 8 * i), hi = *reinterpret_cast<const float4*>(buf + 8 * i + 4);
+    float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    if (a.signs != nullptr && a.inverse) flip_run<8>(a.signs, 8 * i, v);
+    store_run<8>(a.y, offset + 8 * i, a.dtype, v);
+  }
+}
+
+__global__ void hadamard_kernel(HadamardArgs a) {
+  extern __shared__ __align__(16) float smem_f[];
+  depend_on_previous_grid();
+  float* buf = smem_f;               // [W]
+  const int64_t offset = int64_t(blockIdx.x) * a.W;
+  for (int i = threadIdx.x; i < a.W; i += blockDim.x) {
+    float v = load_as_float(a.x, offset + i, a.dtype);
+    if (a.signs != nullptr && !a.inverse) v = __fmul_rn(v, float(a.signs[i]));
+    buf[i] = v;
+  }
+  __syncthreads();
+  remaining_passes(buf, a.W, a.log2p, 0, a.scale);
+  for (int i = threadIdx.x; i < a.W; i += blockDim.x) {
+    float v = buf[i];
+    if (a.signs != nullptr && a.inverse) v = __fmul_rn(v, float(a.signs[i]));
+    store_from_float(a.y, offset + i, a.dtype, v);
+  }
+}
+
+__global__ void hadamard_factor_kernel(HadamardArgs a) {
+  extern __shared__ __align__(16) float smem_f[];
+  depend_on_previous_grid();
   const int P = a.pow2, F = a.factor;
-  for (int task = threadIdx.x; task < (F4 / 4) * P; task += blockDim.x) {
-    const int quad = task / P, p = task - quad * P;
+  float* buf = smem_f;                                         // [4][P]: this CTA's four output blocks
+  float4* mix = reinterpret_cast<float4*>(smem_f + 4 * ((P + 3) & ~3));   // [F]: the four basis columns
+  const int64_t offset = int64_t(blockIdx.x) * a.W;
+  const int quad = blockIdx.y;
+  // mix[f][j] multiplies input block f into output block 4 * quad + j
+  for (int f = threadIdx.x; f < F; f += blockDim.x) {
+    float m[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int fo = 4 * quad + j;
+      m[j] = fo < F ? (a.inverse ? a.basis[f * F + fo] : a.basis[fo * F + f]) : 0.f;
+    }
+    mix[f] = make_float4(m[0], m[1], m[2], m[3]);
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int f = 0; f < F; ++f) {
-      const float4 m = *reinterpret_cast<const float4*>(basis_s + f * F4 + 4 * quad);
-      const float h = buf[f * P + p];
+#pragma unroll 4
+    for (int f = 0; f < F; ++f) {      // f in ascending order
+      float h = load_as_float(a.x, offset + f * P + p, a.dtype);
+      if (a.signs != nullptr && !a.inverse) h = __fmul_rn(h, float(a.signs[f * P + p]));
+      const float4 m = mix[f];
       acc[0] = fmaf(m.x, h, acc[0]);
       acc[1] = fmaf(m.y, h, acc[1]);
       acc[2] = fmaf(m.z, h, acc[2]);
       acc[3] = fmaf(m.w, h, acc[3]);
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int fo = 4 * quad + j;
-      if (fo < F) {
-        const int i = fo * P + p;
-        float value = acc[j];
-        if (a.inverse && a.signs != nullptr) value = __fmul_rn(value, float(a.signs[i]));
-        store_from_float(a.y, offset + i, a.dtype, value);
-      }
+    for (int j = 0; j < 4; ++j) buf[j * P + p] = acc[j];
+  }
+  __syncthreads();
+  remaining_passes(buf, 4 * P, a.log2p, 0, a.scale);
+  for (int i = threadIdx.x; i < 4 * P; i += blockDim.x) {
+    const int fo = 4 * quad + (i >> a.log2p), p = i & (P - 1);
+    if (fo < F) {
+      const int at = fo * P + p;
+      float value = buf[i];
+      if (a.inverse && a.signs != nullptr) value = __fmul_rn(value, float(a.signs[at]));
+      store_from_float(a.y, offset + at, a.dtype, value);
     }
   }
 }
@@ -197,30 +306,54 @@ extern "C" int mkb_hadamard(const void* x, const int8_t* signs, const float* bas
   if (M == 0) return MKB_OK;
   MKB_REQUIRE(x != nullptr && y != nullptr, MKB_E_ARGUMENT, "hadamard: null pointer");
   MKB_REQUIRE(M <= 0x7fffffffLL, MKB_E_UNSUPPORTED, "hadamard: too many rows");
-  const size_t smem = (size_t((W + 3) & ~3) + (factor > 1 ? size_t(factor) * ((factor + 3) & ~3) : 0)) * sizeof(float);
-  const DeviceInfo& info = device_info();
-  MKB_REQUIRE(smem <= size_t(info.max_smem_optin), MKB_E_UNSUPPORTED,
-              "hadamard: width %d needs %zu B shared memory", W, smem);
-  static thread_local size_t opted[64];
-  int device = 0;
-  cudaGetDevice(&device);
-  if (device >= 0 && device < 64 && smem > 48 * 1024 && smem > opted[device]) {
-    cudaError_t status = cudaFuncSetAttribute(hadamard_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              info.max_smem_optin);
-    if (status != cudaSuccess) return cuda_fail(status, "hadamard: shared memory opt-in");
-    opted[device] = size_t(info.max_smem_optin);
-  }
   HadamardArgs a{};
   a.x = x; a.signs = signs; a.basis = basis; a.y = y; a.M = M;
   a.W = W; a.factor = factor; a.pow2 = pow2; a.dtype = dtype; a.inverse = inverse;
-  a.vector_io = dtype != MKB_F32 && W % 8 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
-                reinterpret_cast<uintptr_t>(y) % 16 == 0 && (signs == nullptr || reinterpret_cast<uintptr_t>(signs) % 8 == 0);
   a.log2p = 0;
   while ((1 << a.log2p) < pow2) ++a.log2p;
   // the reference forms the scale in fp32: float(torch.tensor(1.0) / torch.tensor(math.sqrt(width)))
   a.scale = normalize ? 1.0f / float(sqrt(double(pow2))) : 1.0f;
-  int threads = W >= 8192 ? 1024 : W >= 4096 ? 512 : W >= 1024 ? 256 : 128;
-  hadamard_kernel<<<dim3((unsigned)M), threads, smem, static_cast<cudaStream_t>(stream)>>>(a);
-  MKB_LAUNCH_CHECK("hadamard launch");
+  const auto aligned = [](const void* p, uintptr_t to) { return reinterpret_cast<uintptr_t>(p) % to == 0; };
+  const bool by_warp = factor == 1 && W % kWarpSpan == 0 && aligned(x, 16) && aligned(y, 16) &&
+                       (signs == nullptr || aligned(signs, 8));
+  void (*kernel)(HadamardArgs) = factor > 1 ? hadamard_factor_kernel : by_warp ? hadamard_warp_kernel : hadamard_kernel;
+  size_t smem;
+  dim3 grid((unsigned)M);
+  int threads;
+  if (factor > 1) {
+    smem = (size_t(4) * ((pow2 + 3) & ~3) + size_t(4) * factor) * sizeof(float);
+    grid.y = (factor + 3) / 4;
+    threads = pow2 >= 1024 ? 1024 : pow2 >= 128 ? pow2 : 128;
+  } else if (by_warp) {
+    smem = a.log2p <= kWarpBits ? 0 : size_t(W) * sizeof(float);
+    threads = W / kWarpRun >= 1024 ? 1024 : W / kWarpRun;
+  } else {
+    smem = size_t((W + 3) & ~3) * sizeof(float);
+    threads = W >= 8192 ? 1024 : W >= 4096 ? 512 : W >= 1024 ? 256 : 128;
+  }
+  const DeviceInfo& info = device_info();
+  MKB_REQUIRE(smem <= size_t(info.max_smem_optin), MKB_E_UNSUPPORTED,
+              "hadamard: width %d needs %zu B shared memory", W, smem);
+  const int which = factor > 1 ? 2 : by_warp ? 1 : 0;
+  static thread_local bool opted[64][3];
+  int device = 0;
+  cudaGetDevice(&device);
+  if (smem > 48 * 1024 && !(device >= 0 && device < 64 && opted[device][which])) {
+    cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, info.max_smem_optin);
+    if (status != cudaSuccess) return cuda_fail(status, "hadamard: shared memory opt-in");
+    if (device >= 0 && device < 64) opted[device][which] = true;
+  }
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = dim3(threads);
+  config.dynamicSmemBytes = smem;
+  config.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  const cudaError_t launched = cudaLaunchKernelEx(&config, kernel, a);
+  if (launched != cudaSuccess) return cuda_fail(launched, "hadamard launch");
   return MKB_OK;
 }
