@@ -16,8 +16,9 @@ twice in a row.
 N > 1: the 70B-shaped tensor-parallel decode step of ``mlkit_b200.tp`` (see ``bench_tp.py``).
 
 ``value`` is algorithmic GB/s with every input resident in HBM; ``e2e`` is the same pass through the
-public module call (``PackedLinear.forward``) with activations coming from pinned host memory and
-results returned to it inside the timed region.  ``--impl reference`` times the reference's CPU route
+public module call (``mk.capture`` of a block whose forward calls its seven ``PackedLinear``: one
+CUDA graph per call with its host copies as nodes) with activations coming from pinned host memory
+and results returned to it inside the timed region.  ``--impl reference`` times the reference's CPU route
 (unpack, reconstruct, ``F.linear``) through ``oracle/cpu_path.py`` on the host cores.
 """
 
@@ -55,6 +56,9 @@ def matvec_bytes(out_rows: int, width: int, rows_in: int, bits: int = BITS, grou
     """Algorithmic bytes of one packed matvec: codes + fp16 scales + activations + outputs + table."""
     return (out_rows * width * bits // 8 + out_rows * (width // group) * 2 + rows_in * width * 2 +
             rows_in * out_rows * 2 + 4 * levels)
+
+
+E2E_STREAMS = 4
 
 
 def pass_bytes(blocks: int) -> int:
@@ -194,19 +198,39 @@ def run_pass_resident(blocks, inputs, outputs) -> int:
     return launches
 
 
-def run_pass_e2e(blocks, host_inputs, host_outputs, device) -> tuple[int, int]:
-    """One step through ``PackedLinear.forward`` with host-resident activations and results."""
+class BlockCall(torch.nn.Module):
+    """The seven linears of one block as a module call: (hidden, mlp) -> the seven outputs."""
+
+    def __init__(self, block) -> None:
+        super().__init__()
+        self.block = block
+
+    def forward(self, hidden, mlp):
+        b = self.block
+        return (b.q_proj(hidden), b.k_proj(hidden), b.v_proj(hidden), b.o_proj(hidden), b.gate_proj(hidden),
+                b.up_proj(hidden), b.down_proj(mlp))
+
+
+def run_pass_e2e(calls, host_inputs, streams) -> tuple[int, int]:
+    """One step through the public module call (``mk.capture`` of a block of ``PackedLinear``) with
+    host-resident activations and results: the copies from and to pinned host memory are part of
+    every call.  The calls are independent, so they alternate between ``streams`` and one call's
+    copies overlap another's kernels; the current stream waits for all of them at the end."""
     h2d = d2h = 0
+    main = torch.cuda.current_stream()
+    for stream in streams:
+        stream.wait_stream(main)
+    turn = 0
     for rows in ROW_COUNTS:
-        for block in blocks:
-            for names, width in ((("q", "k", "v"), 4096), (("o",), 4096), (("gate", "up"), 4096), (("down",), 14336)):
-                x_host = host_inputs[rows][width]
-                x = x_host.to(device, non_blocking=True)
-                h2d += x_host.numel() * 2
-                for name in names:
-                    y = getattr(block, PROJECTION[name])(x)
-                    host_outputs[rows][name].copy_(y, non_blocking=True)
-                    d2h += y.numel() * 2
+        hidden, mlp = host_inputs[rows][4096], host_inputs[rows][14336]
+        for call in calls:
+            with torch.cuda.stream(streams[turn % len(streams)]):
+                outputs = call(hidden, mlp)
+            turn += 1
+            h2d += (hidden.numel() + mlp.numel()) * 2
+            d2h += sum(y.numel() for y in outputs) * 2
+    for stream in streams:
+        main.wait_stream(stream)
     return h2d, d2h
 
 
@@ -517,8 +541,6 @@ def main() -> None:
     inputs = {m: {k: torch.randn(m, k, generator=generator, device=device).half() for k in widths} for m in ROW_COUNTS}
     outputs = {m: {n: torch.empty(m, n, device=device, dtype=torch.float16) for n in outs} for m in ROW_COUNTS}
     host_inputs = {m: {k: inputs[m][k].cpu().pin_memory() for k in widths} for m in ROW_COUNTS}
-    host_outputs = {m: {name: torch.empty(m, n, dtype=torch.float16).pin_memory() for name, (n, _) in LLAMA8B.items()}
-                    for m in ROW_COUNTS}
 
     # ---- resident-input timing: W warm-up steps, then exactly K steps between two events ----
     launches_per_step = run_pass_resident(blocks, inputs, outputs)
@@ -544,16 +566,20 @@ def main() -> None:
         torch.cuda.synchronize()
         eager_ms = start.elapsed_time(stop) / args.steps
         # ---- end-to-end timing through the module call with host activations ----
-        with torch.inference_mode():
-            for _ in range(max(3, args.warmup)):
-                run_pass_e2e(blocks, host_inputs, host_outputs, device)
-            torch.cuda.synchronize()
-            start.record()
-            for _ in range(args.steps):
-                h2d, d2h = run_pass_e2e(blocks, host_inputs, host_outputs, device)
-            stop.record()
-            torch.cuda.synchronize()
-            e2e_ms = start.elapsed_time(stop) / args.steps
+        import mlkit_b200 as mk
+
+        calls = [mk.capture(BlockCall(block), synchronize=False) for block in blocks]
+        streams = [torch.cuda.Stream() for _ in range(E2E_STREAMS)]
+        for _ in range(max(3, args.warmup)):
+            run_pass_e2e(calls, host_inputs, streams)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(args.steps):
+            h2d, d2h = run_pass_e2e(calls, host_inputs, streams)
+        stop.record()
+        torch.cuda.synchronize()
+        e2e_ms = start.elapsed_time(stop) / args.steps
+        del calls
         alone, grouped = per_layer_tables(blocks, inputs, outputs, peak)
     step_bytes = pass_bytes(BLOCKS)
     value = step_bytes / resident_ms / 1e6

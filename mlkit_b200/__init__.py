@@ -16,6 +16,8 @@ from mlkit_b200.inference import (
     PackedLinear,
     benchmark,
     benchmark_model,
+    CapturedCall,
+    capture,
     fuse_siblings,
     layout_for,
     optimize,
@@ -48,7 +50,7 @@ __version__ = "0.1.0"
 __all__ = [
     "BenchmarkResult", "Ctx", "Grid", "LayerReport", "Model", "PackedEmbedding", "PackedLayout", "PackedLinear",
     "Q", "QModel", "Scaled", "as_q", "benchmark", "benchmark_model", "codec", "decode_feedback", "decode_scaled",
-    "decoder", "fuse_siblings", "grid", "hadamard", "install_transform", "int", "layer_seed", "layout_for", "load",
+    "CapturedCall", "capture", "decoder", "fuse_siblings", "grid", "hadamard", "install_transform", "int", "layer_seed", "layout_for", "load",
     "load_checkpoint", "nf4", "optimize", "pack", "packed_compatible", "quantize", "randomized_transform",
     "record_transform", "registered", "rht", "rotate_inputs", "save", "scaled", "structured_transform",
     "transform_factor", "unpack",

@@ -428,3 +428,53 @@ def test_reference_checkpoint_with_a_rotation_installs_the_hook(tmp_path):
     assert again["transforms"] == json.loads((source / "mlkit.json").read_text())["transforms"]
     before, after = _stored_tensors(source), _stored_tensors(tmp_path / "again")
     assert set(before) == set(after) and all(torch.equal(before[key], after[key]) for key in before)
+
+
+def test_captured_call_matches_eager_with_device_and_host_inputs():
+    """``mk.capture``: one graph per input signature; host inputs (pinned or not) and host results are
+    copy nodes of the graph.  Every replay equals the eager call bit for bit, also after the input's
+    contents change and with sibling launches inside the captured module."""
+    import torch.nn as nn
+
+    class Pair(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate_proj = nn.Linear(256, 384, bias=False)
+            self.up_proj = nn.Linear(256, 384, bias=False)
+            self.down_proj = nn.Linear(384, 256, bias=True)
+
+        def forward(self, x):
+            hidden = torch.nn.functional.silu(self.gate_proj(x)) * self.up_proj(x)
+            return self.down_proj(hidden), hidden
+
+    torch.manual_seed(3)
+    model = Pair().half().cuda()
+    quantized = mk.quantize(model, mk.int(4, group=128))
+    fast = mk.optimize(quantized, backend="packed")
+    assert fast.module.gate_proj._siblings is not None
+    call = mk.capture(fast.module)
+    with torch.inference_mode():
+        for rows in (1, 3):
+            for trial in range(3):
+                x = torch.randn(rows, 256, device="cuda").half()
+                expected = [t.clone() for t in fast.module(x)]
+                got = call(x)
+                assert all(t.is_cuda for t in got)
+                assert all(torch.equal(a, b) for a, b in zip(got, expected))
+                pinned = x.cpu().pin_memory()
+                for host in (x.cpu(), pinned):
+                    got = call(host)
+                    assert all(not t.is_cuda for t in got)
+                    assert all(torch.equal(a, b.cpu()) for a, b in zip(got, expected))
+                # a pinned input is read in place: new contents, same address, same graph
+                pinned.copy_(-x.cpu())
+                expected = [t.clone() for t in fast.module(-x)]
+                got = call(pinned)
+                assert all(torch.equal(a, b.cpu()) for a, b in zip(got, expected))
+    assert len(call.entries) == 2 * (1 + 1 + 3)   # per row count: device, pageable host, one pinned tensor per trial
+    lazy = mk.capture(fast.module, synchronize=False)
+    host = torch.randn(2, 256, device="cpu").half().pin_memory()
+    out = lazy(host)
+    lazy.wait()
+    with torch.inference_mode():
+        assert torch.equal(out[0], fast.module(host.cuda())[0].cpu())
