@@ -48,8 +48,9 @@ BITS, GROUP = 4, 128
 METRIC = "packed_int4_g128_gemv_hbm_gbps"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the profiler
 # capture summarised in the file named beside it (a past capture, not a counter of this run)
-DOMINANT_DRAM_BYTES = None
-DOMINANT_DRAM_SOURCE = None
+DOMINANT_DRAM_BYTES = 30352000
+DOMINANT_DRAM_SOURCE = ("dram__bytes_read.sum + dram__bytes_write.sum of gemv_stream_kernel<4,0,1,2,3> on 4096->14336, M=1, "
+                        "one ncu --set full capture (profiles/gemv_stream_gate_4096x14336_M1.md): 30.352 MB read, 0 written")
 
 
 def matvec_bytes(out_rows: int, width: int, rows_in: int, bits: int = BITS, group: int = GROUP, levels: int = 16) -> int:
@@ -551,11 +552,13 @@ def main() -> None:
     with ClockSampler(local_rank) as sampler:
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
+        torch.cuda.profiler.start()     # a profiler started with its collection off sees the timed region only
         start.record()
         for _ in range(args.steps):
             graph.replay()
         stop.record()
         torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
         resident_ms = start.elapsed_time(stop) / args.steps
         launches = launches_per_step * args.steps
         # the same step launched eagerly (host launch path included)

@@ -135,7 +135,7 @@ class PackedLinear(nn.Module):
         scales = quantized.params["scales"]
         scale_dtype = SCALE_STORAGE_DTYPES.get(str(quantized.metadata.get("scale_fmt")), scales.dtype)
         zero = quantized.params.get("zero")
-        self.register_buffer("packed", pack(quantized.codes, self.code_bits).to(device))
+        self.register_buffer("packed", quantized.packed_stream(self.code_bits).to(device))
         self.register_buffer("scales", scales.to(device=device, dtype=scale_dtype).contiguous())
         self.register_buffer("values", quantized.params["values"].to(device=device, dtype=torch.float32).contiguous())
         self.register_buffer("zeros", None if zero is None else zero.to(device=device, dtype=scale_dtype).contiguous())

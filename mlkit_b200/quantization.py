@@ -49,6 +49,15 @@ class Q:
         self.decode = decode
         self.codec = codec
         self.metadata = dict(metadata or {})
+        self._stream: tuple[Tensor, Tensor, int, int] | None = None   # (packed, codes it came from, their version, bits)
+
+    def packed_stream(self, bits: int) -> Tensor:
+        """``pack(self.codes, bits)``; the stream the device encoder wrote beside the codes is returned
+        as it is while the codes are the same tensor, unmodified."""
+        held = self._stream
+        if (held is not None and held[1] is self.codes and held[2] == _version_of(self.codes) and held[3] == bits):
+            return held[0]
+        return pack(self.codes, bits)
 
     @property
     def w(self) -> Tensor:
@@ -164,6 +173,10 @@ def decode_feedback(codes: Tensor, *, scales: Tensor, values: Tensor, group: int
 # --------------------------------------------------------------------------------- bit streams
 
 _CHUNK_CODES = 1 << 22  # a multiple of eight codes, so every chunk ends on a byte
+
+
+def _version_of(tensor: Tensor) -> int:
+    return 0 if tensor.is_inference() else tensor._version
 
 
 def pack(codes: Tensor, bits: int) -> Tensor:
@@ -418,15 +431,17 @@ class Scaled:
 
             if not torch.isfinite(weight).all():
                 raise ValueError("scaled requires a finite floating-point weight matrix")
-            _, scales16, codes = kernels.rtn_encode(weight, levels, group=group, bits=bits, integer_grid=self.grid.integer,
+            stream, scales16, codes = kernels.rtn_encode(weight, levels, group=group, bits=bits, integer_grid=self.grid.integer,
                                                     low=self._low, high=self._high, reciprocal=self._reciprocal, codes=True)
             scales = scales16.float()
-            return Q(
+            encoded = Q(
                 bits=bits * weight.numel() + scales.numel() * 16, codes=codes,
                 params={"scales": scales, "values": levels, "group": group, "offset": 0, "zero": None},
                 decode=decode_scaled, codec="scaled",
                 metadata={"code_bits": bits, "scale_fmt": self.scale_fmt, "trainable": ["scales"]},
             )
+            encoded._stream = (stream, codes, _version_of(codes), bits)
+            return encoded
         low, high = _group_range(weight, group)
         if not (torch.isfinite(low).all() and torch.isfinite(high).all()):
             raise ValueError("scaled requires a finite floating-point weight matrix")

@@ -129,7 +129,7 @@ def _packed_parts(quantized: Q, device: torch.device) -> tuple[Tensor, Tensor, T
     bits, group = int(quantized.metadata["code_bits"]), int(quantized.params["group"])
     if quantized.params.get("zero") is not None:
         raise ValueError("tensor-parallel decode covers symmetric formats")
-    return (pack(quantized.codes, bits).to(device), quantized.params["scales"].to(device).half(),
+    return (quantized.packed_stream(bits).to(device), quantized.params["scales"].to(device).half(),
             quantized.params["values"].to(device).float().contiguous(), bits, group)
 
 

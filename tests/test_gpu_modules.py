@@ -478,3 +478,14 @@ def test_captured_call_matches_eager_with_device_and_host_inputs():
     lazy.wait()
     with torch.inference_mode():
         assert torch.equal(out[0], fast.module(host.cuda())[0].cpu())
+
+
+def test_device_encoder_stream_is_reused_only_while_codes_are_untouched():
+    weight = torch.randn(48, 256, device="cuda")
+    q = mk.int(4, group=128)(weight, mk.Ctx("layer", device="cuda"))
+    assert q._stream is not None
+    assert torch.equal(q.packed_stream(4), mk.pack(q.codes, 4))
+    assert q.packed_stream(4) is q._stream[0]
+    q.codes[0, 0] = (q.codes[0, 0] + 1) % 16          # in-place edit: the stream on record is stale
+    assert q.packed_stream(4) is not q._stream[0]
+    assert torch.equal(q.packed_stream(4), mk.pack(q.codes, 4))
