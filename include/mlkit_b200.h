@@ -144,6 +144,34 @@ int mkb_gemv_static(const void* x, const uint8_t* packed, const void* scales, co
 int mkb_gemv_static_status(int* status);
 
 /*
+ * Fused dequantise + GEMM for more activation rows than the matvec takes:
+ *   y[m,n] = sum_k x[m,k] * fp16(lut[code[n,k]] * scale[n, k / 128]) (+ bias[n]),  1 <= M <= 128.
+ * Replaces the dense route the reference takes above eight rows, which reconstructs the whole weight
+ * in global memory and hands it to a library GEMM (PackedLinear.forward,
+ * src/mlkit/inference/packed_linear.py:153-154 with the `weight` property at :110-130).  The weights
+ * are rounded to fp16 exactly as that reconstruction rounds them, products are accumulated in fp32
+ * on the tensor cores (tcgen05.mma, weights through tensor memory), the result is rounded once.
+ * Covers symmetric INT4 on the integer grid -8..7 (bits = 4, lut_len = 16, integer_grid = 1,
+ * grid_minimum = -8, zeros = null), fp16 activations and scales, group = 128, K a multiple of 128,
+ * x and packed 16-byte aligned; anything else returns MKB_E_UNSUPPORTED and the caller keeps the
+ * dense route.  Argument meaning as for mkb_gemv_ws.
+ * workspace: device memory of at least mkb_gemm_workspace_bytes(M, N, K) bytes, 16-byte aligned,
+ *         ZERO-FILLED ONCE before its first use; the kernel leaves it ready for the next call.  Calls
+ *         that may overlap on the GPU need workspaces of their own.
+ * mkb_gemm_status reads the workspace's status word (synchronises with the device): non-zero when
+ * a bounded wait inside a call that used this workspace expired (its results are not valid).
+ */
+int64_t mkb_gemm_workspace_bytes(int M, int N, int K);
+int mkb_gemm(const void* x, const uint8_t* packed, const void* scales, const float* lut,
+             const void* zeros, const void* bias, void* y,
+             int M, int N, int K, int group, int bits, int lut_len,
+             int x_dtype, int scale_dtype,
+             int64_t packed_row_stride, int64_t scale_row_stride,
+             int integer_grid, float grid_minimum,
+             void* workspace, int64_t workspace_bytes, void* stream);
+int mkb_gemm_status(const void* workspace, int* status);
+
+/*
  * Unpack and dequantise a packed weight:
  *   codes_out[n,k] = code (uint8), w_out[n,k] = lut[code] * scale (+ zero) rounded once to out_dtype.
  * Either output may be null.  The multiply and the add are separate IEEE binary32 operations,

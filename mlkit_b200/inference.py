@@ -203,6 +203,17 @@ class PackedLinear(nn.Module):
             raise ValueError("packed inference requires CUDA inputs")
         rows = inputs.numel() // width
         if rows > self.maximum_fused_rows or rows == 0:
+            if (rows and self.layout is not None and not torch.compiler.is_compiling() and self._dense_weight is None
+                    and not (inputs.requires_grad and torch.is_grad_enabled())
+                    and kernels.gemm_supported(rows, width=width, group=self.group, bits=self.code_bits, dtype=inputs.dtype,
+                                               scales=self.scales, zeros=self.zeros, integer_grid=self.integer_grid,
+                                               grid_minimum=self.grid_minimum, levels=self.values.numel())):
+                # up to 128 rows: the weight is reconstructed inside the GEMM kernel, tile by tile
+                flat = inputs.reshape(rows, width).contiguous()
+                out = kernels.packed_gemm(flat, self.packed, self.scales, self.values, self.bias,
+                                          inputs.new_empty((rows, self.out_features)), group=self.group,
+                                          bits=self.code_bits, integer_grid=True, grid_minimum=self.grid_minimum)
+                return out.view(inputs.shape[:-1] + (self.out_features,))
             return functional.linear(inputs, self.weight.to(inputs.dtype), self.bias)
         if inputs.requires_grad and torch.is_grad_enabled():
             raise RuntimeError("packed CUDA inference does not support autograd")

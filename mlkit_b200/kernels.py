@@ -89,6 +89,66 @@ def integer_grid_of(values: Tensor) -> tuple[bool, float]:
     return exact, low
 
 
+_gemm_workspaces: dict[tuple[int, int], Tensor] = {}
+GEMM_MAXIMUM_ROWS = 128
+
+
+def gemm_workspace(device: torch.device, rows: int, outputs: int, width: int) -> Tensor:
+    """Zero-initialised scratch of the fused dequantise + GEMM kernel, one per (device, stream), grown to
+    the largest request; the kernel leaves it zeroed where it must be."""
+    need = _native.library().mkb_gemm_workspace_bytes(rows, outputs, width)
+    if need <= 0:
+        raise ValueError(f"no fused GEMM for {rows} rows, {outputs} outputs, width {width}")
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(device).cuda_stream)
+    held = _gemm_workspaces.get(key)
+    if held is None or held.numel() < need:
+        held = _gemm_workspaces[key] = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+    return held
+
+
+def gemm_status() -> int:
+    """Non-zero when a bounded wait expired inside a fused GEMM that used a pooled workspace."""
+    import ctypes
+
+    worst = 0
+    for held in _gemm_workspaces.values():
+        value = ctypes.c_int(0)
+        with torch.cuda.device(held.device):
+            _native.check(_native.library().mkb_gemm_status(held.data_ptr(), ctypes.byref(value)), "gemm_status")
+        worst = max(worst, value.value)
+    return worst
+
+
+def gemm_supported(rows: int, *, width: int, group: int, bits: int, dtype: torch.dtype, scales: Tensor,
+                   zeros: Tensor | None, integer_grid: bool, grid_minimum: float, levels: int) -> bool:
+    """Whether ``packed_gemm`` covers the layer (the C entry point checks the same and more)."""
+    return (1 <= rows <= GEMM_MAXIMUM_ROWS and bits == 4 and group == 128 and width % 128 == 0 and zeros is None
+            and dtype == torch.float16 and scales.dtype == torch.float16 and bool(integer_grid)
+            and float(grid_minimum) == -8.0 and levels == 16)
+
+
+def packed_gemm(x: Tensor, packed: Tensor, scales: Tensor, values: Tensor, bias: Tensor | None, out: Tensor, *,
+                group: int, bits: int, integer_grid: bool, grid_minimum: float) -> Tensor:
+    """``out[M, N] = x[M, K] @ dequant(packed)^T (+ bias)`` for up to 128 rows in one launch (``mkb_gemm``)."""
+    device = _require_cuda(x, packed, scales, values, bias, out)
+    rows, width = x.shape
+    outputs = out.shape[1]
+    if not x.is_contiguous() or not out.is_contiguous():
+        raise ValueError("packed_gemm needs contiguous activations and outputs")
+    if bias is not None and bias.dtype != x.dtype:
+        bias = bias.to(x.dtype)
+    with torch.cuda.device(device):
+        workspace = gemm_workspace(device, rows, outputs, width)
+        status = _native.library().mkb_gemm(
+            x.data_ptr(), packed.data_ptr(), scales.data_ptr(), values.data_ptr(), None, _pointer(bias), out.data_ptr(),
+            rows, outputs, width, group, bits, values.numel(), _tag(x.dtype, "activation"), _tag(scales.dtype, "scale"),
+            width * bits // 8, scales.stride(0) if scales.dim() == 2 else -(-width // group), int(integer_grid),
+            float(grid_minimum), workspace.data_ptr(), workspace.numel(), torch.cuda.current_stream().cuda_stream)
+    _native.check(status, "packed_gemm")
+    return out
+
+
 def packed_matvec(x: Tensor, packed: Tensor, scales: Tensor, values: Tensor, zeros: Tensor | None,
                   bias: Tensor | None, out: Tensor, *, group: int, bits: int, integer_grid: bool = False,
                   grid_minimum: float = 0.0, kernel: str = "auto", packed_row_stride: int | None = None,
