@@ -8,17 +8,21 @@
 // the reference's reconstruction holds -- and stores them to tensor memory (TMEM) as the A operand of
 // tcgen05.mma.  Activations are the B operand in shared memory, accumulators live in TMEM in fp32.
 //
-// Work: a unit is 128 weight rows x one K slab; one CTA computes one unit.  Roles (416 threads):
-//   * warps 0-7, "decoders": thread t owns row t % 128 and half t / 128 of every 128-code block.  The
-//     128 x 64 B code tile of a block arrives by cp.async in a deep shared-memory ring (the ring is what
-//     keeps enough bytes in flight towards HBM); the thread reads its 32 bytes, turns each byte pair
-//     into two fp16 weights (PRMT + LOP3 + HFMA2 + HMUL2) in natural K order and stores 32 columns of
-//     the A buffer of that block's parity (tcgen05.st).  At the end of the unit the same threads read
-//     the accumulators (tcgen05.ld) and store y, or a partial when K is split over slabs;
-//   * warps 8-11, "loaders": copy the [Mpad x 128] activation tile of every block into a three-stage
-//     ring in the canonical K-major core-matrix layout (cp.async, 16 B = 8 K of one row);
-//   * warp 12, "issuer": one lane waits for A and B of a block, issues its eight tcgen05.mma
-//     (M128, N = Mpad, K16) and commits them to the mbarriers that free the A buffer and the B stage.
+// Work: a unit is 128 weight rows x one K slab; one CTA computes one unit.  Roles (512 threads):
+//   * warps 0-7, "decoders": warp w owns rows 32 * (w % 4) .. + 31 and the 128-code blocks of parity w / 4,
+//     so the two warp groups alternate and one decodes while the other's block is multiplied.  The 32 x
+//     64 B code tile of a block arrives by cp.async in the warp's own shared-memory ring (six stages; the
+//     rings are what keeps enough bytes in flight towards HBM, and only the warp itself reads its ring, so
+//     the loop has no CTA-wide barrier); a thread reads the 64 bytes of its row, turns each byte into two
+//     fp16 weights (PRMT + LOP3 + HFMA2 + HMUL2) in natural K order and stores the 64 columns of one of four
+//     A buffers (tcgen05.st).  At the end of the unit the same threads read the accumulators (tcgen05.ld) and store y,
+//     or a partial when K is split over slabs;
+//   * warps 8-11, "loaders": copy the [Mpad x 128] activation tile of every block into a ring of three to
+//     eight stages in the canonical K-major core-matrix layout (cp.async, 16 B = 8 K of one row);
+//   * warps 12-15, "issuers": one lane of issuer i waits for A and B of the blocks t = i (mod issuers), issues
+//     their eight tcgen05.mma each (M128, N = Mpad, K16) into its own accumulator columns and commits them to
+//     the mbarriers that free the A buffer and the B stage.  Issuing a step costs the thread about a hundred
+//     cycles whatever N is, so two (Mpad > 64) or four issuers share the blocks.
 // With K split over slabs the last CTA of a row block (atomic counter) adds the partials in slab order.
 // All hand-offs are mbarriers; every wait is bounded: on expiry the CTA records a status word, stops
 // issuing and drains.
@@ -29,15 +33,19 @@ namespace {
 
 constexpr int kDecoders = 256;
 constexpr int kLoaders = 128;
-constexpr int kThreadsG = kDecoders + kLoaders + 32;
-constexpr int kCodeStage = 128 * 64;      // bytes of codes per block of 128 K: 128 rows x 64 B
-constexpr int kCodeStages = 12;           // 96 KB of codes in flight per SM
-constexpr int kBStages = 3;
+constexpr int kMaxIssuers = 4;
+constexpr int kThreadsG = kDecoders + kLoaders + 32 * kMaxIssuers;   // warps 12..15 issue
+constexpr int kWarpStage = 32 * 64;       // bytes of codes per block of 128 K and decoder warp: 32 rows x 64 B
+constexpr int kCodeStages = 6;            // ring stages per decoder warp: 8 warps x 6 x 2 KB = 96 KB in flight per SM
+constexpr int kCodeBytes = 8 * kCodeStages * kWarpStage;
+constexpr int kABuffers = 4;              // A operand buffers in tensor memory, 64 columns each
+constexpr int kMaxBStages = 8;            // activation tiles in shared memory: as many as fit, at least 3
 constexpr int kMaxUnitBlocks = 32;        // blocks of 128 K per unit: its scales sit in shared memory
 constexpr int kScalePitch = kMaxUnitBlocks + 2;   // halves per row of the scale table (17 words: no bank conflicts)
-constexpr int kTmemColumnsG = 256;        // A[2]: 0..127; D: 128..128 + Mpad
+constexpr int kTmemColumnsG = 512;        // A[4]: 0..255; D_i: 256 + i * Mpad, one per issuer
+constexpr int kDColumn = kABuffers * 64;
 constexpr int kMaxRowsG = 128;
-constexpr uint32_t kSpinLimitG = 4000000;
+constexpr uint32_t kSpinLimitG = 200000;   // tries of up to 20 us each: a few seconds
 
 struct GemmArgs {
   const __half* x;
@@ -50,14 +58,14 @@ struct GemmArgs {
   int* status;       // set non-zero when a bounded wait expired
   int M, Mpad, N, K;
   int64_t packed_row_stride, scale_row_stride;
-  int row_blocks, slabs, slab_blocks, k_blocks, b_stage_bytes;
+  int row_blocks, slabs, slab_blocks, k_blocks, b_stage_bytes, b_stages, issuers;
 };
 
 struct GemmBarriers {
-  uint64_t a_full[2];            // decoders -> issuer (256 arrivals)
-  uint64_t a_empty[2];           // issuer -> decoders (tcgen05.commit)
-  uint64_t b_full[kBStages];     // loaders -> issuer (128 arrivals)
-  uint64_t b_empty[kBStages];    // issuer -> loaders (tcgen05.commit)
+  uint64_t a_full[kABuffers];    // decoders -> issuer (128 arrivals: the four warps that own the block)
+  uint64_t a_empty[kABuffers];   // issuer -> decoders (tcgen05.commit)
+  uint64_t b_full[kMaxBStages];  // loaders -> issuer (128 arrivals)
+  uint64_t b_empty[kMaxBStages]; // issuer -> loaders (tcgen05.commit)
   uint64_t d_full;               // issuer -> decoders: every step of the unit is complete
 };
 
@@ -76,8 +84,10 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* failed) {
   uint32_t done = 0;
   for (uint32_t spins = 0; spins < kSpinLimitG; ++spins) {
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
-                 : "=r"(done) : "r"(shared_address(bar)), "r"(parity) : "memory");
+    // the hint lets the hardware park the thread (up to that many nanoseconds, or until the phase completes)
+    // instead of spinning through the issue slots the decoders need
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+                 : "=r"(done) : "r"(shared_address(bar)), "r"(parity), "r"(20000u) : "memory");
     if (done) return true;
     if ((spins & 1023) == 1023 && *failed) return false;
   }
@@ -96,12 +106,26 @@ template <int BYTE>
 __device__ __forceinline__ uint32_t weight_pair(uint32_t word, __half2 scale) {
   constexpr uint32_t selector = BYTE == 0 ? 0x1010u : BYTE == 1 ? 0x2121u : BYTE == 2 ? 0x3232u : 0x0303u;
   const uint32_t both = __byte_perm(word, word, selector);
-  const uint32_t biased = (both & 0x00f0000fu) | 0x64006400u;
+  uint32_t biased;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(biased) : "r"(both), "r"(0x00f0000fu), "r"(0x64006400u));   // (both & mask) | exponent
   const __half2 one_sixteenth = __halves2half2(__ushort_as_half(0x3c00), __ushort_as_half(0x2c00));  // (1, 1/16)
   const __half2 offset = __halves2half2(__ushort_as_half(0xe408), __ushort_as_half(0xd480));         // (-1032, -72)
   const __half2 centred = __hfma2(*reinterpret_cast<const __half2*>(&biased), one_sixteenth, offset);
   const __half2 weight = __hmul2(centred, scale);
   return *reinterpret_cast<const uint32_t*>(&weight);
+}
+
+// cp.async.wait_group with a run-time count (the instruction takes an immediate)
+__device__ __forceinline__ void wait_for_all_but(int pending) {
+  switch (pending) {
+    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+  }
 }
 
 __device__ __forceinline__ void store_columns16(uint32_t address, const uint32_t* r) {
@@ -112,9 +136,9 @@ __device__ __forceinline__ void store_columns16(uint32_t address, const uint32_t
 
 __global__ void __launch_bounds__(kThreadsG, 1) gemm_umma_kernel(const GemmArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
-  uint8_t* code_s = smem;                                               // [stages][128 rows][64 B], 16-byte chunks swizzled
-  uint8_t* b_s = code_s + size_t(kCodeStages) * kCodeStage;             // [3][16 chunks][Mpad + 1][16 B]
-  __half* scale_s = reinterpret_cast<__half*>(b_s + size_t(kBStages) * a.b_stage_bytes);   // [128][kScalePitch]
+  uint8_t* code_s = smem;                                               // [8 warps][stages][32 rows][64 B], 16-byte chunks swizzled
+  uint8_t* b_s = code_s + kCodeBytes;             // [b_stages][16 chunks][Mpad + 1][16 B]
+  __half* scale_s = reinterpret_cast<__half*>(b_s + size_t(a.b_stages) * a.b_stage_bytes);   // [128][kScalePitch]
   __shared__ __align__(8) GemmBarriers bars;
   __shared__ uint32_t tmem_base_s;
   __shared__ int failed_s, last_s;
@@ -134,27 +158,32 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_umma_kernel(const GemmArgs 
   if (tid == 0) {
     failed_s = 0;
     last_s = 0;
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&bars.a_full[b], kDecoders);
+    for (int b = 0; b < kABuffers; ++b) {
+      mbar_init(&bars.a_full[b], kDecoders / 2);
       mbar_init(&bars.a_empty[b], 1);
     }
-    for (int b = 0; b < kBStages; ++b) {
+    for (int b = 0; b < kMaxBStages; ++b) {
       mbar_init(&bars.b_full[b], kLoaders);
       mbar_init(&bars.b_empty[b], 1);
     }
-    mbar_init(&bars.d_full, 1);
+    mbar_init(&bars.d_full, a.issuers);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
 
-  // ---- decoders: the code ring.  Copy i of a stage is chunk i % 4 of row i / 4; chunk c of row r sits at
-  // chunk position c ^ ((r >> 1) & 3), so a quarter warp reading one chunk of eight rows meets all banks once
+  // ---- decoders: one code ring per warp.  Warp w decodes rows 32 * (w % 4) .. + 31 of the blocks of
+  // parity w / 4, so a stage is 32 rows x 64 B; copy i of a stage is chunk i % 4 of row i / 4, and chunk c
+  // of row r sits at chunk position c ^ ((r >> 1) & 3): a quarter warp reading one chunk of eight rows
+  // meets every bank once.  Nothing but the warp itself reads its ring: no CTA-wide barrier per block.
+  const int parity = (warp >> 2) & 1;
+  const int own_blocks = tid < kDecoders ? (blocks + 1 - parity) >> 1 : 0;
   int issued = 0, issue_slot = 0;
-  const uint8_t* code_source[2] = {nullptr, nullptr};
-  uint32_t code_target[2] = {0u, 0u};
+  const uint8_t* code_source[4] = {nullptr, nullptr, nullptr, nullptr};
+  uint32_t code_target[4] = {0u, 0u, 0u, 0u};
   auto issue_codes = [&]() {
-    if (issued < blocks) {
+    if (issued < own_blocks) {
 #pragma unroll
-      for (int j = 0; j < 2; ++j) async_copy16(code_target[j] + issue_slot * kCodeStage, code_source[j] + int64_t(issued) * 64);
+      for (int j = 0; j < 4; ++j)
+        async_copy16(code_target[j] + issue_slot * kWarpStage, code_source[j] + int64_t(2 * issued + parity) * 64);
       ++issued;
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -162,11 +191,11 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_umma_kernel(const GemmArgs 
   };
   if (tid < kDecoders) {
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int i = tid + j * kDecoders, r = i >> 2, c = i & 3;
-      const int64_t global_row = min(row_block * 128 + r, a.N - 1);
+    for (int j = 0; j < 4; ++j) {
+      const int i = lane + 32 * j, r = i >> 2, c = i & 3;
+      const int64_t global_row = min(row_block * 128 + (warp & 3) * 32 + r, a.N - 1);
       code_source[j] = a.packed + global_row * a.packed_row_stride + int64_t(first_block) * 64 + c * 16;
-      code_target[j] = shared_address(code_s) + r * 64 + ((c ^ ((r >> 1) & 3)) << 4);
+      code_target[j] = shared_address(code_s) + warp * (kCodeStages * kWarpStage) + r * 64 + ((c ^ ((r >> 1) & 3)) << 4);
     }
 #pragma unroll
     for (int d = 0; d < kCodeStages - 1; ++d) issue_codes();
@@ -178,7 +207,7 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_umma_kernel(const GemmArgs 
     scale_s[r * kScalePitch + t] = __ldg(a.scales + global_row * a.scale_row_stride + first_block + t);
   }
   // rows M..Mpad of the activation tiles are never copied: they read as zero
-  for (int i = tid; i < kBStages * a.b_stage_bytes / 16; i += kThreadsG)
+  for (int i = tid; i < a.b_stages * a.b_stage_bytes / 16; i += kThreadsG)
     reinterpret_cast<uint4*>(b_s)[i] = make_uint4(0u, 0u, 0u, 0u);
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -190,38 +219,43 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_umma_kernel(const GemmArgs 
     // ================================ decoders ================================
     const int r = tid & 127, half_block = tid >> 7;
     const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
-    const int swizzle = (r >> 1) & 3;
-    const uint8_t* my_codes = code_s + r * 64;
+    const int swizzle = (lane >> 1) & 3;
+    const uint8_t* my_codes = code_s + warp * (kCodeStages * kWarpStage) + lane * 64;
     const __half* my_scales = scale_s + r * kScalePitch;
     int slot = 0;
     bool alive = true;
-    for (int t = 0; t < blocks && alive; ++t) {
+    for (int j = 0; j < own_blocks && alive; ++j) {
+      const int t = 2 * j + parity;                   // the block this warp decodes now
       asm volatile("cp.async.wait_group %0;" ::"n"(kCodeStages - 2) : "memory");
-      asm volatile("bar.sync 1, 256;" ::: "memory");   // every decoder's share of stage t has landed
-      issue_codes();                                    // refills the stage read one iteration ago
-      const uint8_t* stage = my_codes + slot * kCodeStage;
+      __syncwarp();                                    // every lane's share of the stage has landed
+      issue_codes();                                   // refills the stage read one iteration ago
+      const uint8_t* stage = my_codes + slot * kWarpStage;
       slot = slot + 1 == kCodeStages ? 0 : slot + 1;
-      const uint4 lo = *reinterpret_cast<const uint4*>(stage + (((2 * half_block) ^ swizzle) << 4));
-      const uint4 hi = *reinterpret_cast<const uint4*>(stage + (((2 * half_block + 1) ^ swizzle) << 4));
-      const __half2 scale = __half2half2(my_scales[t]);
-      const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-      uint32_t weights[32];
+      uint4 chunk[4];
 #pragma unroll
-      for (int w = 0; w < 8; ++w) {
-        weights[4 * w] = weight_pair<0>(words[w], scale);
-        weights[4 * w + 1] = weight_pair<1>(words[w], scale);
-        weights[4 * w + 2] = weight_pair<2>(words[w], scale);
-        weights[4 * w + 3] = weight_pair<3>(words[w], scale);
-      }
-      // the A buffer of this parity was last read by the steps of block t - 2
-      if (t >= 2 && !mbar_wait(&bars.a_empty[t & 1], uint32_t((t >> 1) - 1) & 1u, failed)) { alive = false; break; }
+      for (int c = 0; c < 4; ++c) chunk[c] = *reinterpret_cast<const uint4*>(stage + ((c ^ swizzle) << 4));
+      const __half2 scale = __half2half2(my_scales[t]);
+      // this A buffer was last read by the steps of block t - 4
+      if (t >= kABuffers && !mbar_wait(&bars.a_empty[t & 3], uint32_t((t >> 2) - 1) & 1u, failed)) { alive = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t a_address = tmem_base + lane_base + (t & 1) * 64 + half_block * 32;
-      store_columns16(a_address, weights);
-      store_columns16(a_address + 16, weights + 16);
+      const uint32_t a_address = tmem_base + lane_base + (t & 3) * 64;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t words[4] = {chunk[c].x, chunk[c].y, chunk[c].z, chunk[c].w};
+        uint32_t weights[16];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          weights[4 * w] = weight_pair<0>(words[w], scale);
+          weights[4 * w + 1] = weight_pair<1>(words[w], scale);
+          weights[4 * w + 2] = weight_pair<2>(words[w], scale);
+          weights[4 * w + 3] = weight_pair<3>(words[w], scale);
+        }
+        store_columns16(a_address + 16 * c, weights);
+      }
+      // publish at once: the steps of this block then run under the decode of the next two
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(&bars.a_full[t & 1]);
+      mbar_arrive(&bars.a_full[t & 3]);
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 
@@ -231,22 +265,30 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_umma_kernel(const GemmArgs 
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int n = row_block * 128 + r;
       const int half_columns = a.Mpad >> 1;
+      const int live = min(a.issuers, blocks);      // accumulators that took part in this unit
       const float bias = (a.slabs == 1 && a.bias != nullptr && n < a.N) ? __half2float(a.bias[n]) : 0.f;
       float* slot_out = a.partials + (int64_t(row_block) * a.slabs + slab) * a.Mpad * 128;
       for (int c = 0; c < half_columns; c += 8) {
         const int m0 = half_block * half_columns + c;
-        uint32_t d[8];
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7])
-                     : "r"(tmem_base + lane_base + 128 + m0) : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        float d[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) d[j] = 0.f;
+        for (int i = 0; i < live; ++i) {
+          uint32_t part[8];
+          asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                       : "=r"(part[0]), "=r"(part[1]), "=r"(part[2]), "=r"(part[3]), "=r"(part[4]), "=r"(part[5]), "=r"(part[6]), "=r"(part[7])
+                       : "r"(tmem_base + lane_base + kDColumn + i * a.Mpad + m0) : "memory");
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+          for (int j = 0; j < 8; ++j) d[j] += __uint_as_float(part[j]);
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const int m = m0 + j;
           if (a.slabs == 1) {
-            if (m < a.M && n < a.N) a.y[int64_t(m) * a.N + n] = __float2half_rn(__uint_as_float(d[j]) + bias);
+            if (m < a.M && n < a.N) a.y[int64_t(m) * a.N + n] = __float2half_rn(d[j] + bias);
           } else if (m < a.M) {
-            slot_out[m * 128 + r] = __uint_as_float(d[j]);
+            slot_out[m * 128 + r] = d[j];
           }
         }
       }
@@ -281,55 +323,78 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_umma_kernel(const GemmArgs 
     // item i of a block is chunk i % 16 (8 K) of activation row i / 16: sixteen threads read 256 contiguous
     // bytes; chunk c of row m lands at (c * (Mpad + 1) + m) * 16, the odd pitch spreads the chunks over banks
     const int ltid = tid - kDecoders;
-    const int items = a.M * 16;
     const uint32_t b_base = shared_address(b_s);
+    const __half* my_source = a.x + int64_t(ltid >> 4) * a.K + int64_t(first_block) * 128 + (ltid & 15) * 8;
+    const uint32_t my_target = b_base + ((ltid & 15) * (a.Mpad + 1) + (ltid >> 4)) * 16;
+    const int64_t row_step = int64_t(kLoaders / 16) * a.K;
     asm volatile("griddepcontrol.wait;" ::: "memory");
     bool alive = true;
-    for (int t = 0; t < blocks + 2 && alive; ++t) {
+    int stage = 0, round = 0;        // of the block being copied
+    int done_stage = 0;              // of the block `lag` steps back, whose copies are waited for
+    const int lag = a.b_stages - 1;  // tiles in flight: a tile is published `lag` steps after its copies were issued
+    for (int t = 0; t < blocks + lag && alive; ++t) {
+      if (t >= lag) {
+        // before this step's copies are issued the newest groups are blocks t - lag .. t - 1
+        wait_for_all_but(lag - 1);                             // the tile of block t - lag has landed (this thread's share)
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(&bars.b_full[done_stage]);
+        done_stage = done_stage + 1 == a.b_stages ? 0 : done_stage + 1;
+      }
       if (t < blocks) {
-        const int stage = t % kBStages;
-        if (t >= kBStages && !mbar_wait(&bars.b_empty[stage], uint32_t(t / kBStages - 1) & 1u, failed)) { alive = false; break; }
-        const __half* source = a.x + int64_t(first_block + t) * 128;
-        const uint32_t target = b_base + stage * a.b_stage_bytes;
-        for (int i = ltid; i < items; i += kLoaders) {
-          const int m = i >> 4, c = i & 15;
-          async_copy16(target + (c * (a.Mpad + 1) + m) * 16, source + int64_t(m) * a.K + c * 8);
+        if (round > 0 && !mbar_wait(&bars.b_empty[stage], uint32_t(round - 1) & 1u, failed)) { alive = false; break; }
+        // this thread copies chunk c of rows m0, m0 + 8, ...: the source advances by 8 rows, the target by 128 B
+        const __half* source = my_source + int64_t(t) * 128;
+        uint32_t target = my_target + stage * a.b_stage_bytes;
+#pragma unroll 4
+        for (int m = ltid >> 4; m < a.M; m += kLoaders / 16) {
+          async_copy16(target, source);
+          source += row_step;
+          target += 128;
         }
+        if (++stage == a.b_stages) { stage = 0; ++round; }
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
-      if (t >= 2) {
-        asm volatile("cp.async.wait_group 2;" ::: "memory");   // the tile of block t - 2 has landed (this thread's share)
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive(&bars.b_full[(t - 2) % kBStages]);
-      }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-  } else if (lane == 0) {
-    // ================================ issuer ================================
+  } else if (lane == 0 && warp - 12 < a.issuers) {
+    // ================================ issuers ================================
+    // issuer i takes the blocks t = i (mod issuers) and accumulates them in its own columns D_i: the cost
+    // of a step is in issuing it, so the issuers work side by side; the decoders add the D_i at the end
+    const int me = warp - 12;
     const uint32_t idesc = (1u << 4) | (uint32_t(a.Mpad >> 3) << 17) | (8u << 24);  // fp32 accumulate, fp16 A/B, K-major, N = Mpad, M = 128
     const uint32_t chunk_pitch = uint32_t(a.Mpad + 1) * 16;     // bytes from one 8-K chunk to the next
     // shared-memory descriptor: version 1, no swizzle, leading (next 8 K) chunk_pitch, stride (next 8 rows) 128 B
     const uint64_t desc_fixed = (uint64_t(chunk_pitch >> 4) << 16) | (uint64_t(128 >> 4) << 32) | (uint64_t(1) << 46);
-    const uint32_t d_columns = tmem_base + 128;
-    for (int t = 0; t < blocks; ++t) {
-      const int b = t & 1, stage = t % kBStages;
-      if (!mbar_wait(&bars.a_full[b], uint32_t(t >> 1) & 1u, failed)) break;
-      if (!mbar_wait(&bars.b_full[stage], uint32_t(t / kBStages) & 1u, failed)) break;
+    const uint32_t d_columns = tmem_base + kDColumn + me * a.Mpad;
+    int stage = me % a.b_stages, round = me / a.b_stages;     // the tile ring: stage t % b_stages on its (t / b_stages)-th use
+    bool sent = false;
+    for (int t = me; t < blocks; t += a.issuers) {
+      const int b = t & 3;
+      if (!mbar_wait(&bars.a_full[b], uint32_t(t >> 2) & 1u, failed)) break;
+      if (!mbar_wait(&bars.b_full[stage], uint32_t(round) & 1u, failed)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t tile = shared_address(b_s) + stage * a.b_stage_bytes;
+      uint64_t desc = desc_fixed | uint64_t((tile & 0x3FFFFu) >> 4);
+      const uint64_t desc_step = uint64_t((2 * chunk_pitch) >> 4);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const uint64_t desc = desc_fixed | uint64_t(((tile + uint32_t(2 * j) * chunk_pitch) & 0x3FFFFu) >> 4);
         const uint32_t a_columns = tmem_base + b * 64 + 8 * j;
-        const uint32_t accumulate = (t > 0 || j > 0) ? 1u : 0u;
+        const uint32_t accumulate = (t > me || j > 0) ? 1u : 0u;
         asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
                      :: "r"(d_columns), "r"(a_columns), "l"(desc), "r"(idesc), "r"(accumulate) : "memory");
+        desc += desc_step;
       }
       commit_to(&bars.a_empty[b]);
       commit_to(&bars.b_empty[stage]);
-      if (t == blocks - 1) commit_to(&bars.d_full);
+      if (t + a.issuers >= blocks) {
+        commit_to(&bars.d_full);
+        sent = true;
+      }
+      stage += a.issuers;
+      while (stage >= a.b_stages) { stage -= a.b_stages; ++round; }
     }
+    if (!sent && me >= blocks) mbar_arrive(&bars.d_full);   // a unit with fewer blocks than issuers
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -347,11 +412,11 @@ constexpr int64_t kGemmHeadBytes = 65536;
 constexpr int64_t kGemmMaxRowBlocks = kGemmHeadBytes / 4 - 1;
 
 struct GemmPlan {
-  int Mpad, row_blocks, k_blocks, slabs, slab_blocks, b_stage_bytes;
+  int Mpad, row_blocks, k_blocks, slabs, slab_blocks, b_stage_bytes, b_stages;
   size_t smem;
 };
 
-static GemmPlan plan_gemm(int M, int N, int K, int sm_count) {
+static GemmPlan plan_gemm(int M, int N, int K, int sm_count, int max_smem) {
   GemmPlan p{};
   p.Mpad = (M + 15) & ~15;
   p.row_blocks = (N + 127) / 128;
@@ -365,7 +430,10 @@ static GemmPlan plan_gemm(int M, int N, int K, int sm_count) {
   p.slab_blocks = (p.k_blocks + slabs - 1) / slabs;
   p.slabs = (p.k_blocks + p.slab_blocks - 1) / p.slab_blocks;   // no empty slab
   p.b_stage_bytes = 16 * (p.Mpad + 1) * 16;
-  p.smem = size_t(kCodeStages) * kCodeStage + size_t(kBStages) * p.b_stage_bytes + size_t(128) * kScalePitch * 2;
+  const int fixed = kCodeBytes + 128 * kScalePitch * 2 + 2048;   // 2 KB: static shared memory and slack
+  p.b_stages = (max_smem - fixed) / p.b_stage_bytes;
+  if (p.b_stages > kMaxBStages) p.b_stages = kMaxBStages;
+  p.smem = size_t(kCodeBytes) + size_t(p.b_stages) * p.b_stage_bytes + size_t(128) * kScalePitch * 2;
   return p;
 }
 
@@ -381,21 +449,23 @@ int gemm_umma_supported(int M, int N, int K, int group, int bits, int lut_len, i
 }
 
 int64_t gemm_umma_workspace_bytes(int M, int N, int K) {
-  const GemmPlan p = plan_gemm(M, N, K, device_info().sm_count);
+  const GemmPlan p = plan_gemm(M, N, K, device_info().sm_count, device_info().max_smem_optin);
   return kGemmHeadBytes + (p.slabs > 1 ? int64_t(p.row_blocks) * p.slabs * p.Mpad * 128 * 4 : 0);
 }
 
 int launch_gemm_umma(const void* x, const uint8_t* packed, const void* scales, const void* bias, void* y, void* workspace,
                      int M, int N, int K, int64_t packed_row_stride, int64_t scale_row_stride, cudaStream_t stream) {
   const DeviceInfo& info = device_info();
-  const GemmPlan p = plan_gemm(M, N, K, info.sm_count);
+  const GemmPlan p = plan_gemm(M, N, K, info.sm_count, info.max_smem_optin);
   GemmArgs a{};
   a.x = static_cast<const __half*>(x); a.packed = packed; a.scales = static_cast<const __half*>(scales);
   a.bias = static_cast<const __half*>(bias); a.y = static_cast<__half*>(y);
   a.M = M; a.Mpad = p.Mpad; a.N = N; a.K = K;
   a.packed_row_stride = packed_row_stride; a.scale_row_stride = scale_row_stride;
   a.row_blocks = p.row_blocks; a.slabs = p.slabs; a.slab_blocks = p.slab_blocks; a.k_blocks = p.k_blocks;
-  a.b_stage_bytes = p.b_stage_bytes;
+  a.b_stage_bytes = p.b_stage_bytes; a.b_stages = p.b_stages;
+  a.issuers = p.Mpad <= 64 ? 4 : 2;     // issuers * Mpad accumulator columns beside the 256 of the A buffers
+  MKB_REQUIRE(p.b_stages >= 3, MKB_E_UNSUPPORTED, "gemm: the activation tiles do not fit shared memory");
   a.counters = static_cast<int*>(workspace);
   a.status = a.counters + kGemmMaxRowBlocks;
   a.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kGemmHeadBytes);

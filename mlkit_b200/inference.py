@@ -207,7 +207,8 @@ class PackedLinear(nn.Module):
                     and not (inputs.requires_grad and torch.is_grad_enabled())
                     and kernels.gemm_supported(rows, width=width, group=self.group, bits=self.code_bits, dtype=inputs.dtype,
                                                scales=self.scales, zeros=self.zeros, integer_grid=self.integer_grid,
-                                               grid_minimum=self.grid_minimum, levels=self.values.numel())):
+                                               grid_minimum=self.grid_minimum, levels=self.values.numel(),
+                                               outputs=self.out_features)):
                 # up to 128 rows: the weight is reconstructed inside the GEMM kernel, tile by tile
                 flat = inputs.reshape(rows, width).contiguous()
                 out = kernels.packed_gemm(flat, self.packed, self.scales, self.values, self.bias,

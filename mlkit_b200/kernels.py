@@ -121,11 +121,17 @@ def gemm_status() -> int:
 
 
 def gemm_supported(rows: int, *, width: int, group: int, bits: int, dtype: torch.dtype, scales: Tensor,
-                   zeros: Tensor | None, integer_grid: bool, grid_minimum: float, levels: int) -> bool:
-    """Whether ``packed_gemm`` covers the layer (the C entry point checks the same and more)."""
-    return (1 <= rows <= GEMM_MAXIMUM_ROWS and bits == 4 and group == 128 and width % 128 == 0 and zeros is None
+                   zeros: Tensor | None, integer_grid: bool, grid_minimum: float, levels: int,
+                   outputs: int | None = None) -> bool:
+    """Whether ``packed_gemm`` covers the layer (the C entry point checks the same and more).  With
+    ``outputs`` given, also whether it is the faster route: measured on B200 against reconstruct +
+    library GEMM it wins at every shape up to 32 rows, and up to 128 rows once the weight has 2^25
+    codes (4096 x 8192) or more; small weights with many rows are quicker through the dense route."""
+    if not (1 <= rows <= GEMM_MAXIMUM_ROWS and bits == 4 and group == 128 and width % 128 == 0 and zeros is None
             and dtype == torch.float16 and scales.dtype == torch.float16 and bool(integer_grid)
-            and float(grid_minimum) == -8.0 and levels == 16)
+            and float(grid_minimum) == -8.0 and levels == 16):
+        return False
+    return outputs is None or rows <= 32 or outputs * width >= 1 << 25
 
 
 def packed_gemm(x: Tensor, packed: Tensor, scales: Tensor, values: Tensor, bias: Tensor | None, out: Tensor, *,
