@@ -11,14 +11,14 @@
 // Work: a unit is 128 weight rows x one K slab; one CTA computes one unit.  Roles (512 threads):
 //   * warps 0-7, "decoders": warp w owns rows 32 * (w % 4) .. + 31 and the 128-code blocks of parity w / 4,
 //     so the two warp groups alternate and one decodes while the other's block is multiplied.  The 32 x
-//     64 B code tile of a block arrives by cp.async in the warp's own shared-memory ring (six stages; the
+//     64 B code tile of a block arrives by cp.async in the warp's own shared-memory ring (five stages; the
 //     rings are what keeps enough bytes in flight towards HBM, and only the warp itself reads its ring, so
 //     the loop has no CTA-wide barrier); a thread reads the 64 bytes of its row, turns each byte into two
 //     fp16 weights (PRMT + LOP3 + HFMA2 + HMUL2) in natural K order and stores the 64 columns of one of four
 //     A buffers (tcgen05.st).  At the end of the unit the same threads read the accumulators (tcgen05.ld) and store y,
 //     or a partial when K is split over slabs;
-//   * warps 8-11, "loaders": copy the [Mpad x 128] activation tile of every block into a ring of three to
-//     eight stages in the canonical K-major core-matrix layout (cp.async, 16 B = 8 K of one row);
+//   * warps 8-11, "loaders": warp w copies the [Mpad x 128] activation tiles of the blocks t = w (mod 4) into a
+//     ring of four or eight stages in the canonical K-major core-matrix layout (cp.async, 16 B = 8 K of one row);
 //   * warps 12-15, "issuers": one lane of issuer i waits for A and B of the blocks t = i (mod issuers), issues
 //     their eight tcgen05.mma each (M128, N = Mpad, K16) into its own accumulator columns and commits them to
 //     the mbarriers that free the A buffer and the B stage.  Issuing a step costs the thread about a hundred
@@ -36,10 +36,10 @@ constexpr int kLoaders = 128;
 constexpr int kMaxIssuers = 4;
 constexpr int kThreadsG = kDecoders + kLoaders + 32 * kMaxIssuers;   // warps 12..15 issue
 constexpr int kWarpStage = 32 * 64;       // bytes of codes per block of 128 K and decoder warp: 32 rows x 64 B
-constexpr int kCodeStages = 6;            // ring stages per decoder warp: 8 warps x 6 x 2 KB = 96 KB in flight per SM
+constexpr int kCodeStages = 5;            // ring stages per decoder warp: 8 warps x 5 x 2 KB = 80 KB in flight per SM
 constexpr int kCodeBytes = 8 * kCodeStages * kWarpStage;
 constexpr int kABuffers = 4;              // A operand buffers in tensor memory, 64 columns each
-constexpr int kMaxBStages = 8;            // activation tiles in shared memory: as many as fit, at least 3
+constexpr int kMaxBStages = 8;            // activation tiles in shared memory: eight if they fit, else four
 constexpr int kMaxUnitBlocks = 32;        // blocks of 128 K per unit: its scales sit in shared memory
 constexpr int kScalePitch = kMaxUnitBlocks + 2;   // halves per row of the scale table (17 words: no bank conflicts)
 constexpr int kTmemColumnsG = 512;        // A[4]: 0..255; D_i: 256 + i * Mpad, one per issuer
@@ -64,7 +64,7 @@ struct GemmArgs {
 struct GemmBarriers {
   uint64_t a_full[kABuffers];    // decoders -> issuer (128 arrivals: the four warps that own the block)
   uint64_t a_empty[kABuffers];   // issuer -> decoders (tcgen05.commit)
-  uint64_t b_full[kMaxBStages];  // loaders -> issuer (128 arrivals)
+  uint64_t b_full[kMaxBStages];  // loaders -> issuer (32 arrivals: the warp that copied the tile)
   uint64_t b_empty[kMaxBStages]; // issuer -> loaders (tcgen05.commit)
   uint64_t d_full;               // issuer -> decoders: every step of the unit is complete
 };
@@ -115,19 +115,6 @@ __device__ __forceinline__ uint32_t weight_pair(uint32_t word, __half2 scale) {
   return *reinterpret_cast<const uint32_t*>(&weight);
 }
 
-// cp.async.wait_group with a run-time count (the instruction takes an immediate)
-__device__ __forceinline__ void wait_for_all_but(int pending) {
-  switch (pending) {
-    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
-    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
-  }
-}
-
 __device__ __forceinline__ void store_columns16(uint32_t address, const uint32_t* r) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
                :: "r"(address), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
@@ -163,7 +150,7 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_umma_kernel(const GemmArgs 
       mbar_init(&bars.a_empty[b], 1);
     }
     for (int b = 0; b < kMaxBStages; ++b) {
-      mbar_init(&bars.b_full[b], kLoaders);
+      mbar_init(&bars.b_full[b], 32);
       mbar_init(&bars.b_empty[b], 1);
     }
     mbar_init(&bars.d_full, a.issuers);
@@ -322,38 +309,40 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_umma_kernel(const GemmArgs 
     // ================================ loaders ================================
     // item i of a block is chunk i % 16 (8 K) of activation row i / 16: sixteen threads read 256 contiguous
     // bytes; chunk c of row m lands at (c * (Mpad + 1) + m) * 16, the odd pitch spreads the chunks over banks
-    const int ltid = tid - kDecoders;
+    // loader warp w copies the tiles of the blocks t = w (mod 4): a block's round trip (wait for its
+    // stage, issue, land, publish) is about a thousand cycles whatever its size, so four of them run side
+    // by side.  Lane l copies chunk l % 16 (8 K) of rows l / 16, l / 16 + 2, ...: sixteen lanes read 256
+    // contiguous bytes; chunk c of row m lands at (c * (Mpad + 1) + m) * 16, the odd pitch spreads the
+    // chunks over the banks.
+    const int me = warp - 8;
     const uint32_t b_base = shared_address(b_s);
-    const __half* my_source = a.x + int64_t(ltid >> 4) * a.K + int64_t(first_block) * 128 + (ltid & 15) * 8;
-    const uint32_t my_target = b_base + ((ltid & 15) * (a.Mpad + 1) + (ltid >> 4)) * 16;
-    const int64_t row_step = int64_t(kLoaders / 16) * a.K;
+    const __half* my_source = a.x + int64_t(lane >> 4) * a.K + int64_t(first_block) * 128 + (lane & 15) * 8;
+    const uint32_t my_target = b_base + ((lane & 15) * (a.Mpad + 1) + (lane >> 4)) * 16;
+    const int64_t row_step = int64_t(2) * a.K;
+    const int own = blocks > me ? (blocks - me + 3) >> 2 : 0;
+    const int lag = a.b_stages >= 8 ? 1 : 0;       // own tiles still in flight when one is published
     asm volatile("griddepcontrol.wait;" ::: "memory");
     bool alive = true;
-    int stage = 0, round = 0;        // of the block being copied
-    int done_stage = 0;              // of the block `lag` steps back, whose copies are waited for
-    const int lag = a.b_stages - 1;  // tiles in flight: a tile is published `lag` steps after its copies were issued
-    for (int t = 0; t < blocks + lag && alive; ++t) {
-      if (t >= lag) {
-        // before this step's copies are issued the newest groups are blocks t - lag .. t - 1
-        wait_for_all_but(lag - 1);                             // the tile of block t - lag has landed (this thread's share)
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive(&bars.b_full[done_stage]);
-        done_stage = done_stage + 1 == a.b_stages ? 0 : done_stage + 1;
-      }
-      if (t < blocks) {
+    for (int j = 0; j < own + lag && alive; ++j) {
+      if (j < own) {
+        const int t = me + 4 * j, stage = t % a.b_stages, round = t / a.b_stages;
         if (round > 0 && !mbar_wait(&bars.b_empty[stage], uint32_t(round - 1) & 1u, failed)) { alive = false; break; }
-        // this thread copies chunk c of rows m0, m0 + 8, ...: the source advances by 8 rows, the target by 128 B
         const __half* source = my_source + int64_t(t) * 128;
         uint32_t target = my_target + stage * a.b_stage_bytes;
 #pragma unroll 4
-        for (int m = ltid >> 4; m < a.M; m += kLoaders / 16) {
+        for (int m = lane >> 4; m < a.M; m += 2) {
           async_copy16(target, source);
           source += row_step;
-          target += 128;
+          target += 32;
         }
-        if (++stage == a.b_stages) { stage = 0; ++round; }
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
+      if (j >= lag) {
+        if (lag) asm volatile("cp.async.wait_group 1;" ::: "memory");
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(&bars.b_full[(me + 4 * (j - lag)) % a.b_stages]);
+      }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
   } else if (lane == 0 && warp - 12 < a.issuers) {
@@ -431,8 +420,10 @@ static GemmPlan plan_gemm(int M, int N, int K, int sm_count, int max_smem) {
   p.slabs = (p.k_blocks + p.slab_blocks - 1) / p.slab_blocks;   // no empty slab
   p.b_stage_bytes = 16 * (p.Mpad + 1) * 16;
   const int fixed = kCodeBytes + 128 * kScalePitch * 2 + 2048;   // 2 KB: static shared memory and slack
-  p.b_stages = (max_smem - fixed) / p.b_stage_bytes;
-  if (p.b_stages > kMaxBStages) p.b_stages = kMaxBStages;
+  // four loader warps fill the ring, warp w the blocks t = w (mod 4): with four or eight stages a stage has
+  // one producer, which keeps every waiter within one phase of its mbarrier
+  const int fit = (max_smem - fixed) / p.b_stage_bytes;
+  p.b_stages = fit >= 8 ? 8 : fit >= 4 ? 4 : 0;
   p.smem = size_t(kCodeBytes) + size_t(p.b_stages) * p.b_stage_bytes + size_t(128) * kScalePitch * 2;
   return p;
 }
@@ -465,7 +456,7 @@ int launch_gemm_umma(const void* x, const uint8_t* packed, const void* scales, c
   a.row_blocks = p.row_blocks; a.slabs = p.slabs; a.slab_blocks = p.slab_blocks; a.k_blocks = p.k_blocks;
   a.b_stage_bytes = p.b_stage_bytes; a.b_stages = p.b_stages;
   a.issuers = p.Mpad <= 64 ? 4 : 2;     // issuers * Mpad accumulator columns beside the 256 of the A buffers
-  MKB_REQUIRE(p.b_stages >= 3, MKB_E_UNSUPPORTED, "gemm: the activation tiles do not fit shared memory");
+  MKB_REQUIRE(p.b_stages >= 4, MKB_E_UNSUPPORTED, "gemm: the activation tiles do not fit shared memory");
   a.counters = static_cast<int*>(workspace);
   a.status = a.counters + kGemmMaxRowBlocks;
   a.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + kGemmHeadBytes);
