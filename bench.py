@@ -353,6 +353,46 @@ def transform_table(device: torch.device, peak: float) -> dict:
     return table
 
 
+def gemm_table(device, peak: float) -> dict:
+    """The fused dequantise + GEMM (``mkb_gemm``, 9..128 activation rows) on the gate and down shapes,
+    beside the dense route it replaces (reconstruct the fp16 weight, then the library GEMM): per launch
+    over 6 distinct weights in one graph, algorithmic GB/s and TFLOP/s."""
+    from mlkit_b200 import kernels
+
+    generator = torch.Generator(device=device).manual_seed(11)
+    values = torch.arange(-8, 8, dtype=torch.float32, device=device)
+    table = {}
+    for name, (out_rows, width) in (("gate", (14336, 4096)), ("down", (4096, 14336))):
+        packed = [torch.randint(0, 256, (out_rows * width // 2,), dtype=torch.uint8, device=device, generator=generator)
+                  for _ in range(6)]
+        scales = [(torch.rand(out_rows, width // GROUP, device=device, generator=generator) * 0.01 + 0.001).half()
+                  for _ in range(6)]
+        for rows in (16, 32, 64, 128):
+            x = torch.randn(rows, width, device=device, generator=generator).half()
+            out = torch.empty(rows, out_rows, device=device, dtype=torch.float16)
+
+            def fused():
+                for i in range(6):
+                    kernels.packed_gemm(x, packed[i], scales[i], values, None, out, group=GROUP, bits=BITS,
+                                        integer_grid=True, grid_minimum=-8.0)
+
+            def dense():
+                for i in range(6):
+                    weight, _ = kernels.dequantize(packed[i], scales[i], values, None, shape=(out_rows, width),
+                                                   group=GROUP, bits=BITS, dtype=torch.float16)
+                    torch.nn.functional.linear(x, weight)
+
+            moved = matvec_bytes(out_rows, width, rows)
+            record = entry(replay_us(graph_of(fused), 6), moved, peak)
+            record["tflops"] = round(2 * rows * out_rows * width / record["us"] / 1e6, 1)
+            record["dense_route_us"] = round(replay_us(graph_of(dense), 6)["median"], 3)
+            table[f"{name}_{width}x{out_rows}_M{rows}"] = record
+        del packed, scales
+        torch.cuda.empty_cache()
+    table["status"] = kernels.gemm_status()
+    return table
+
+
 def comparator_table(device, peak: float) -> dict:
     """The reference's own Triton ``PackedLinear`` and dense fp16 ``F.linear`` on this GPU, with the
     per-layer protocol (8 weight copies in one graph).  Comparators only: nothing of the product runs
@@ -621,6 +661,7 @@ def main() -> None:
                                 single_layers(device, 4864, 896, __import__("mlkit_b200").int(4, group=128), 16, 5), 1, peak,
                                 matvec_bytes(4864, 896, 1))}),
                             ("per_codec", lambda: codec_table(device, peak)),
+                            ("fused_gemm", lambda: gemm_table(device, peak)),
                             ("rotated", lambda: rotated_table(device, peak)),
                             ("transform", lambda: transform_table(device, peak)),
                             ("comparators", lambda: comparator_table(device, peak))):
