@@ -99,7 +99,8 @@ __device__ __forceinline__ void mma_next(float (&d)[4], uint32_t a0, uint32_t a1
 //   TABLE any table of at most 16 levels with 3- or 4-bit codes and one scale per 64 or 128 codes: a
 //         pair of neighbouring codes indexes a shared-memory table of fp16 pairs (one copy per lane,
 //         so the gather has no bank conflicts), the pair is multiplied by the fp16 scale of its row
-//         group, and the products accumulate directly.  The table holds fp16(lut[c]): the matvec is
+//         group (one scale per k-tile: the scale multiplies the tile's sum instead), and the products
+//         accumulate directly.  The table holds fp16(lut[c]): the matvec is
 //         within the 2e-3 bound of reconstruct-then-matmul, not bit-equal to it (the dequantisation
 //         kernel is the bit-exact route).
 enum { MODE_RAW = 0, MODE_TABLE = 1 };
@@ -410,18 +411,25 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
       const uint32_t s1 = load_shared2(scales_at + 8 * V::SCALE_ROW_BYTES + (kk * GPT + group_of_lane) * 2 + odd_scale_1);
       const uint32_t scale_0 = s0 | (s0 << 16), scale_1 = s1 | (s1 << 16);
       const __half2 f0 = *reinterpret_cast<const __half2*>(&scale_0), f1 = *reinterpret_cast<const __half2*>(&scale_1);
+      // with one scale per k-tile (GPT == 1) the scale multiplies the tile's sum, as in the RAW codecs: the
+      // table values go to the tensor core as they are; with two groups per k-tile a step mixes groups,
+      // so every pair is scaled before it
+      constexpr bool SCALE_SUM = GPT == 1;
       auto weight_pair = [&](uint32_t entry, __half2 scale) -> uint32_t {
         const uint32_t bits = load_shared4(table_lane + entry * 128u);
+        if constexpr (SCALE_SUM) return bits;
         const __half2 scaled = __hmul2(*reinterpret_cast<const __half2*>(&bits), scale);
         return *reinterpret_cast<const uint32_t*>(&scaled);
       };
+      float tile_sum[4] = {0.f, 0.f, 0.f, 0.f};
+      float (&into)[4] = SCALE_SUM ? tile_sum : y;
       if constexpr (BITS == 4) {
         const uint4 lo = load_shared16(slot_at + tile_offset<4>(kk, g, t)), hi = load_shared16(slot_at + tile_offset<4>(kk, g + 8, t));
         const uint32_t q[4] = {lo.x, lo.y, lo.z, lo.w}, p[4] = {hi.x, hi.y, hi.z, hi.w};
 #pragma unroll
         for (int step = 0; step < 8; ++step) {   // bytes 2 * step and 2 * step + 1 of the lane's 16
           const int w = step >> 1, low = (step & 1) ? 0x4442 : 0x4440, high = (step & 1) ? 0x4443 : 0x4441;
-          mma_next(y, weight_pair(__byte_perm(q[w], 0u, low), f0), weight_pair(__byte_perm(p[w], 0u, low), f1),
+          mma_next(into, weight_pair(__byte_perm(q[w], 0u, low), f0), weight_pair(__byte_perm(p[w], 0u, low), f1),
                    weight_pair(__byte_perm(q[w], 0u, high), f0), weight_pair(__byte_perm(p[w], 0u, high), f1),
                    b[kk][2 * step], b[kk][2 * step + 1]);
         }
@@ -436,9 +444,14 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
         };
 #pragma unroll
         for (int step = 0; step < 8; ++step)
-          mma_next(y, weight_pair(field(q, 2 * step), f0), weight_pair(field(p, 2 * step), f1),
+          mma_next(into, weight_pair(field(q, 2 * step), f0), weight_pair(field(p, 2 * step), f1),
                    weight_pair(field(q, 2 * step + 1), f0), weight_pair(field(p, 2 * step + 1), f1),
                    b[kk][2 * step], b[kk][2 * step + 1]);
+      }
+      if constexpr (SCALE_SUM) {
+        const float scale_low = __half2float(__low2half(f0)), scale_high = __half2float(__low2half(f1));
+#pragma unroll
+        for (int q = 0; q < 4; ++q) y[q] = fmaf(q < 2 ? scale_low : scale_high, tile_sum[q], y[q]);
       }
     }
   };
