@@ -56,25 +56,8 @@ struct BulkArgs {
   int rows_outer;    // 0: a stage is [chunk][row][128 B]; 1: [row][chunk][128 B] (tensor map with natural dimension order)
   int reducers;
   float grid_min;
-#ifdef MKB_STAMPS
-  unsigned long long* stamps;
-  int launch_id;
-#endif
 };
 
-#ifdef MKB_STAMPS
-static unsigned long long* g_probe_stamps = nullptr;
-static int g_probe_launch = 0, g_probe_consumers = 0, g_probe_stage_cap = 0;
-
-__device__ __forceinline__ unsigned long long now_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-#define MKB_STAMP(slot) a.stamps[(size_t(a.launch_id) * gridDim.x + blockIdx.x) * 8 + (slot)] = now_ns()
-#else
-#define MKB_STAMP(slot)
-#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
 
@@ -228,7 +211,6 @@ gemv_bulk_kernel(const __grid_constant__ CUtensorMap weights, const BulkArgs a) 
   };
   const int first_wave = n_units < a.stages ? n_units : a.stages;
   if (warp == W && lane == 0) {
-    MKB_STAMP(0);
     for (int s = 0; s < a.stages; ++s) {
       bar_init(full + s, 1);
       bar_init(empty + s, W);
@@ -239,9 +221,7 @@ gemv_bulk_kernel(const __grid_constant__ CUtensorMap weights, const BulkArgs a) 
     }
     *failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    MKB_STAMP(7);
     for (int i = 0; i < first_wave; ++i) issue_unit();
-    MKB_STAMP(1);
   }
   __syncthreads();
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -354,7 +334,6 @@ gemv_bulk_kernel(const __grid_constant__ CUtensorMap weights, const BulkArgs a) 
     if (n_units > 1) { load_scales(slab_ahead, rt_ahead, scale_next); advance(slab_ahead, rt_ahead); }
 
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (warp == 0 && lane == 0) { MKB_STAMP(2); }
     int stage = 0;
     uint32_t phase = 0, stage_offset = 0;
     for (int i = 0; i < n_units; ++i) {
@@ -367,8 +346,6 @@ gemv_bulk_kernel(const __grid_constant__ CUtensorMap weights, const BulkArgs a) 
 
       if (!bar_wait(full + stage, phase, failed)) break;
       if (warp == 0 && lane == 0) {
-        if (i == 0) { MKB_STAMP(3); }
-        if (i == n_units - 1) { MKB_STAMP(4); }
       }
       const uint4 d00 = lds128(a00 + stage_offset), d10 = lds128(a10 + stage_offset);   // group 0: rows g, g+8
       const uint4 d01 = lds128(a01 + stage_offset), d11 = lds128(a11 + stage_offset);   // group 1
@@ -406,7 +383,6 @@ gemv_bulk_kernel(const __grid_constant__ CUtensorMap weights, const BulkArgs a) 
       __syncwarp();
       if (lane == 0) bar_arrive(red_full + buffer);
     }
-    if (warp == 0 && lane == 0) { MKB_STAMP(5); }
   } else {
     // ---- reducers: warp r of R takes the units i = r, r + R, ... in batches, so that the slow part
     // of a K split (fence, counter, reading the other slabs' sums) is paid once per batch ----
@@ -484,7 +460,6 @@ gemv_bulk_kernel(const __grid_constant__ CUtensorMap weights, const BulkArgs a) 
         }
       }
     }
-    if (lane == 0 && r == 0) { MKB_STAMP(6); }
     if (*failed && lane == 0 && a.status != nullptr) atomicExch(a.status, 1);
   }
 }
@@ -569,12 +544,6 @@ Split split_for(int N, int K, int sm_count) {
     split.slabs *= 2;
     split.consumers /= 2;
   }
-#ifdef MKB_STAMPS
-  if (g_probe_consumers > 0) {
-    split.consumers = g_probe_consumers;
-    split.slabs = (chunks + split.consumers - 1) / split.consumers;
-  }
-#endif
   split.ctas_per_sm = split.consumers <= 8 ? 2 : 1;
   split.reducers = split.consumers <= 8 ? 1 : 2;
   return split;
@@ -641,12 +610,6 @@ int launch_gemv_bulk(const void* x, const uint8_t* packed, const void* scales, c
   if (grid > a.units) grid = a.units;
   const int most = (a.units + grid - 1) / grid;
   if (stages > most) stages = most;  // no CTA ever has more units than this
-#ifdef MKB_STAMPS
-  if (g_probe_stage_cap > 1 && stages > g_probe_stage_cap) stages = g_probe_stage_cap;
-  a.stamps = g_probe_stamps;
-  a.launch_id = g_probe_launch++;
-
-#endif
   a.stages = stages;
   const size_t smem = 1024 + size_t(stages) * stage_bytes + red_bytes + size_t(2 * stages + 2 * kRedBuffers) * 8 + 16;
 

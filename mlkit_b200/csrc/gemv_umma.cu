@@ -51,20 +51,12 @@ struct UmmaArgs {
   float* partials;   // [row_blocks][slabs][M][128]
   int* counters;     // [row_blocks], zero between launches
   int* status;       // set non-zero when a bounded wait expired
-#ifdef MKB_TRACE
-  long long* trace;
-#endif
   int M, N, K, group_shift;
   int64_t packed_row_stride, scale_row_stride;
   int row_blocks, slabs, units;
   float grid_min;
 };
 
-#ifdef MKB_TRACE
-#define MKB_MARK(who, t, slot) if (blockIdx.x == 0 && (t) < 12) a.trace[((who) * 12 + (t)) * 8 + (slot)] = clock64();
-#else
-#define MKB_MARK(who, t, slot)
-#endif
 
 struct Barriers {          // shared-memory mbarriers
   uint64_t a_full[2];      // row threads -> issuer: A buffer written (128 arrivals)
@@ -277,18 +269,14 @@ __global__ void __launch_bounds__(kThreadsU) gemv_umma_kernel(const UmmaArgs a) 
     };
 
     for (int t = 0; t < total && alive; ++t) {
-      if (tid == 0) { MKB_MARK(0, t, 0) }
       asm volatile("cp.async.wait_group %0;" ::"n"(kDepthU - 2) : "memory");
-      if (tid == 0) { MKB_MARK(0, t, 1) }
       asm volatile("bar.sync 1, 128;" ::: "memory");  // every row thread's share of stage t has landed
-      if (tid == 0) { MKB_MARK(0, t, 2) }
       issue();                                         // refills the stage read one iteration ago
       const uint8_t* mine = ring_s + slot_index * kStageBytes + tid * kPitch;
       slot_index = slot_index + 1 == kDepthU ? 0 : slot_index + 1;
       uint4 chunk[4];
 #pragma unroll
       for (int c = 0; c < 4; ++c) chunk[c] = *reinterpret_cast<const uint4*>(mine + 16 * c);
-      if (tid == 0) { MKB_MARK(0, t, 5) }
       const uint32_t a_address = tmem_base + lane_base + (t & 1) * 64;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -306,14 +294,10 @@ __global__ void __launch_bounds__(kThreadsU) gemv_umma_kernel(const UmmaArgs a) 
                      :: "r"(a_address + 16 * c), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
                         "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
       }
-      if (tid == 0) { MKB_MARK(0, t, 6) }
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-      if (tid == 0) { MKB_MARK(0, t, 7) }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       barrier_arrive(&bars.a_full[t & 1]);
-      if (tid == 0) { MKB_MARK(0, t, 3) }
       if (t > 0) retire(t - 1);
-      if (tid == 0) { MKB_MARK(0, t, 4) }
       previous_scale = __half2float(group == 0 ? unit_scales[0] : group == 1 ? unit_scales[1]
                                     : group == 2 ? unit_scales[2] : unit_scales[3]);
       previous_group = group;
@@ -339,11 +323,8 @@ __global__ void __launch_bounds__(kThreadsU) gemv_umma_kernel(const UmmaArgs a) 
       int group = 0;
       for (int g = 0; g < total; ++g) {
         const int b = g & 1;
-        if (cls == 0) { MKB_MARK(1, g, 0) }
         if (!barrier_wait(&bars.a_full[b], uint32_t(g >> 1) & 1u, failed)) break;
-        if (cls == 0) { MKB_MARK(1, g, 1) }
         if (g >= 2 && !barrier_wait(&bars.d_empty[b], uint32_t((g >> 1) - 1) & 1u, failed)) break;
-        if (cls == 0) { MKB_MARK(1, g, 2) }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint64_t desc_group = desc_base + uint64_t(group * 8 * (kTileBytes >> 4));
 #pragma unroll
@@ -362,7 +343,6 @@ __global__ void __launch_bounds__(kThreadsU) gemv_umma_kernel(const UmmaArgs a) 
         }
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_address(&bars.d_full[b]))
                      : "memory");
-        if (cls == 0) { MKB_MARK(1, g, 3) }
         group = group + 1 == kSlabGroups ? 0 : group + 1;
       }
     }
