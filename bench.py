@@ -497,10 +497,17 @@ def run_case(spec: str, device: torch.device, launches: int) -> None:
     """One layer shape, ``launches`` launches over distinct weight copies (each cold in L2), nothing
     else on the device: the small case a profiler captures.  Prints the mean launch time.
     ``NAME[:ROWS[:KERNEL]]`` with NAME a block linear, ``qkv`` or ``gate_up``; ``rht:ROWS:WIDTH`` runs
-    the activation transform instead."""
+    the activation transform instead; ``tp_layer:WORLD:BATCH`` times the operators of one decoder layer with
+    the shard shapes of WORLD ranks."""
     from mlkit_b200 import kernels
 
     fields = spec.split(":")
+    if fields[0] == "tp_layer":     # tp_layer:WORLD:BATCH -- per-operator times of one tensor-parallel-shaped layer
+        import bench_tp
+
+        world, batch = int(fields[1]), int(fields[2]) if len(fields) > 2 else 1
+        print(json.dumps({"case": spec, "us": bench_tp.layer_breakdown(world, batch, device)}))
+        return
     if fields[0] == "rht":
         rows, width = int(fields[1]), int(fields[2])
         us = time_transform(device, rows, width, launches)

@@ -93,6 +93,82 @@ def dominant_kernel(model: tp.TensorParallelDecoder, batch: int) -> tuple[float,
     return min(samples), shard.nbytes + batch * width * 2 + batch * rows * 2 + 64
 
 
+def layer_breakdown(world: int, batch: int, device: torch.device, layers: int = 16) -> dict:
+    """Per-operator launch time of one decoder layer with the shard shapes of ``world`` ranks, on ONE GPU
+    and without communication (the peer reduction is a plain add + norm here): every operator alone over
+    ``layers`` distinct layers in one CUDA graph (weights cold in L2), then the chained layer.  Microseconds."""
+    from mlkit_b200 import kernels
+
+    c = tp.LLAMA3_70B
+    generator = torch.Generator(device=device).manual_seed(1)
+    q_heads, kv_heads, mlp = c.q_heads // world, c.kv_heads // world, c.intermediate // world
+    shapes = {"qkv": ((q_heads + 2 * kv_heads) * c.head_dim, c.hidden), "o": (c.hidden, q_heads * c.head_dim),
+              "gate_up": (2 * mlp, c.hidden), "down": (c.hidden, mlp)}
+    shards = [{name: tp.PackedShard.synthetic(n, k, c, device, generator) for name, (n, k) in shapes.items()}
+              for _ in range(layers)]
+    capacity = CONTEXT + 64
+    keys = [torch.randn(batch, kv_heads, capacity, c.head_dim, device=device).half() for _ in range(layers)]
+    values = [torch.randn(batch, kv_heads, capacity, c.head_dim, device=device).half() for _ in range(layers)]
+    positions = torch.full((batch,), CONTEXT, dtype=torch.int32, device=device)
+    residual = torch.randn(batch, c.hidden, device=device).half()
+    normed, weight = torch.empty_like(residual), torch.ones(c.hidden, device=device).half()
+    out = {name: torch.empty(batch, n, device=device, dtype=torch.float16) for name, (n, _) in shapes.items()}
+    attended = torch.randn(batch, q_heads * c.head_dim, device=device).half()
+
+    def timed(launch_all) -> float:
+        graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            launch_all()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                launch_all()
+        torch.cuda.current_stream().wait_stream(side)
+        graph.replay()
+        torch.cuda.synchronize()
+        samples = []
+        for _ in range(5):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            graph.replay()
+            stop.record()
+            torch.cuda.synchronize()
+            samples.append(start.elapsed_time(stop) * 1e3 / layers)
+        return statistics.median(samples)
+
+    activation = torch.empty(batch, mlp, device=device, dtype=torch.float16)
+    operators = {
+        "add_rmsnorm": lambda i: kernels.add_rmsnorm(residual, out["down"], weight, normed, 1e-5),
+        "qkv": lambda i: shards[i]["qkv"](normed, out["qkv"]),
+        "rope_attention": lambda i: kernels.rope_attention_decode(out["qkv"], positions, keys[i], values[i], attended,
+                                                                  q_heads=q_heads, kv_heads=kv_heads,
+                                                                  head_dim=c.head_dim, theta=c.rope_theta),
+        "o": lambda i: shards[i]["o"](attended, out["o"]),
+        "gate_up": lambda i: shards[i]["gate_up"](normed, out["gate_up"]),
+        "silu_mul": lambda i: kernels.silu_mul(out["gate_up"], activation),
+        "down": lambda i: shards[i]["down"](activation, out["down"]),
+    }
+    table = {}
+    for name, operator in operators.items():
+        table[name] = round(timed(lambda: [operator(i) for i in range(layers)]), 2)
+
+    def layer(i: int) -> None:
+        operators["add_rmsnorm"](i)
+        operators["qkv"](i)
+        operators["rope_attention"](i)
+        operators["o"](i)
+        kernels.add_rmsnorm(residual, out["o"], weight, normed, 1e-5)
+        operators["gate_up"](i)
+        operators["silu_mul"](i)
+        operators["down"](i)
+
+    table["layer_chained"] = round(timed(lambda: [layer(i) for i in range(layers)]), 2)
+    table["sum_of_parts"] = round(sum(table[name] for name in operators) + table["add_rmsnorm"], 2)
+    weights = sum(shard.nbytes for shard in shards[0].values())
+    table["weight_mb_per_layer"] = round(weights / 1e6, 2)
+    return table
+
+
 def measure(rank: int, world: int, device: torch.device, steps: int, warmup: int, layers: int | None = None) -> dict:
     """Build the synthetic model on this rank and time decode for every batch in ``BATCHES``."""
     group = dist.group.WORLD if world > 1 else None

@@ -267,7 +267,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
         v[kk][w] = make_uint4(0u, 0u, 0u, 0u);
         if (has_x) v[kk][w] = __ldg(reinterpret_cast<const uint4*>(x_lane + kk * 128 + w * 8));
       }
-    if (a.gated) {  // the up half sits K elements further in the same row
+    if (a.gated && has_x) {  // the up half sits K elements further in the same row; lanes without a row keep their
+                             // zeros (and stay off the slow path a division of zero would take)
 #pragma unroll
       for (int kk = 0; kk < KT; ++kk)
 #pragma unroll

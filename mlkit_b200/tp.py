@@ -99,10 +99,6 @@ class PackedShard:
         self.plan = kernels.MatvecPlan(packed, scales, values, None, None, outputs=out_rows, width=width,
                                        group=group, bits=bits, dtype=torch.float16, integer_grid=integer,
                                        grid_minimum=low)
-        # the same launch reading gate | up and forming SwiGLU on the way (the down projection of an MLP)
-        self.gated_plan = kernels.MatvecPlan(packed, scales, values, None, None, outputs=out_rows, width=width,
-                                             group=group, bits=bits, dtype=torch.float16, integer_grid=integer,
-                                             grid_minimum=low, gated=True) if integer else None
 
     def __call__(self, x: Tensor, out: Tensor) -> Tensor:
         return self.plan(x, out)
@@ -426,11 +422,10 @@ class TensorParallelDecoder:
                 self._all_reduce(work["o"])
                 kernels.add_rmsnorm(residual, work["o"], mlp_norm, normed, c.eps)
             block["gate_up"](normed, work["gate_up"])
-            if block["down"].gated_plan is not None:   # SwiGLU formed while the down projection loads its input
-                block["down"].gated_plan(work["gate_up"], work["down"])
-            else:
-                kernels.silu_mul(work["gate_up"], work["act"])
-                block["down"](work["act"], work["down"])
+            # SwiGLU as its own 1.5 us launch: formed on load inside the down projection (MKB_GEMV_GATED) every
+            # CTA would redo the activation of its K slice, which measured 3 us slower per layer at every shard size
+            kernels.silu_mul(work["gate_up"], work["act"])
+            block["down"](work["act"], work["down"])
             if exchange is None:
                 self._all_reduce(work["down"])
             delta = work["down"]
