@@ -309,6 +309,7 @@ def codec_table(device, peak: float) -> dict:
 def rotated_table(device, peak: float) -> dict:
     """The Hadamard-rotated INT4 path: transform and matvec chained in one graph, against the matvec alone."""
     import mlkit_b200 as mk
+    from mlkit_b200 import kernels
 
     table = {}
     generator = torch.Generator(device=device).manual_seed(21)
@@ -316,7 +317,7 @@ def rotated_table(device, peak: float) -> dict:
         layers = single_layers(device, out_rows, width, mk.int(4, group=128), copies=8, seed=width)
         signs = (torch.randint(0, 2, (width,), device=device, generator=generator) * 2 - 1).to(torch.int8)
         plans = [layer._plan(torch.float16) for layer in layers]
-        for rows in (1, 8):
+        for rows in (1, 2, 4, 8):
             x = torch.randn(rows, width, device=device, generator=generator)
             picks = torch.randperm(width, device=device, generator=generator)[: width // 100]
             x[:, picks] *= 50
@@ -326,8 +327,14 @@ def rotated_table(device, peak: float) -> dict:
             alone = graph_of(lambda: [plan(x, out) for plan in plans])
             moved = matvec_bytes(out_rows, width, rows)
             both, only = replay_us(chained, len(plans)), replay_us(alone, len(plans))
-            table[f"rht+matvec_{width}x{out_rows}_M{rows}"] = dict(entry(both, moved, peak),
-                                                                   matvec_alone_us=round(only["median"], 3))
+            record = dict(entry(both, moved, peak), matvec_alone_us=round(only["median"], 3))
+            if kernels.rotated_matvec_supported(rows, width, torch.float16):
+                # rotation on load inside the matvec launch (mkb_gemv_hadamard): what the module path takes
+                fused = graph_of(lambda: [kernels.packed_matvec_rotated(
+                    x, signs, layer.packed, layer.scales, layer.values, None, out, group=GROUP, bits=BITS,
+                    integer_grid=True, grid_minimum=-8.0) for layer in layers])
+                record["fused_us"] = round(replay_us(fused, len(layers))["median"], 3)
+            table[f"rht+matvec_{width}x{out_rows}_M{rows}"] = record
         del layers
         torch.cuda.empty_cache()
     return table

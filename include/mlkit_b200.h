@@ -144,6 +144,28 @@ int mkb_gemv_static(const void* x, const uint8_t* packed, const void* scales, co
 int mkb_gemv_static_status(int* status);
 
 /*
+ * The matvec with the randomised Hadamard rotation of its input fused into the activation load:
+ *   y = mkb_gemv(S(x * signs), ...),  S the normalised (normalize != 0) Walsh-Hadamard transform of width K.
+ * Replaces the pair the reference runs for a rotated layer: the pre-hook's transform
+ * (src/mlkit/conversion/model_transforms.py:189-196 calling src/mlkit/kernels/hadamard.py:21-136) as
+ * launches of its own, then the packed matvec.  Every CTA transforms the (at most 64 KB of fp32) activations
+ * in shared memory with the butterflies of mkb_hadamard and rounds them to fp16 as that call stores them, so
+ * the result equals mkb_hadamard followed by mkb_gemv bit for bit; no rotated activation is written to
+ * or read from global memory.
+ * signs: int8 [K] of +1 / -1, 16-byte aligned, or null for the plain transform.
+ * Covers what the streaming matvec covers (fp16 activations and scales; INT2/4/8 on the integer grid with
+ * groups of 128, 3- and 4-bit tables with groups of 64 or 128) when K is a power of two >= 512 and
+ * M * K * 4 <= 65536 (K = 4096: M <= 4); anything else returns MKB_E_UNSUPPORTED and the caller runs
+ * mkb_hadamard, then mkb_gemv.  Widths with an odd factor (14336 = 28 * 512) are not covered.
+ */
+int mkb_gemv_hadamard(const void* x, const int8_t* signs, const uint8_t* packed, const void* scales,
+                      const float* lut, const void* bias, void* y,
+                      int M, int N, int K, int group, int bits, int lut_len,
+                      int x_dtype, int scale_dtype,
+                      int64_t packed_row_stride, int64_t scale_row_stride,
+                      int integer_grid, float grid_minimum, int normalize, void* stream);
+
+/*
  * Fused dequantise + GEMM for more activation rows than the matvec takes:
  *   y[m,n] = sum_k x[m,k] * fp16(lut[code[n,k]] * scale[n, k / 128]) (+ bias[n]),  1 <= M <= 128.
  * Replaces the dense route the reference takes above eight rows, which reconstructs the whole weight

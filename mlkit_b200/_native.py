@@ -21,6 +21,7 @@ SIGNATURES = {
     "mkb_gemv_ex": (c_int, [c_void_p] * 7 + [c_int] * 8 + [c_int64, c_int64, c_int, c_float, c_int, c_void_p]),
     "mkb_gemv_workspace_bytes": (c_int64, [c_int] * 4),
     "mkb_gemv_workspace_status": (c_int, [c_void_p, c_int64, c_void_p]),
+    "mkb_gemv_hadamard": (c_int, [c_void_p] * 7 + [c_int] * 8 + [c_int64, c_int64, c_int, c_float, c_int, c_void_p]),
     "mkb_gemm_workspace_bytes": (c_int64, [c_int] * 3),
     "mkb_gemm": (c_int, [c_void_p] * 7 + [c_int] * 8 + [c_int64, c_int64, c_int, c_float, c_void_p, c_int64, c_void_p]),
     "mkb_gemm_status": (c_int, [c_void_p, c_void_p]),

@@ -48,7 +48,12 @@ class _RotateInputs:
         inputs = arguments[0]
         if not inputs.is_cuda:
             raise ValueError("the online rotation runs on CUDA activations only")
-        rotated = transforms.structured_transform(inputs, signs=self.signs_for(inputs.shape[-1], inputs.device))
+        signs = self.signs_for(inputs.shape[-1], inputs.device)
+        take = getattr(layer, "take_rotation", None)
+        last = next(reversed(layer._forward_pre_hooks.values()), None) is self   # nothing edits the input after this hook
+        if take is not None and last and take(inputs, signs):
+            return None     # the layer rotates while it loads its activations (one launch instead of two)
+        rotated = transforms.structured_transform(inputs, signs=signs)
         return (rotated, *arguments[1:])
 
     def __deepcopy__(self, memo: dict) -> "_RotateInputs":

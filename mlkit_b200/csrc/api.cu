@@ -71,6 +71,13 @@ int gemv_stream_supported(int M, int N, int K, int group, int bits, int lut_len,
 int launch_gemv_stream(const void* x, const uint8_t* packed, const void* scales, const float* lut, const void* bias,
                        void* y, int M, int N, int K, int group, int bits, int lut_len, int64_t packed_row_stride,
                        int64_t scale_row_stride, int integer_grid, float grid_minimum, int gated, cudaStream_t stream);
+int gemv_stream_rotation_supported(int M, int N, int K, int group, int bits, int lut_len, int integer_grid,
+                                   float grid_minimum, const void* signs);
+int launch_gemv_stream_rotated(const void* x, const uint8_t* packed, const void* scales, const float* lut,
+                               const void* bias, void* y, int M, int N, int K, int group, int bits, int lut_len,
+                               int64_t packed_row_stride, int64_t scale_row_stride, int integer_grid,
+                               float grid_minimum, int gated, const int8_t* signs, int rotate, int normalize,
+                               cudaStream_t stream);
 
 }  // namespace mkb
 
@@ -201,4 +208,23 @@ extern "C" int mkb_gemv(const void* x, const uint8_t* packed, const void* scales
   return mkb_gemv_ex(x, packed, scales, lut, zeros, bias, y, M, N, K, group, bits, lut_len, x_dtype,
                      scale_dtype, packed_row_stride, scale_row_stride, integer_grid, grid_minimum,
                      MKB_GEMV_AUTO, stream);
+}
+
+extern "C" int mkb_gemv_hadamard(const void* x, const int8_t* signs, const uint8_t* packed, const void* scales,
+                                 const float* lut, const void* bias, void* y, int M, int N, int K, int group, int bits,
+                                 int lut_len, int x_dtype, int scale_dtype, int64_t packed_row_stride,
+                                 int64_t scale_row_stride, int integer_grid, float grid_minimum, int normalize,
+                                 void* stream) {
+  using namespace mkb;
+  MKB_REQUIRE(M >= 1 && N >= 1 && K >= 1 && group >= 1, MKB_E_ARGUMENT, "gemv_hadamard: bad shape");
+  MKB_REQUIRE(x && packed && scales && lut && y, MKB_E_ARGUMENT, "gemv_hadamard: null pointer");
+  MKB_REQUIRE(gemv_stream_supported(M, N, K, group, bits, lut_len, x_dtype, scale_dtype, x, packed, scales, packed_row_stride,
+                                    scale_row_stride, nullptr, integer_grid, grid_minimum) &&
+                  gemv_stream_rotation_supported(M, N, K, group, bits, lut_len, integer_grid, grid_minimum, signs),
+              MKB_E_UNSUPPORTED,
+              "gemv_hadamard: needs a layer the streaming matvec covers, K a power of two of at least 512, "
+              "M * K * 4 <= 65536 and 16-byte aligned signs");
+  return launch_gemv_stream_rotated(x, packed, scales, lut, bias, y, M, N, K, group, bits, lut_len, packed_row_stride,
+                                    scale_row_stride, integer_grid, grid_minimum, 0, signs, 1, normalize,
+                                    static_cast<cudaStream_t>(stream));
 }

@@ -30,7 +30,7 @@
 #include <tuple>
 #include <type_traits>
 
-#include "mkb_common.cuh"
+#include "hadamard_steps.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -57,6 +57,13 @@ struct StreamArgs {
   int visits;       // visits of every CTA
   int batch;        // visits whose partial sums shared memory holds between two reductions (a multiple of R)
   int gated;        // x is [M, 2K] = gate | up of a SwiGLU MLP: the activation is silu(gate) * up, formed on load
+  // rotation on load (K a power of two): the CTA transforms x * signs with the Walsh-Hadamard butterflies in
+  // shared memory and its warps take their activations from there, rounded to fp16 as the transform's own
+  // launch would store them
+  const int8_t* rot_signs;
+  int rot_log2;     // 0: no rotation
+  uint32_t rot_offset;   // of the [M][K] fp32 buffer in shared memory
+  float rot_scale;
   int early;        // visits copied before the dependency wait; the rest of the ring follows the activation loads
   int kw_inverse, rg_inverse;  // ceil(65536 / KW), ceil(65536 / RG): small quotients by multiply and shift
   float grid_min;
@@ -254,6 +261,61 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
 
   // ---- activations: the B fragments of this warp's k-tiles, permuted in registers ----
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  float* rotated = reinterpret_cast<float*>(smem + a.rot_offset);   // [M][K] when the rotation is on
+  if (a.rot_log2) {
+    // nine stages per 512 values in a warp's registers, the rest in shared memory, three stages per pass
+    const int front = a.rot_log2 < kWarpBits ? a.rot_log2 : kWarpBits;
+    const int chunks_per_row = a.K / kWarpSpan;
+    // a warp takes chunks warp, warp + warps, ...: two at a time, so both chunks' loads are in flight together
+    const int chunks = a.M * chunks_per_row;
+    for (int chunk0 = warp; chunk0 < chunks; chunk0 += 2 * warps) {
+      uint4 raw[2][2];
+      int row[2], first[2];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int chunk = chunk0 + c * warps;
+        row[c] = chunk / chunks_per_row;
+        first[c] = (chunk - row[c] * chunks_per_row) * kWarpSpan + lane * kWarpRun;
+        if (chunk < chunks) {
+          const uint4* source = reinterpret_cast<const uint4*>(a.x + int64_t(row[c]) * a.K + first[c]);
+          raw[c][0] = __ldg(source);
+          raw[c][1] = __ldg(source + 1);
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        if (chunk0 + c * warps >= chunks) break;
+        float values[kWarpRun];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const uint32_t words[4] = {raw[c][q].x, raw[c][q].y, raw[c][q].z, raw[c][q].w};
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const float2 pair = __half22float2(*reinterpret_cast<const __half2*>(&words[w]));
+            values[8 * q + 2 * w] = pair.x;
+            values[8 * q + 2 * w + 1] = pair.y;
+          }
+        }
+        if (a.rot_signs != nullptr) {
+          const uint4 flips = *reinterpret_cast<const uint4*>(a.rot_signs + first[c]);
+          const uint32_t words[4] = {flips.x, flips.y, flips.z, flips.w};
+#pragma unroll
+          for (int j = 0; j < kWarpRun; ++j)
+            values[j] = __fmul_rn(values[j], float(int8_t((words[j >> 2] >> (8 * (j & 3))) & 0xffu)));
+        }
+        warp_butterflies16(values, lane, front);
+        if (a.rot_log2 <= kWarpBits) {
+#pragma unroll
+          for (int j = 0; j < kWarpRun; ++j) values[j] = __fmul_rn(values[j], a.rot_scale);
+        }
+        float4* target = reinterpret_cast<float4*>(rotated + row[c] * a.K + first[c]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) target[q] = make_float4(values[4 * q], values[4 * q + 1], values[4 * q + 2], values[4 * q + 3]);
+      }
+    }
+    __syncthreads();
+    remaining_passes(rotated, a.M * a.K, a.rot_log2, kWarpBits, a.rot_scale);
+  }
   uint32_t b[KT][16];     // tensor-core step s of a k-tile multiplies by b[2s], b[2s + 1]
   float start[KT][4];     // RAW: accumulator start, min * sum(x) * 2^-24 for activation rows 2t, 2t+1 (twice)
   {
@@ -265,7 +327,16 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
         v[kk][w] = make_uint4(0u, 0u, 0u, 0u);
-        if (has_x) v[kk][w] = __ldg(reinterpret_cast<const uint4*>(x_lane + kk * 128 + w * 8));
+        if (has_x && a.rot_log2) {
+          const float* from = rotated + g * a.K + tile0 * 128 + t * 32 + kk * 128 + w * 8;
+          const float4 lo = *reinterpret_cast<const float4*>(from), hi = *reinterpret_cast<const float4*>(from + 4);
+          const __half2 h0 = __floats2half2_rn(lo.x, lo.y), h1 = __floats2half2_rn(lo.z, lo.w);
+          const __half2 h2 = __floats2half2_rn(hi.x, hi.y), h3 = __floats2half2_rn(hi.z, hi.w);
+          v[kk][w] = make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1),
+                                *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
+        } else if (has_x) {
+          v[kk][w] = __ldg(reinterpret_cast<const uint4*>(x_lane + kk * 128 + w * 8));
+        }
       }
     if (a.gated && has_x) {  // the up half sits K elements further in the same row; lanes without a row keep their
                              // zeros (and stay off the slow path a division of zero would take)
@@ -566,6 +637,8 @@ int opt_in_shared(Kernel kernel) {
   return MKB_OK;
 }
 
+constexpr size_t kMaxRotationBytes = 64 * 1024;   // of fp32 activations a CTA rotates in shared memory
+
 struct StreamPlan {
   int bits, mode, gpt;   // the codec: code width, MODE_*, scale groups per k-tile
   int KT, KW, RG, slabs, columns, visits, depth, batch, per_sm;
@@ -575,7 +648,7 @@ struct StreamPlan {
 // Chooses the decomposition: slabs of K (CTAs of a cluster), warps along K and row tiles per visit of a
 // CTA, CTAs per SM (small CTAs share an SM), ring depth (= visits per round).
 // `cluster_cap` > 0 bounds the number of clusters in flight.  bits, mode, gpt are inputs.
-bool plan_stream(int M, int N, int K, int sm_count, int max_smem, int cluster_cap, StreamPlan& p) {
+bool plan_stream(int M, int N, int K, int sm_count, int max_smem, int cluster_cap, StreamPlan& p, size_t extra = 0) {
   (void)M;
   const int k_tiles = K / 128;
   const int KT = k_tiles % 2 == 0 ? 2 : 1;
@@ -602,7 +675,7 @@ bool plan_stream(int M, int N, int K, int sm_count, int max_smem, int cluster_ca
   if (slabs > 1 && visits > kMaxClusterVisits) return false;
   int depth = visits < 2 ? 2 : visits > 3 ? 3 : visits;
   const size_t budget = (size_t(max_smem) + 1024) / per_sm - 1024;  // every resident CTA reserves 1 KB
-  const size_t sums = (slabs > 1 ? size_t(visits) * RG * 512 : 0) + table;
+  const size_t sums = (slabs > 1 ? size_t(visits) * RG * 512 : 0) + table + extra;   // extra: the rotation buffer, last
   while (depth > 2 && size_t(depth) * warps * (slot + 512) + sums > budget) --depth;
   if (size_t(depth) * warps * (slot + 512) + sums > budget) return false;
   // partial sums of as many visits as fit (whole rounds), ideally all: one reduction at the end
@@ -724,13 +797,27 @@ int gemv_stream_supported(int M, int N, int K, int group, int bits, int lut_len,
   return plan_stream(M, N, K, info.sm_count, info.max_smem_optin, 0, plan) ? 1 : 0;
 }
 
-int launch_gemv_stream(const void* x, const uint8_t* packed, const void* scales, const float* lut, const void* bias,
-                       void* y, int M, int N, int K, int group, int bits, int lut_len, int64_t packed_row_stride,
-                       int64_t scale_row_stride, int integer_grid, float grid_minimum, int gated, cudaStream_t stream) {
+// Rotation on load: K = 2^log2 >= 512 and M * K fp32 values of shared memory beside the rings.
+int gemv_stream_rotation_supported(int M, int N, int K, int group, int bits, int lut_len, int integer_grid,
+                                   float grid_minimum, const void* signs) {
+  if (K < kWarpSpan || (K & (K - 1)) != 0 || size_t(M) * K * 4 > kMaxRotationBytes) return 0;
+  if (reinterpret_cast<uintptr_t>(signs) % 16) return 0;
+  StreamPlan plan{};
+  if (!codec_of(group, bits, lut_len, nullptr, integer_grid, grid_minimum, plan)) return 0;
+  const DeviceInfo& info = device_info();
+  return plan_stream(M, N, K, info.sm_count, info.max_smem_optin, 0, plan, size_t(M) * K * 4) ? 1 : 0;
+}
+
+int launch_gemv_stream_rotated(const void* x, const uint8_t* packed, const void* scales, const float* lut,
+                               const void* bias, void* y, int M, int N, int K, int group, int bits, int lut_len,
+                               int64_t packed_row_stride, int64_t scale_row_stride, int integer_grid,
+                               float grid_minimum, int gated, const int8_t* signs, int rotate, int normalize,
+                               cudaStream_t stream) {
   const DeviceInfo& info = device_info();
   StreamPlan p{};
+  const size_t extra = rotate ? size_t(M) * K * 4 : 0;
   MKB_REQUIRE(codec_of(group, bits, lut_len, nullptr, integer_grid, grid_minimum, p) &&
-                  plan_stream(M, N, K, info.sm_count, info.max_smem_optin, 0, p),
+                  plan_stream(M, N, K, info.sm_count, info.max_smem_optin, 0, p, extra),
               MKB_E_UNSUPPORTED, "gemv_stream: no decomposition for N=%d K=%d bits=%d group=%d", N, K, bits, group);
   StreamArgs a{};
   if (p.slabs > 1) {  // a grid of clusters must be resident as a whole, or it runs in waves
@@ -739,7 +826,7 @@ int launch_gemv_stream(const void* x, const uint8_t* packed, const void* scales,
     if (status != MKB_OK) return status;
     MKB_REQUIRE(cap >= 1, MKB_E_UNSUPPORTED, "gemv_stream: no cluster of %d CTAs fits the GPU", p.slabs);
     if (p.columns > cap)
-      MKB_REQUIRE(plan_stream(M, N, K, info.sm_count, info.max_smem_optin, cap, p),
+      MKB_REQUIRE(plan_stream(M, N, K, info.sm_count, info.max_smem_optin, cap, p, extra),
                   MKB_E_UNSUPPORTED, "gemv_stream: no decomposition for N=%d K=%d in %d clusters", N, K, cap);
   }
   a.x = static_cast<const __half*>(x); a.packed = packed; a.scales = static_cast<const __half*>(scales);
@@ -748,7 +835,21 @@ int launch_gemv_stream(const void* x, const uint8_t* packed, const void* scales,
   a.row_tiles = (N + 15) / 16; a.k_warps = K / (128 * p.KT); a.KW = p.KW; a.RG = p.RG; a.slabs = p.slabs;
   a.visits = p.visits; a.grid_min = p.mode == MODE_RAW ? grid_minimum : 0.f; a.batch = p.batch; a.early = 1; a.gated = gated;
   a.kw_inverse = (65536 + p.KW - 1) / p.KW; a.rg_inverse = (65536 + p.RG - 1) / p.RG;
+  if (rotate) {
+    a.rot_signs = signs;
+    while ((1 << a.rot_log2) < K) ++a.rot_log2;
+    a.rot_offset = uint32_t(p.smem - extra);
+    // the reference forms the scale in fp32: float(torch.tensor(1.0) / torch.tensor(math.sqrt(width)))
+    a.rot_scale = normalize ? 1.0f / float(sqrt(double(K))) : 1.0f;
+  }
   return dispatch_stream(a, p, stream, nullptr);
+}
+
+int launch_gemv_stream(const void* x, const uint8_t* packed, const void* scales, const float* lut, const void* bias,
+                       void* y, int M, int N, int K, int group, int bits, int lut_len, int64_t packed_row_stride,
+                       int64_t scale_row_stride, int integer_grid, float grid_minimum, int gated, cudaStream_t stream) {
+  return launch_gemv_stream_rotated(x, packed, scales, lut, bias, y, M, N, K, group, bits, lut_len, packed_row_stride,
+                                    scale_row_stride, integer_grid, grid_minimum, gated, nullptr, 0, 0, stream);
 }
 
 }  // namespace mkb

@@ -17,7 +17,7 @@
 // scale is one multiply after the last stage.
 // The reference needs ceil(log2(P)/3) global round trips plus casts, a sign multiply, two transposes
 // and a small library matmul for the same result.
-#include "mkb_common.cuh"
+#include "hadamard_steps.cuh"
 
 namespace mkb {
 namespace {
@@ -31,45 +31,6 @@ struct HadamardArgs {
   int W, factor, pow2, log2p, dtype, inverse;
   float scale;  // fp32(1) / fp32(sqrt(pow2)), or 1
 };
-
-template <int STAGES>
-__device__ __forceinline__ void butterfly_pass(float* buf, int groups, int stride, int stride_bits, float scale) {
-  for (int grp = threadIdx.x; grp < groups; grp += blockDim.x) {
-    const int low = grp & (stride - 1);
-    const int base = ((grp >> stride_bits) << (stride_bits + STAGES)) + low;
-    float v[1 << STAGES];
-    if (STAGES == 3 && stride == 1) {   // eight consecutive values: two 16-byte accesses, no bank conflicts
-      const float4 lo = *reinterpret_cast<const float4*>(buf + base), hi = *reinterpret_cast<const float4*>(buf + base + 4);
-      v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
-      v[4 % (1 << STAGES)] = hi.x; v[5 % (1 << STAGES)] = hi.y; v[6 % (1 << STAGES)] = hi.z; v[7 % (1 << STAGES)] = hi.w;
-    } else {
-#pragma unroll
-      for (int j = 0; j < (1 << STAGES); ++j) v[j] = buf[base + j * stride];
-    }
-#pragma unroll
-    for (int s = 0; s < STAGES; ++s) {
-      const int span = 1 << s;
-#pragma unroll
-      for (int j = 0; j < (1 << STAGES); ++j) {
-        if ((j & span) == 0) {
-          const float a = v[j], b = v[j + span];
-          v[j] = __fadd_rn(a, b);
-          v[j + span] = __fsub_rn(a, b);
-        }
-      }
-    }
-    if (STAGES == 3 && stride == 1) {
-      *reinterpret_cast<float4*>(buf + base) = make_float4(__fmul_rn(v[0], scale), __fmul_rn(v[1], scale),
-                                                          __fmul_rn(v[2], scale), __fmul_rn(v[3], scale));
-      *reinterpret_cast<float4*>(buf + base + 4) =
-          make_float4(__fmul_rn(v[4 % (1 << STAGES)], scale), __fmul_rn(v[5 % (1 << STAGES)], scale),
-                      __fmul_rn(v[6 % (1 << STAGES)], scale), __fmul_rn(v[7 % (1 << STAGES)], scale));
-    } else {
-#pragma unroll
-      for (int j = 0; j < (1 << STAGES); ++j) buf[base + j * stride] = __fmul_rn(v[j], scale);
-    }
-  }
-}
 
 __device__ __forceinline__ void depend_on_previous_grid() {
   // programmatic dependent launch: the kernel that follows in the stream (a packed matvec prefetching
@@ -146,25 +107,6 @@ __device__ __forceinline__ void flip_run(const int8_t* signs, int index, float* 
   }
 }
 
-// the stages that are left after `done_bits` of them, on `count` values in shared memory
-__device__ __forceinline__ void remaining_passes(float* buf, int count, int log2p, int done_bits, float last_scale) {
-  int remaining = log2p - done_bits, stride_bits = done_bits;
-  while (remaining > 0) {
-    const int stages = remaining >= 3 ? 3 : remaining;
-    remaining -= stages;
-    const float scale = remaining == 0 ? last_scale : 1.0f;
-    const int groups = count >> stages;
-    if (stages == 3) butterfly_pass<3>(buf, groups, 1 << stride_bits, stride_bits, scale);
-    else if (stages == 2) butterfly_pass<2>(buf, groups, 1 << stride_bits, stride_bits, scale);
-    else butterfly_pass<1>(buf, groups, 1 << stride_bits, stride_bits, scale);
-    stride_bits += stages;
-    __syncthreads();
-  }
-}
-
-constexpr int kWarpRun = 16;                 // values per lane in the warp kernel
-constexpr int kWarpSpan = 32 * kWarpRun;     // values per warp: nine stages without shared memory
-constexpr int kWarpBits = 9;
 
 __global__ void __launch_bounds__(1024) hadamard_warp_kernel(HadamardArgs a) {
   extern __shared__ __align__(16) float smem_f[];
@@ -179,29 +121,7 @@ __global__ void __launch_bounds__(1024) hadamard_warp_kernel(HadamardArgs a) {
     float v[kWarpRun];
     load_run<kWarpRun>(a.x, offset + first, a.dtype, v);
     if (a.signs != nullptr && !a.inverse) flip_run<kWarpRun>(a.signs, first, v);
-#pragma unroll
-    for (int s = 0; s < 4; ++s) {
-      const int span = 1 << s;
-#pragma unroll
-      for (int j = 0; j < kWarpRun; ++j) {
-        if ((j & span) == 0) {
-          const float low = v[j], high = v[j + span];
-          v[j] = __fadd_rn(low, high);
-          v[j + span] = __fsub_rn(low, high);
-        }
-      }
-    }
-#pragma unroll
-    for (int s = 4; s < kWarpBits; ++s) {
-      if (s < front) {
-        const int mask = 1 << (s - 4);
-        // the lane with the bit clear keeps low + high, its partner low - high: one rounding of
-        // (+-own + other), the same value as the add or the subtract
-        const float sign = (lane & mask) ? -1.0f : 1.0f;
-#pragma unroll
-        for (int j = 0; j < kWarpRun; ++j) v[j] = __fmaf_rn(v[j], sign, __shfl_xor_sync(0xffffffffu, v[j], mask));
-      }
-    }
+    warp_butterflies16(v, lane, front);
     if (direct) {
 #pragma unroll
       for (int j = 0; j < kWarpRun; ++j) v[j] = __fmul_rn(v[j], a.scale);

@@ -150,6 +150,7 @@ class PackedLinear(nn.Module):
         self.integer_grid, _ = kernels.integer_grid_of(levels)
         self.layout = layout_for(self.code_bits, self.in_features, self.group)
         self.maximum_fused_rows = 0 if self.layout is None else MAXIMUM_FUSED_ROWS
+        self._rotation_refused = False
         self._plans: dict[torch.dtype, kernels.MatvecPlan] = {}
         self._siblings: SiblingLaunch | None = None
         preserve_input_processing(original, self)
@@ -195,7 +196,36 @@ class PackedLinear(nn.Module):
             self._dense_weight = dense
         return dense
 
+    def take_rotation(self, inputs: Tensor, signs: Tensor) -> bool:
+        """Called by the rotation pre-hook: ``True`` when the coming ``forward`` will rotate ``inputs`` itself,
+        inside the matvec launch (``mkb_gemv_hadamard``); the hook then leaves the input as it is."""
+        rows = inputs.numel() // max(self.in_features, 1)
+        if (self.layout is None or self._siblings is not None or self.zeros is not None or torch.compiler.is_compiling()
+                or inputs.shape[-1] != self.in_features or not inputs.is_cuda or rows > self.maximum_fused_rows
+                or not kernels.rotated_matvec_supported(rows, self.in_features, inputs.dtype, profitable=True)
+                or self.scales.dtype != torch.float16
+                or self._rotation_refused):
+            return False
+        self._pending_rotation = signs
+        return True
+
     def forward(self, inputs: Tensor) -> Tensor:
+        signs = self.__dict__.pop("_pending_rotation", None)
+        if signs is not None:
+            rows = inputs.numel() // self.in_features
+            flat = inputs.reshape(rows, self.in_features).contiguous()
+            out = inputs.new_empty((rows, self.out_features))
+            try:
+                kernels.packed_matvec_rotated(flat, signs, self.packed, self.scales, self.values, self.bias, out,
+                                              group=self.group, bits=self.code_bits, integer_grid=self.integer_grid,
+                                              grid_minimum=self.grid_minimum)
+                return out.view(inputs.shape[:-1] + (self.out_features,))
+            except ValueError:
+                # the layer's codec is outside the fused launch: rotate with the transform's own launch from now on
+                self._rotation_refused = True
+                from mlkit_b200 import transforms
+
+                inputs = transforms.structured_transform(inputs, signs=signs)
         width = self.in_features
         if inputs.shape[-1] != width:
             raise ValueError("input width does not match the packed linear")

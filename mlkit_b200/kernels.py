@@ -89,6 +89,41 @@ def integer_grid_of(values: Tensor) -> tuple[bool, float]:
     return exact, low
 
 
+ROTATED_MAXIMUM_BYTES = 65536     # of fp32 activations the fused rotation holds in shared memory
+ROTATED_PROFITABLE_BYTES = 16384  # up to here the fused launch measured faster than transform + matvec
+
+
+def rotated_matvec_supported(rows: int, width: int, dtype: torch.dtype, *, profitable: bool = False) -> bool:
+    """Whether ``packed_matvec_rotated`` may cover the input (the C entry point checks the layer as well).
+    Every CTA of the matvec redoes the rotation, so its cost grows with the rows: measured on B200 at
+    K = 4096 the fused launch wins at one row (6.4 against 7.0 us), ties at two and loses at four;
+    ``profitable`` asks for the range where it wins."""
+    limit = ROTATED_PROFITABLE_BYTES if profitable else ROTATED_MAXIMUM_BYTES
+    return (dtype == torch.float16 and 1 <= rows <= 8 and width >= 512 and width & (width - 1) == 0
+            and rows * width * 4 <= limit)
+
+
+def packed_matvec_rotated(x: Tensor, signs: Tensor | None, packed: Tensor, scales: Tensor, values: Tensor,
+                          bias: Tensor | None, out: Tensor, *, group: int, bits: int, integer_grid: bool,
+                          grid_minimum: float, normalize: bool = True) -> Tensor:
+    """``out = matvec(S(x * signs))`` in one launch (``mkb_gemv_hadamard``): equal to ``structured_transform``
+    followed by ``packed_matvec`` bit for bit.  Raises ``ValueError`` where the fused launch does not apply."""
+    device = _require_cuda(x, signs, packed, scales, values, bias, out)
+    rows, width = x.shape
+    if signs is not None and signs.dtype != torch.int8:
+        raise ValueError("signs must be int8")
+    if bias is not None and bias.dtype != x.dtype:
+        bias = bias.to(x.dtype)
+    with torch.cuda.device(device):
+        status = _native.library().mkb_gemv_hadamard(
+            x.data_ptr(), _pointer(signs), packed.data_ptr(), scales.data_ptr(), values.data_ptr(), _pointer(bias),
+            out.data_ptr(), rows, out.shape[1], width, group, bits, values.numel(), _tag(x.dtype, "activation"),
+            _tag(scales.dtype, "scale"), width * bits // 8, scales.stride(0) if scales.dim() == 2 else -(-width // group),
+            int(integer_grid), float(grid_minimum), int(normalize), torch.cuda.current_stream().cuda_stream)
+    _native.check(status, "packed_matvec_rotated")
+    return out
+
+
 _gemm_workspaces: dict[tuple[int, int], Tensor] = {}
 GEMM_MAXIMUM_ROWS = 128
 

@@ -526,3 +526,55 @@ def test_zz_no_bounded_wait_expired_in_this_session():
     x = helpers.activations(8, 8192, seed=1)
     assert matvec.relative_l2(run_matvec(layer, x, "bulk"), oracle_matvec(layer, x)) < TOLERANCE
     assert kernels.workspace_status() == 0
+
+
+# ---------------------------------------------------------------- rotation fused into the matvec
+@pytest.mark.parametrize("case", [("int4", 4096, 4, 128), ("int4", 8192, 2, 128), ("int4", 1024, 8, 128),
+                                  ("int4", 512, 3, 128), ("nf4", 4096, 2, 64), ("int8", 2048, 4, 128),
+                                  ("int2", 4096, 1, 128)])
+def test_matvec_with_rotation_on_load_equals_transform_then_matvec(case):
+    """``mkb_gemv_hadamard``: every CTA rotates the activations in shared memory with the butterflies of the
+    transform kernel and rounds them to fp16 as that kernel stores them, so the result equals the two
+    launches bit for bit, with and without a sign vector, for every row count up to the limit."""
+    from mlkit_b200 import kernels
+
+    kind, width, most_rows, group = case
+    bits = {"int4": 4, "nf4": 4, "int8": 8, "int2": 2}[kind]
+    outputs = 272
+    layer = helpers.make_layer(outputs, width, bits, group, kind="nf4" if kind == "nf4" else "int", seed=width)
+    packed, scales, values = dev(layer["packed"]), dev(layer["scales16"]), dev(layer["values"])
+    integer, low = kernels.integer_grid_of(values)
+    rng = np.random.default_rng(width + bits)
+    signs = dev((rng.integers(0, 2, width) * 2 - 1).astype(np.int8))
+    for rows in range(1, most_rows + 1):
+        x = dev(helpers.activations(rows, width, seed=rows, outliers=True))
+        for sign_vector in (signs, None):
+            rotated = kernels.structured_transform(x, factor=1, power=width, signs=sign_vector)
+            expected = torch.empty((rows, outputs), dtype=torch.float16, device="cuda")
+            kernels.packed_matvec(rotated, packed, scales, values, None, None, expected, group=group, bits=bits,
+                                  integer_grid=integer, grid_minimum=low, kernel="stream")
+            fused = torch.empty_like(expected)
+            kernels.packed_matvec_rotated(x, sign_vector, packed, scales, values, None, fused, group=group, bits=bits,
+                                          integer_grid=integer, grid_minimum=low)
+            assert torch.equal(fused, expected), (case, rows, sign_vector is None)
+    # and against the oracle, end to end
+    x = helpers.activations(1, width, seed=3, outliers=True)
+    turned = transforms.randomized_transform(x.astype(np.float32), signs.cpu().numpy(), by_multiply=True)
+    got = torch.empty((1, outputs), dtype=torch.float16, device="cuda")
+    kernels.packed_matvec_rotated(dev(x), signs, packed, scales, values, None, got, group=group, bits=bits,
+                                  integer_grid=integer, grid_minimum=low)
+    assert matvec.relative_l2(got.cpu().numpy(), oracle_matvec(layer, turned.astype(np.float16))) < TOLERANCE
+
+
+def test_matvec_with_rotation_on_load_refuses_what_it_does_not_cover():
+    from mlkit_b200 import kernels
+
+    for width, rows in ((4096, 5), (14336, 1), (256, 1)):
+        layer = helpers.random_layer(64, width, 4, 128, seed=1, lut_len=16)
+        layer["values"] = codec.int_values(4)
+        out = torch.empty((rows, 64), dtype=torch.float16, device="cuda")
+        x = torch.zeros((rows, width), dtype=torch.float16, device="cuda")
+        assert not kernels.rotated_matvec_supported(rows, width, torch.float16)
+        with pytest.raises(ValueError, match="gemv_hadamard"):
+            kernels.packed_matvec_rotated(x, None, dev(layer["packed"]), dev(layer["scales16"]), dev(layer["values"]),
+                                          None, out, group=128, bits=4, integer_grid=True, grid_minimum=-8.0)

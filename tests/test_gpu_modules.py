@@ -14,6 +14,7 @@ import torch
 from torch import nn
 
 import mlkit_b200 as mk
+from mlkit_b200 import kernels
 from oracle import matvec, transforms as oracle_transforms
 
 pytestmark = pytest.mark.gpu
@@ -489,3 +490,40 @@ def test_device_encoder_stream_is_reused_only_while_codes_are_untouched():
     q.codes[0, 0] = (q.codes[0, 0] + 1) % 16          # in-place edit: the stream on record is stale
     assert q.packed_stream(4) is not q._stream[0]
     assert torch.equal(q.packed_stream(4), mk.pack(q.codes, 4))
+
+
+def test_rotated_packed_linear_fuses_the_rotation_for_few_rows():
+    """With at most M * K * 4 <= 16 KB of activations (where the fused launch is the faster one) the rotation
+    hook hands its sign vector to the layer, which rotates while it loads (``mkb_gemv_hadamard``); the output
+    equals the two launches bit for bit, and the hook still rotates by itself for more rows and when another
+    hook follows it."""
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.o_proj = nn.Linear(2048, 96, bias=True, dtype=torch.float16)
+
+        def forward(self, x):
+            return self.o_proj(x)
+
+    torch.manual_seed(5)
+    block = Block()
+    mk.rotate_inputs(block, seed=11)
+    packed = mk.optimize(mk.quantize(block, mk.int(4, group=128), calib=None), backend="packed")
+    layer = packed.module.o_proj
+    inputs = torch.randn(8, 2048, dtype=torch.float16)
+    calls = []
+    original = kernels.packed_matvec_rotated
+    kernels.packed_matvec_rotated = lambda *a, **k: (calls.append(a[0].shape[0]), original(*a, **k))[1]
+    try:
+        with torch.inference_mode():
+            fused = [packed(inputs[:rows]) for rows in (1, 2, 8)]
+            layer._rotation_refused = True
+            separate = [packed(inputs[:rows]) for rows in (1, 2, 8)]
+            layer._rotation_refused = False
+            layer.register_forward_pre_hook(lambda module, arguments: None)   # a later hook: the fusion stands down
+            after = packed(inputs[:1])
+    finally:
+        kernels.packed_matvec_rotated = original
+    assert calls == [1, 2]             # 2 x 2048 x 4 B = 16 KB is the limit; nothing fused after the later hook
+    assert all(torch.equal(a, b) for a, b in zip(fused, separate))
+    assert torch.equal(after, separate[0])
