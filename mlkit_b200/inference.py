@@ -210,7 +210,8 @@ class PackedLinear(nn.Module):
         return True
 
     def forward(self, inputs: Tensor) -> Tensor:
-        signs = self.__dict__.pop("_pending_rotation", None)
+        # (under torch.compile nothing is ever pending: take_rotation refuses while a graph is being traced)
+        signs = None if torch.compiler.is_compiling() else self.__dict__.pop("_pending_rotation", None)
         if signs is not None:
             rows = inputs.numel() // self.in_features
             flat = inputs.reshape(rows, self.in_features).contiguous()
