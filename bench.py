@@ -503,7 +503,8 @@ def reference_arm(args) -> None:
 def run_case(spec: str, device: torch.device, launches: int) -> None:
     """One layer shape, ``launches`` launches over distinct weight copies (each cold in L2), nothing
     else on the device: the small case a profiler captures.  Prints the mean launch time.
-    ``NAME[:ROWS[:KERNEL]]`` with NAME a block linear, ``qkv`` or ``gate_up``; ``rht:ROWS:WIDTH`` runs
+    ``NAME[:ROWS[:KERNEL]]`` with NAME a block linear, ``qkv`` or ``gate_up``; ``gemm:NAME:ROWS`` runs the
+    fused dequantise + GEMM on that shape; ``rht:ROWS:WIDTH`` runs
     the activation transform instead; ``tp_layer:WORLD:BATCH`` times the operators of one decoder layer with
     the shard shapes of WORLD ranks."""
     from mlkit_b200 import kernels
@@ -522,6 +523,9 @@ def run_case(spec: str, device: torch.device, launches: int) -> None:
                           "bytes_per_launch": 2 * rows * width * 2 + width}))
         return
     shapes = dict(LLAMA8B, qkv=(6144, 4096), gate_up=(28672, 4096))
+    fused_gemm = fields[0] == "gemm"      # gemm:NAME:ROWS -- the fused dequantise + GEMM on that layer shape
+    if fused_gemm:
+        fields = fields[1:]
     out_rows, width = shapes[fields[0]]
     rows = int(fields[1]) if len(fields) > 1 else 1
     kernel = fields[2] if len(fields) > 2 else "auto"
@@ -535,8 +539,12 @@ def run_case(spec: str, device: torch.device, launches: int) -> None:
     out = torch.empty(rows, out_rows, device=device, dtype=torch.float16)
 
     def launch(i):
-        kernels.packed_matvec(x, packed[i], scales[i], values, None, None, out, group=GROUP, bits=BITS,
-                              integer_grid=True, grid_minimum=-8.0, kernel=kernel)
+        if fused_gemm:
+            kernels.packed_gemm(x, packed[i], scales[i], values, None, out, group=GROUP, bits=BITS, integer_grid=True,
+                                grid_minimum=-8.0)
+        else:
+            kernels.packed_matvec(x, packed[i], scales[i], values, None, None, out, group=GROUP, bits=BITS,
+                                  integer_grid=True, grid_minimum=-8.0, kernel=kernel)
     launch(0)
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -547,7 +555,8 @@ def run_case(spec: str, device: torch.device, launches: int) -> None:
     torch.cuda.synchronize()
     us = start.elapsed_time(stop) * 1e3 / launches
     print(json.dumps({"case": spec, "launches": launches, "us_per_launch_eager": round(us, 2),
-                      "bytes_per_launch": matvec_bytes(out_rows, width, rows)}))
+                      "bytes_per_launch": matvec_bytes(out_rows, width, rows),
+                      "flops_per_launch": 2 * rows * out_rows * width}))
 
 
 def main() -> None:
