@@ -311,11 +311,13 @@ int mkb_decode_status(int* status);
  * sharding of src/mlkit/inference/packed_linear.py:145-179 would call after each row-parallel layer.
  *
  * Every rank allocates one exchange buffer (mkb_peer_alloc, mkb_peer_buffer_bytes(rows, H, world)
- * bytes, rows <= 8: a 2 KB header of arrival flags and counters, then 2 x world slots of rows x H
- * fp16), exports it (64-byte handle), and opens the buffers of all other ranks of the node.  A
- * reduction of a partial [M, H] is ONE kernel, mkb_peer_reduce_add_rmsnorm: CTA m copies row m of the
- * partial into this rank's slot on every rank with plain stores over NVLink and raises its flag
- * there, waits (bounded) for the flags of all ranks, adds the slots in rank order in fp32, rounds to
+ * bytes, rows <= 8: a 2 KB header of counters and a status word, then 2 x world slots of rows x H / 2
+ * packets of 8 bytes: two fp16 values and a 32-bit flag), exports it (64-byte handle), and opens the
+ * buffers of all other ranks of the node.  A reduction of a partial [M, H] is ONE kernel,
+ * mkb_peer_reduce_add_rmsnorm: CTA m writes row m of the partial, as packets whose flag is the number of
+ * the reduction, into this rank's slot on every rank with plain stores over NVLink (data and flag in one
+ * store: no fence, no second message), polls (bounded) the packets of all ranks in its own buffer, adds
+ * them in rank order in fp32, rounds to
  * fp16, and then residual += sum, normed = rmsnorm(residual) * weight; `reduced`, when not null,
  * receives the sum.  All ranks must issue the same sequence of reductions.  `peers` is a DEVICE
  * array of `world` buffer pointers (entry `rank` is the rank's own buffer).  A wait that expires sets

@@ -3,18 +3,22 @@
 // kernel per reduction, no library collective.
 //
 // Every rank owns one exchange buffer that all ranks of the node have mapped:
-//   [ flags: 2 parities x world x 8 rows x uint32 | sent: 8 x uint32 | status | poll limit | pad to 2 KB ]
-//   [ slots: 2 parities x world x rows x H fp16 ]
+//   [ header: sent: 8 x uint32 | status | poll limit | pad to 2 KB ]
+//   [ slots: 2 parities x world x rows x H/2 packets of 8 bytes ]
+// A packet is one 32-bit word of data (two fp16 values) and one 32-bit flag; data and flag travel in the
+// same store, so a receiver that sees the flag has the data: no fence, no second message.  (The stores are
+// 16 bytes = two packets; each 8-byte half validates itself, so it does not matter whether a 16-byte
+// store stays whole on its way.)
 // CTA m of the kernel handles row m of the partial [M, H]:
-//   * push: it copies row m into slot[parity][rank] of every rank's buffer (its own included) with
-//     plain 16-byte stores over NVLink, fences, and raises flag[parity][rank][m] = v in each buffer.
-//     v counts the reductions this row has taken part in (kept in the rank's own buffer); all ranks
-//     run the same sequence of reductions, so v is the same number everywhere, and parity = v & 1
-//     keeps a fast rank's next reduction out of the slots a slow rank is still reading;
-//   * wait: it polls (bounded) its own buffer until the `world` flags of row m carry v.  Every CTA
-//     pushes before it waits and flags persist, so no rank can wait for a rank that waits for it;
-//   * add + norm: it adds the `world` slots in rank order in fp32 (every rank gets the same bits),
-//     rounds the sum to fp16 as the library all-reduce would, adds the residual and normalises.
+//   * push: it writes row m, as packets flagged v, into slot[parity][rank] of every rank's buffer (its own
+//     included) with plain stores over NVLink.  v counts the reductions this row has taken part in (kept
+//     in the rank's own buffer); all ranks run the same sequence of reductions, so v is the same number
+//     everywhere, and parity = v & 1 keeps a fast rank's next reduction out of the slots a slow rank is
+//     still reading; a slot sees v, v + 2, v + 4, ..., so a stale packet never carries the awaited flag;
+//   * wait + add: every thread polls (bounded) the packets it needs of source 0, adds them, then source 1,
+//     ...: the sum is formed in rank order in fp32 (every rank gets the same bits).  Every CTA pushes before
+//     it waits and packets persist, so no rank can wait for a rank that waits for it;
+//   * norm: the sum is rounded to fp16 as the library all-reduce would, added to the residual, normalised.
 // A wait that gives up sets the status word and lets the kernel finish; later waits are skipped.
 #include "mkb_common.cuh"
 
@@ -28,16 +32,21 @@ constexpr int kGatherThreads = 1024;
 constexpr uint32_t kDefaultPolls = 60000000;  // of the order of half a minute: ranks are separate processes
 
 struct Header {
-  uint32_t flags[2][kMaxWorld][kMaxRows];   // written by the peers: [parity][source rank][row]
-  uint32_t sent[kMaxRows];                  // reductions row m has taken part in (touched by CTA m only)
+  uint32_t sent[kMaxRows];        // reductions row m has taken part in (touched by CTA m only)
   uint32_t status;                // non-zero when a wait expired
-  uint32_t poll_limit;            // polls of one flag before a wait gives up
+  uint32_t poll_limit;            // polls of one packet pair before a wait gives up
 };
 static_assert(sizeof(Header) <= kHeaderBytes, "header does not fit");
 
-__device__ __forceinline__ __half* slot_of(void* buffer, int parity, int source, int world, int64_t slot_halves) {
-  return reinterpret_cast<__half*>(static_cast<uint8_t*>(buffer) + kHeaderBytes) +
-         (int64_t(parity) * world + source) * slot_halves;
+// packets of (parity, source): [rows][H / 4] units of 16 bytes (two packets: four fp16 values)
+__device__ __forceinline__ uint4* slot_of(void* buffer, int parity, int source, int world, int64_t slot_units) {
+  return reinterpret_cast<uint4*>(static_cast<uint8_t*>(buffer) + kHeaderBytes) + (int64_t(parity) * world + source) * slot_units;
+}
+
+__device__ __forceinline__ uint4 load_volatile16(const uint4* address) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(address));
+  return v;
 }
 
 // One CTA per row m: push, wait, then residual[m,:] += sum over ranks of slot[r][m,:]; normed = rmsnorm(residual) * weight.
@@ -47,17 +56,17 @@ constexpr int kGatherPieces = 2;   // rows up to 1024 * 2 * 8 = 16384 elements s
 __global__ void __launch_bounds__(kGatherThreads) peer_reduce_add_rmsnorm_kernel(
     const __half* __restrict__ partial, void* const* peers, void* own, __half* __restrict__ residual,
     const __half* __restrict__ weight, __half* __restrict__ normed, __half* __restrict__ reduced, int H, int world,
-    int rank, int64_t slot_halves, float eps) {
+    int rank, int64_t slot_units, float eps) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ float part_s[kGatherThreads / 32];
-  __shared__ int ready_s;
   Header* mine = static_cast<Header*>(own);
   const int m = blockIdx.x;
   const uint32_t v = mine->sent[m] + 1;   // only this CTA touches sent[m]
   const int parity = int(v & 1u);
+  const int64_t row_units = int64_t(m) * (H / 4);   // 16-byte units of row m inside a slot
   {
-    // push row m of the partial into this rank's slot on every rank
+    // push row m of the partial, as flagged packets, into this rank's slot on every rank
     const uint4* source = reinterpret_cast<const uint4*>(partial + int64_t(m) * H);
     uint4 piece[kGatherPieces];
 #pragma unroll
@@ -66,58 +75,51 @@ __global__ void __launch_bounds__(kGatherThreads) peer_reduce_add_rmsnorm_kernel
       piece[k] = i * 8 < H ? source[i] : make_uint4(0u, 0u, 0u, 0u);
     }
     for (int p = 0; p < world; ++p) {
-      uint4* target = reinterpret_cast<uint4*>(slot_of(peers[p], parity, rank, world, slot_halves) + int64_t(m) * H);
+      uint4* target = slot_of(peers[p], parity, rank, world, slot_units) + row_units;
 #pragma unroll
       for (int k = 0; k < kGatherPieces; ++k) {
         const int i = k * kGatherThreads + threadIdx.x;
-        if (i * 8 < H) target[i] = piece[k];
+        if (i * 8 < H) {
+          target[2 * i] = make_uint4(piece[k].x, v, piece[k].y, v);
+          target[2 * i + 1] = make_uint4(piece[k].z, v, piece[k].w, v);
+        }
       }
     }
   }
-  __threadfence_system();
-  if (threadIdx.x == 0) ready_s = 1;
-  __syncthreads();
-  if (threadIdx.x < world) {
-    // release: the barrier above ordered every thread's stores before this point for this thread;
-    // the fence makes them visible system-wide before the flag that announces them
-    __threadfence_system();
-    volatile uint32_t* raised = &static_cast<Header*>(peers[threadIdx.x])->flags[parity][rank][m];
-    *raised = v;
-  }
-  if (threadIdx.x == 0) mine->sent[m] = v;
-  if (threadIdx.x < world) {
-    const volatile uint32_t* flag = &mine->flags[parity][threadIdx.x][m];
-    // a wait that expired once is not repeated: every later reduction of a broken exchange would
-    // otherwise add its own timeout
-    const uint32_t limit = mine->status != 0 ? 0u : mine->poll_limit;
-    uint32_t polls = 0;
-    while (*flag != v && polls < limit) ++polls;
-    if (*flag != v) {
-      ready_s = 0;
-      atomicExch(&mine->status, 1u);
-    }
-  }
-  __threadfence_system();
-  __syncthreads();
-  const bool ready = ready_s != 0;   // on expiry the kernel still runs through, with whatever arrived
+  // a wait that expired once is not repeated: every later reduction of a broken exchange would otherwise
+  // add its own timeout
+  uint32_t limit = mine->status != 0 ? 0u : mine->poll_limit;
+  bool expired = false;
 
   const int64_t base = int64_t(blockIdx.x) * H;
   uint4 kept[kGatherPieces];
   float sq = 0.f;
 #pragma unroll
   for (int piece = 0; piece < kGatherPieces; ++piece) {
-    const int i = (piece * kGatherThreads + threadIdx.x) * 8;
+    const int unit = piece * kGatherThreads + threadIdx.x;
+    const int i = unit * 8;
     kept[piece] = make_uint4(0u, 0u, 0u, 0u);
     if (i < H) {
       float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       for (int r = 0; r < world; ++r) {
-        const __half* slot = slot_of(own, parity, r, world, slot_halves);
-        // cache-volatile: the slot was written from outside this GPU
-        const uint4 part = ready ? __ldcv(reinterpret_cast<const uint4*>(slot + base + i)) : make_uint4(0u, 0u, 0u, 0u);
-        const __half2* ph = reinterpret_cast<const __half2*>(&part);
+        // the slot is written from outside this GPU: volatile loads, until both units carry the flag
+        const uint4* from = slot_of(own, parity, r, world, slot_units) + row_units + 2 * unit;
+        uint4 low = load_volatile16(from), high = load_volatile16(from + 1);
+        uint32_t polls = 0;
+        while ((low.y != v || low.w != v || high.y != v || high.w != v) && polls < limit) {
+          low = load_volatile16(from);
+          high = load_volatile16(from + 1);
+          ++polls;
+        }
+        if (low.y != v || low.w != v || high.y != v || high.w != v) {
+          expired = true;
+          limit = 0;
+          continue;     // on expiry the kernel still runs through, without what did not arrive
+        }
+        const uint32_t words[4] = {low.x, low.z, high.x, high.z};
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const float2 f = __half22float2(ph[q]);
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&words[q]));
           sum[2 * q] += f.x;
           sum[2 * q + 1] += f.y;
         }
@@ -143,6 +145,8 @@ __global__ void __launch_bounds__(kGatherThreads) peer_reduce_add_rmsnorm_kernel
       }
     }
   }
+  if (threadIdx.x == 0) mine->sent[m] = v;
+  if (expired) atomicExch(&mine->status, 1u);
 #pragma unroll
   for (int offset = 16; offset; offset >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, offset);
   if ((threadIdx.x & 31) == 0) part_s[threadIdx.x >> 5] = sq;
@@ -191,7 +195,7 @@ cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, v
 
 extern "C" int64_t mkb_peer_buffer_bytes(int rows, int H, int world) {
   if (rows < 1 || rows > mkb::kMaxRows || H < 8 || world < 1 || world > mkb::kMaxWorld) return 0;
-  return mkb::kHeaderBytes + int64_t(2) * world * rows * H * 2;
+  return mkb::kHeaderBytes + int64_t(2) * world * rows * H * 4;   // packets: 4 bytes of flags per 4 bytes of data
 }
 
 extern "C" int mkb_peer_set_poll_limit(void* own, int64_t polls) {
@@ -262,7 +266,7 @@ extern "C" int mkb_peer_reduce_add_rmsnorm(const void* partial, void* const* pee
   const cudaError_t launched = launch_dependent(
       peer_reduce_add_rmsnorm_kernel, dim3(M), dim3(kGatherThreads), stream, static_cast<const __half*>(partial), peers,
       own, static_cast<__half*>(residual), static_cast<const __half*>(weight), static_cast<__half*>(normed),
-      static_cast<__half*>(reduced), H, world, rank, int64_t(rows) * H, eps);
+      static_cast<__half*>(reduced), H, world, rank, int64_t(rows) * (H / 4), eps);
   if (launched != cudaSuccess) return cuda_fail(launched, "peer_reduce_add_rmsnorm launch");
   return MKB_OK;
 }
