@@ -108,40 +108,129 @@ __device__ __forceinline__ void flip_run(const int8_t* signs, int index, float* 
 }
 
 
+// four consecutive activations starting at a multiple of four
+__device__ __forceinline__ void load_four(const void* x, int64_t index, int dtype, float* v) {
+  if (dtype == MKB_F32) {
+    const float4 four = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(x) + index));
+    v[0] = four.x; v[1] = four.y; v[2] = four.z; v[3] = four.w;
+    return;
+  }
+  const uint2 raw = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(x) + index));
+  const uint32_t words[2] = {raw.x, raw.y};
+#pragma unroll
+  for (int w = 0; w < 2; ++w) {
+    const float2 pair = dtype == MKB_F16 ? __half22float2(*reinterpret_cast<const __half2*>(&words[w]))
+                                         : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&words[w]));
+    v[2 * w] = pair.x;
+    v[2 * w + 1] = pair.y;
+  }
+}
+
+__device__ __forceinline__ uint32_t pack_pair(float low, float high, int dtype) {
+  if (dtype == MKB_F16) {
+    const __half2 pair = __floats2half2_rn(low, high);
+    return *reinterpret_cast<const uint32_t*>(&pair);
+  }
+  const __nv_bfloat162 pair = __floats2bfloat162_rn(low, high);
+  return *reinterpret_cast<const uint32_t*>(&pair);
+}
+
+__device__ __forceinline__ void store_four(void* y, int64_t index, int dtype, const float* v) {
+  if (dtype == MKB_F32) {
+    *reinterpret_cast<float4*>(static_cast<float*>(y) + index) = make_float4(v[0], v[1], v[2], v[3]);
+    return;
+  }
+  *reinterpret_cast<uint2*>(static_cast<uint16_t*>(y) + index) = make_uint2(pack_pair(v[0], v[1], dtype), pack_pair(v[2], v[3], dtype));
+}
+
+__device__ __forceinline__ void flip_four(const int8_t* signs, int index, float* v) {
+  const uint32_t word = *reinterpret_cast<const uint32_t*>(signs + index);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[j] = __fmul_rn(v[j], float(int8_t((word >> (8 * j)) & 0xffu)));
+}
+
+// The last one to three stages, fused with the scale, the inverse sign flip and the store: a thread takes two
+// neighbouring columns of a butterfly group (8-byte shared loads), so a warp stores 32 consecutive pairs.
+template <int STAGES>
+__device__ __forceinline__ void final_pass_store(const float* buf, const HadamardArgs& a, int64_t offset, int stride_bits) {
+  const int stride = 1 << stride_bits, pairs = a.W >> (STAGES + 1);
+  for (int pair = threadIdx.x; pair < pairs; pair += blockDim.x) {
+    const int grp = 2 * pair, low = grp & (stride - 1);
+    const int base = ((grp >> stride_bits) << (stride_bits + STAGES)) + low;
+    float2 v[1 << STAGES];
+#pragma unroll
+    for (int j = 0; j < (1 << STAGES); ++j) v[j] = *reinterpret_cast<const float2*>(buf + base + j * stride);
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      const int span = 1 << s;
+#pragma unroll
+      for (int j = 0; j < (1 << STAGES); ++j) {
+        if ((j & span) == 0) {
+          const float2 p = v[j], q = v[j + span];
+          v[j] = make_float2(__fadd_rn(p.x, q.x), __fadd_rn(p.y, q.y));
+          v[j + span] = make_float2(__fsub_rn(p.x, q.x), __fsub_rn(p.y, q.y));
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < (1 << STAGES); ++j) {
+      const int at = base + j * stride;
+      float x0 = __fmul_rn(v[j].x, a.scale), x1 = __fmul_rn(v[j].y, a.scale);
+      if (a.signs != nullptr && a.inverse) {
+        x0 = __fmul_rn(x0, float(a.signs[at]));
+        x1 = __fmul_rn(x1, float(a.signs[at + 1]));
+      }
+      if (a.dtype == MKB_F32) *reinterpret_cast<float2*>(static_cast<float*>(a.y) + offset + at) = make_float2(x0, x1);
+      else *reinterpret_cast<uint32_t*>(static_cast<uint16_t*>(a.y) + offset + at) = pack_pair(x0, x1, a.dtype);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(1024) hadamard_warp_kernel(HadamardArgs a) {
   extern __shared__ __align__(16) float smem_f[];
   depend_on_previous_grid();
   float* buf = smem_f;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const int64_t offset = int64_t(blockIdx.x) * a.W;
-  const int front = a.log2p < kWarpBits ? a.log2p : kWarpBits;   // at least 4: the block is 16 wide or wider
+  const int front = a.log2p < kWarpBits ? a.log2p : kWarpBits;
   const bool direct = a.log2p <= kWarpBits;
   for (int chunk = warp; chunk < a.W / kWarpSpan; chunk += warps) {
-    const int first = chunk * kWarpSpan + lane * kWarpRun;
+    const int first = chunk * kWarpSpan + lane * 4;     // group m of the lane starts at first + 128 * m
     float v[kWarpRun];
-    load_run<kWarpRun>(a.x, offset + first, a.dtype, v);
-    if (a.signs != nullptr && !a.inverse) flip_run<kWarpRun>(a.signs, first, v);
-    warp_butterflies16(v, lane, front);
+#pragma unroll
+    for (int m = 0; m < 4; ++m) load_four(a.x, offset + first + 128 * m, a.dtype, v + 4 * m);
+    if (a.signs != nullptr && !a.inverse) {
+#pragma unroll
+      for (int m = 0; m < 4; ++m) flip_four(a.signs, first + 128 * m, v + 4 * m);
+    }
+    warp_butterflies4x4(v, lane, front);
     if (direct) {
 #pragma unroll
       for (int j = 0; j < kWarpRun; ++j) v[j] = __fmul_rn(v[j], a.scale);
-      if (a.signs != nullptr && a.inverse) flip_run<kWarpRun>(a.signs, first, v);
-      store_run<kWarpRun>(a.y, offset + first, a.dtype, v);
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        if (a.signs != nullptr && a.inverse) flip_four(a.signs, first + 128 * m, v + 4 * m);
+        store_four(a.y, offset + first + 128 * m, a.dtype, v + 4 * m);
+      }
     } else {
 #pragma unroll
-      for (int q = 0; q < kWarpRun / 4; ++q)
-        *reinterpret_cast<float4*>(buf + first + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      for (int m = 0; m < 4; ++m)
+        *reinterpret_cast<float4*>(buf + first + 128 * m) = make_float4(v[4 * m], v[4 * m + 1], v[4 * m + 2], v[4 * m + 3]);
     }
   }
   if (direct) return;
   __syncthreads();
-  remaining_passes(buf, a.W, a.log2p, kWarpBits, a.scale);
-  for (int i = threadIdx.x; i < a.W / 8; i += blockDim.x) {
-    const float4 lo = *reinterpret_cast<const float4*>(buf + 8 * i), hi = *reinterpret_cast<const float4*>(buf + 8 * i + 4);
-    float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-    if (a.signs != nullptr && a.inverse) flip_run<8>(a.signs, 8 * i, v);
-    store_run<8>(a.y, offset + 8 * i, a.dtype, v);
+  // all but the last pass in shared memory, three stages each; the last one to three stages go straight out
+  int remaining = a.log2p - kWarpBits, stride_bits = kWarpBits;
+  while (remaining > 3) {
+    butterfly_pass<3>(buf, a.W >> 3, 1 << stride_bits, stride_bits, 1.0f);
+    stride_bits += 3;
+    remaining -= 3;
+    __syncthreads();
   }
+  if (remaining == 3) final_pass_store<3>(buf, a, offset, stride_bits);
+  else if (remaining == 2) final_pass_store<2>(buf, a, offset, stride_bits);
+  else final_pass_store<1>(buf, a, offset, stride_bits);
 }
 
 __global__ void hadamard_kernel(HadamardArgs a) {
@@ -235,7 +324,7 @@ extern "C" int mkb_hadamard(const void* x, const int8_t* signs, const float* bas
   a.scale = normalize ? 1.0f / float(sqrt(double(pow2))) : 1.0f;
   const auto aligned = [](const void* p, uintptr_t to) { return reinterpret_cast<uintptr_t>(p) % to == 0; };
   const bool by_warp = factor == 1 && W % kWarpSpan == 0 && aligned(x, 16) && aligned(y, 16) &&
-                       (signs == nullptr || aligned(signs, 8));
+                       (signs == nullptr || aligned(signs, 4));
   void (*kernel)(HadamardArgs) = factor > 1 ? hadamard_factor_kernel : by_warp ? hadamard_warp_kernel : hadamard_kernel;
   size_t smem;
   dim3 grid((unsigned)M);

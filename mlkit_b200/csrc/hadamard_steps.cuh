@@ -96,4 +96,48 @@ __device__ __forceinline__ void warp_butterflies16(float (&v)[kWarpRun], int lan
   }
 }
 
+// The same stages for a warp that holds its 512 values as four groups of four consecutive ones, 128 apart:
+// value v[4 * m + j] is element 128 * m + 4 * lane + j.  Strides 1 and 2 stay inside a group, strides 4..64
+// are lane exchanges, strides 128 and 256 pair the groups; the order is still ascending.  Loads and stores of
+// a group are 32 lanes x 4 consecutive values: fully coalesced in global memory, conflict-free in shared memory.
+__device__ __forceinline__ void warp_butterflies4x4(float (&v)[kWarpRun], int lane, int front) {
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    if (s < front) {
+      const int span = 1 << s;
+#pragma unroll
+      for (int j = 0; j < kWarpRun; ++j) {
+        if ((j & span) == 0) {
+          const float low = v[j], high = v[j + span];
+          v[j] = __fadd_rn(low, high);
+          v[j + span] = __fsub_rn(low, high);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int s = 2; s < 7; ++s) {
+    if (s < front) {
+      const int mask = 1 << (s - 2);
+      const float sign = (lane & mask) ? -1.0f : 1.0f;   // the partner with the bit set keeps low - high
+#pragma unroll
+      for (int j = 0; j < kWarpRun; ++j) v[j] = __fmaf_rn(v[j], sign, __shfl_xor_sync(0xffffffffu, v[j], mask));
+    }
+  }
+#pragma unroll
+  for (int s = 7; s < kWarpBits; ++s) {
+    if (s < front) {
+      const int span = 4 << (s - 7);   // groups m and m ^ 1 (stride 128), then m and m ^ 2 (stride 256)
+#pragma unroll
+      for (int j = 0; j < kWarpRun; ++j) {
+        if ((j & span) == 0) {
+          const float low = v[j], high = v[j + span];
+          v[j] = __fadd_rn(low, high);
+          v[j + span] = __fsub_rn(low, high);
+        }
+      }
+    }
+  }
+}
+
 }  // namespace mkb
