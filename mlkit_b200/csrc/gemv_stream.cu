@@ -300,8 +300,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
           const uint4 flips = *reinterpret_cast<const uint4*>(a.rot_signs + first[c]);
           const uint32_t words[4] = {flips.x, flips.y, flips.z, flips.w};
 #pragma unroll
-          for (int j = 0; j < kWarpRun; ++j)
-            values[j] = __fmul_rn(values[j], float(int8_t((words[j >> 2] >> (8 * (j & 3))) & 0xffu)));
+          for (int j = 0; j < kWarpRun; ++j)   // the sign byte's top bit flips the value's sign: the product with +-1
+            values[j] = __uint_as_float(__float_as_uint(values[j]) ^ ((words[j >> 2] << (24 - 8 * (j & 3))) & 0x80000000u));
         }
         warp_butterflies16(values, lane, front);
         if (a.rot_log2 <= kWarpBits) {

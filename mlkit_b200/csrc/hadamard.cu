@@ -144,9 +144,11 @@ __device__ __forceinline__ void store_four(void* y, int64_t index, int dtype, co
 }
 
 __device__ __forceinline__ void flip_four(const int8_t* signs, int index, float* v) {
+  // a sign of -1 is the byte 0xff: its top bit, moved to bit 31, flips the value's sign, which is what the
+  // multiplication by +-1 does, bit for bit
   const uint32_t word = *reinterpret_cast<const uint32_t*>(signs + index);
 #pragma unroll
-  for (int j = 0; j < 4; ++j) v[j] = __fmul_rn(v[j], float(int8_t((word >> (8 * j)) & 0xffu)));
+  for (int j = 0; j < 4; ++j) v[j] = __uint_as_float(__float_as_uint(v[j]) ^ ((word << (24 - 8 * j)) & 0x80000000u));
 }
 
 // The last one to three stages, fused with the scale, the inverse sign flip and the store: a thread takes two
