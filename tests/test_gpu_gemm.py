@@ -122,3 +122,23 @@ def test_packed_linear_takes_the_fused_gemm_between_nine_and_128_rows():
                                       zeros=None, integer_grid=True, grid_minimum=-8.0, levels=16, outputs=4096)
         wide = torch.randn(200, 1024, device="cuda").half()        # above 128 rows: the dense route
         assert torch.equal(packed(wide), torch.nn.functional.linear(wide, packed.weight, packed.bias))
+
+
+def test_packed_linear_runs_nine_to_sixteen_rows_as_matvec_chunks():
+    """Up to 16 rows (32 for layers the fused GEMM does not cover) the module runs the matvec on chunks of
+    eight rows: every output row equals the row the matvec gives for it alone or in any other batch."""
+    import mlkit_b200 as mk
+
+    torch.manual_seed(1)
+    for fmt, most in ((mk.int(4, group=128), 16), (mk.nf4(group=64), 32)):
+        linear = torch.nn.Linear(1024, 512, bias=True).half().cuda()
+        packed = mk.PackedLinear(linear, fmt(linear.weight.detach().float(), mk.Ctx("layer", device="cuda")))
+        with torch.inference_mode():
+            x = torch.randn(most, 1024, device="cuda").half()
+            whole = packed(x)
+            pieces = torch.cat([packed(x[start:start + 8]) for start in range(0, most, 8)])
+            assert torch.equal(whole, pieces)
+            odd = packed(x[:most - 3])
+            assert torch.equal(odd, whole[:most - 3])
+            dense = torch.nn.functional.linear(x, packed.weight, packed.bias)
+            assert float((whole.float() - dense.float()).norm() / dense.float().norm()) < TOLERANCE
