@@ -513,23 +513,29 @@ class CapturedCall:
         self.device = next((t.device for t in _module_tensors(function) if t.is_cuda), None)
         self._last: torch.cuda.Event | None = None
 
-    @staticmethod
-    def _signature(inputs: tuple[Tensor, ...]) -> tuple:
-        return tuple((tuple(t.shape), t.dtype, t.device, t.data_ptr() if not t.is_cuda and t.is_pinned() else 0)
-                     for t in inputs)
+    MAXIMUM_PINNED_CAPTURES = 32   # distinct pinned input tensors that get a graph of their own
 
-    def _capture(self, inputs: tuple[Tensor, ...]) -> dict[str, Any]:
+    def _signature(self, inputs: tuple[Tensor, ...]) -> tuple:
+        # a pinned host input is read in place, so its address is part of the signature; a caller that passes
+        # a new pinned tensor every time would grow a graph per call, so beyond a bound pinned inputs are
+        # staged like pageable ones (one graph per shape)
+        in_place = len(self.entries) < self.MAXIMUM_PINNED_CAPTURES
+        return tuple((tuple(t.shape), t.dtype, t.device,
+                      t.data_ptr() if in_place and not t.is_cuda and t.is_pinned() else 0) for t in inputs)
+
+    def _capture(self, inputs: tuple[Tensor, ...], signature: tuple) -> dict[str, Any]:
         device = self.device or next((t.device for t in inputs if t.is_cuda), None)
         if device is None:
             raise ValueError("capture needs a CUDA module or a CUDA input")
         to_host = self.host_outputs if self.host_outputs is not None else all(not t.is_cuda for t in inputs)
         statics, sources = [], []
-        for given in inputs:
+        for given, (_, _, _, address) in zip(inputs, signature):
             statics.append(torch.empty(given.shape, dtype=given.dtype, device=device))
             if given.is_cuda:
                 sources.append(None)
             else:
-                sources.append(given if given.is_pinned() else torch.empty(given.shape, dtype=given.dtype, device="cpu").pin_memory())
+                in_place = given.is_pinned() and address != 0
+                sources.append(given if in_place else torch.empty(given.shape, dtype=given.dtype, device="cpu").pin_memory())
         graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream(device=device)
         side.wait_stream(torch.cuda.current_stream(device))
         results: list[Tensor] = []
@@ -578,7 +584,7 @@ class CapturedCall:
         signature = self._signature(inputs)
         entry = self.entries.get(signature)
         if entry is None:
-            entry = self.entries[signature] = self._capture(inputs)
+            entry = self.entries[signature] = self._capture(inputs, signature)
         for static, source, given in zip(entry["statics"], entry["sources"], inputs):
             if source is None:
                 static.copy_(given, non_blocking=True)
