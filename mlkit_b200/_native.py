@@ -50,6 +50,7 @@ SIGNATURES = {
     "mkb_peer_reduce_add_rmsnorm": (c_int, [c_void_p] * 7 + [c_int] * 5 + [c_float, c_void_p]),
     "mkb_peer_status": (c_int, [c_void_p, c_void_p]),
     "mkb_peer_set_poll_limit": (c_int, [c_void_p, c_int64]),
+    "mkb_peer_set_split": (c_int, [c_void_p, c_int]),
 }
 
 _library = None

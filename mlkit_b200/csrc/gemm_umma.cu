@@ -188,10 +188,21 @@ __global__ void __launch_bounds__(kThreadsG, 1) gemm_umma_kernel(const GemmArgs 
     for (int d = 0; d < kCodeStages - 1; ++d) issue_codes();
   }
   // the scales of the unit: row r, block t at scale_s[r * pitch + t] (weights: no dependency on the previous grid)
-  for (int i = tid; i < 128 * blocks; i += kThreadsG) {
-    const int r = i / blocks, t = i - r * blocks;
-    const int64_t global_row = min(row_block * 128 + r, a.N - 1);
-    scale_s[r * kScalePitch + t] = __ldg(a.scales + global_row * a.scale_row_stride + first_block + t);
+  {
+    // all of a thread's loads are issued before the first is stored: one memory latency, not one per scale
+    constexpr int kLoads = 128 * kMaxUnitBlocks / kThreadsG;
+    __half held[kLoads];
+#pragma unroll
+    for (int j = 0; j < kLoads; ++j) {
+      const int i = tid + j * kThreadsG, r = i / blocks, t = i - r * blocks;
+      const int64_t global_row = min(row_block * 128 + r, a.N - 1);
+      held[j] = i < 128 * blocks ? __ldg(a.scales + global_row * a.scale_row_stride + first_block + t) : __half();
+    }
+#pragma unroll
+    for (int j = 0; j < kLoads; ++j) {
+      const int i = tid + j * kThreadsG, r = i / blocks, t = i - r * blocks;
+      if (i < 128 * blocks) scale_s[r * kScalePitch + t] = held[j];
+    }
   }
   // rows M..Mpad of the activation tiles are never copied: they read as zero
   for (int i = tid; i < a.b_stages * a.b_stage_bytes / 16; i += kThreadsG)

@@ -22,6 +22,9 @@
 // A wait that gives up sets the status word and lets the kernel finish; later waits are skipped.
 #include "mkb_common.cuh"
 
+#include <mutex>
+#include <unordered_map>
+
 namespace mkb {
 namespace {
 
@@ -31,10 +34,13 @@ constexpr int kMaxRows = 8;
 constexpr int kGatherThreads = 1024;
 constexpr uint32_t kDefaultPolls = 60000000;  // of the order of half a minute: ranks are separate processes
 
+constexpr int kMaxSplit = 8;      // CTAs that share one row
+
 struct Header {
-  uint32_t sent[kMaxRows];        // reductions row m has taken part in (touched by CTA m only)
+  uint32_t sent[kMaxRows][kMaxSplit];      // reductions CTA (m, s) has taken part in (touched by that CTA only)
+  uint2 squares[2][kMaxRows][kMaxSplit];   // [parity][row][split]: a partial sum of squares and its flag
   uint32_t status;                // non-zero when a wait expired
-  uint32_t poll_limit;            // polls of one packet pair before a wait gives up
+  uint32_t poll_limit;            // polls of one packet before a wait gives up
 };
 static_assert(sizeof(Header) <= kHeaderBytes, "header does not fit");
 
@@ -48,10 +54,18 @@ __device__ __forceinline__ uint4 load_volatile16(const uint4* address) {
   asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(address));
   return v;
 }
+__device__ __forceinline__ uint2 load_volatile8(const uint2* address) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(address));
+  return v;
+}
 
-// One CTA per row m: push, wait, then residual[m,:] += sum over ranks of slot[r][m,:]; normed = rmsnorm(residual) * weight.
+// CTA (m, s) owns slice s of row m: push, wait, then residual[m, slice] += sum over ranks of slot[r][m, slice];
+// the slices' sums of squares meet through the rank's own header; normed = rmsnorm(residual) * weight.
 // `reduced` (optional) receives the fp16 sum, for callers that need the all-reduced tensor itself.
-constexpr int kGatherPieces = 2;   // rows up to 1024 * 2 * 8 = 16384 elements stay in registers
+// One CTA pushes world * slice * 4 bytes over NVLink; a single SM sustains only a few tens of GB/s of remote
+// stores, so wide worlds split the row over several CTAs (measured at 8 ranks: 256 KB from one SM cost ~10 us).
+constexpr int kGatherPieces = 2;   // slices up to 1024 * 2 * 8 = 16384 elements stay in registers
 
 __global__ void __launch_bounds__(kGatherThreads) peer_reduce_add_rmsnorm_kernel(
     const __half* __restrict__ partial, void* const* peers, void* own, __half* __restrict__ residual,
@@ -60,26 +74,28 @@ __global__ void __launch_bounds__(kGatherThreads) peer_reduce_add_rmsnorm_kernel
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ float part_s[kGatherThreads / 32];
+  __shared__ float total_s;
   Header* mine = static_cast<Header*>(own);
-  const int m = blockIdx.x;
-  const uint32_t v = mine->sent[m] + 1;   // only this CTA touches sent[m]
+  const int m = blockIdx.x, split = gridDim.y, part = blockIdx.y;
+  const int slice = H / split, first = part * slice;       // this CTA's elements of the row
+  const uint32_t v = mine->sent[m][part] + 1;   // only this CTA touches sent[m][part]
   const int parity = int(v & 1u);
-  const int64_t row_units = int64_t(m) * (H / 4);   // 16-byte units of row m inside a slot
+  const int64_t row_units = int64_t(m) * (H / 4) + first / 4;   // 16-byte units of the slice inside a slot
   {
-    // push row m of the partial, as flagged packets, into this rank's slot on every rank
-    const uint4* source = reinterpret_cast<const uint4*>(partial + int64_t(m) * H);
+    // push the slice, as flagged packets, into this rank's slot on every rank
+    const uint4* source = reinterpret_cast<const uint4*>(partial + int64_t(m) * H + first);
     uint4 piece[kGatherPieces];
 #pragma unroll
     for (int k = 0; k < kGatherPieces; ++k) {
       const int i = k * kGatherThreads + threadIdx.x;
-      piece[k] = i * 8 < H ? source[i] : make_uint4(0u, 0u, 0u, 0u);
+      piece[k] = i * 8 < slice ? source[i] : make_uint4(0u, 0u, 0u, 0u);
     }
     for (int p = 0; p < world; ++p) {
       uint4* target = slot_of(peers[p], parity, rank, world, slot_units) + row_units;
 #pragma unroll
       for (int k = 0; k < kGatherPieces; ++k) {
         const int i = k * kGatherThreads + threadIdx.x;
-        if (i * 8 < H) {
+        if (i * 8 < slice) {
           target[2 * i] = make_uint4(piece[k].x, v, piece[k].y, v);
           target[2 * i + 1] = make_uint4(piece[k].z, v, piece[k].w, v);
         }
@@ -91,7 +107,7 @@ __global__ void __launch_bounds__(kGatherThreads) peer_reduce_add_rmsnorm_kernel
   uint32_t limit = mine->status != 0 ? 0u : mine->poll_limit;
   bool expired = false;
 
-  const int64_t base = int64_t(blockIdx.x) * H;
+  const int64_t base = int64_t(blockIdx.x) * H + first;
   uint4 kept[kGatherPieces];
   float sq = 0.f;
 #pragma unroll
@@ -99,7 +115,7 @@ __global__ void __launch_bounds__(kGatherThreads) peer_reduce_add_rmsnorm_kernel
     const int unit = piece * kGatherThreads + threadIdx.x;
     const int i = unit * 8;
     kept[piece] = make_uint4(0u, 0u, 0u, 0u);
-    if (i < H) {
+    if (i < slice) {
       float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       for (int r = 0; r < world; ++r) {
         // the slot is written from outside this GPU: volatile loads, until both units carry the flag
@@ -133,46 +149,80 @@ __global__ void __launch_bounds__(kGatherThreads) peer_reduce_add_rmsnorm_kernel
       __half2* vh = reinterpret_cast<__half2*>(&value);
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const float2 a = __half22float2(vh[q]), b = __half22float2(dh[q]);
-        vh[q] = __floats2half2_rn(a.x + b.x, a.y + b.y);
+        const float2 x = __half22float2(vh[q]), y = __half22float2(dh[q]);
+        vh[q] = __floats2half2_rn(x.x + y.x, x.y + y.y);
       }
       *reinterpret_cast<uint4*>(residual + base + i) = value;
       kept[piece] = value;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const float2 a = __half22float2(vh[q]);
-        sq += a.x * a.x + a.y * a.y;
+        const float2 x = __half22float2(vh[q]);
+        sq += x.x * x.x + x.y * x.y;
       }
     }
   }
-  if (threadIdx.x == 0) mine->sent[m] = v;
-  if (expired) atomicExch(&mine->status, 1u);
+  if (threadIdx.x == 0) mine->sent[m][part] = v;
 #pragma unroll
   for (int offset = 16; offset; offset >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, offset);
   if ((threadIdx.x & 31) == 0) part_s[threadIdx.x >> 5] = sq;
   __syncthreads();
-  float total = 0.f;
-#pragma unroll
-  for (int w = 0; w < kGatherThreads / 32; ++w) total += part_s[w];
-  const float inv = rsqrtf(total / float(H) + eps);
+  if (threadIdx.x == 0) {
+    float total = 0.f;
+    for (int w = 0; w < int(blockDim.x) / 32; ++w) total += part_s[w];
+    if (split > 1) {
+      // the slices' sums meet in this rank's own header, as packets like the data; every CTA of the row adds
+      // them in slice order, so all of them normalise with the same bits
+      asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(&mine->squares[parity][m][part]),
+                   "r"(__float_as_uint(total)), "r"(v) : "memory");
+      total = 0.f;
+      for (int other = 0; other < split; ++other) {
+        const uint2* from = &mine->squares[parity][m][other];
+        uint2 got = load_volatile8(from);
+        uint32_t polls = 0;
+        while (got.y != v && polls < limit) {
+          got = load_volatile8(from);
+          ++polls;
+        }
+        if (got.y != v) {
+          expired = true;
+          limit = 0;
+          continue;
+        }
+        total += __uint_as_float(got.x);
+      }
+    }
+    total_s = total;
+  }
+  if (expired) atomicExch(&mine->status, 1u);
+  __syncthreads();
+  const float inv = rsqrtf(total_s / float(H) + eps);
 #pragma unroll
   for (int piece = 0; piece < kGatherPieces; ++piece) {
     const int i = (piece * kGatherThreads + threadIdx.x) * 8;
-    if (i < H) {
-      const uint4 w = *reinterpret_cast<const uint4*>(weight + i);
+    if (i < slice) {
+      const uint4 w = *reinterpret_cast<const uint4*>(weight + first + i);
       const __half2* vh = reinterpret_cast<const __half2*>(&kept[piece]);
       const __half2* wh = reinterpret_cast<const __half2*>(&w);
       uint4 result;
       __half2* rh = reinterpret_cast<__half2*>(&result);
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const float2 a = __half22float2(vh[q]), ww = __half22float2(wh[q]);
-        const float2 u = __half22float2(__floats2half2_rn(a.x * inv, a.y * inv));
+        const float2 x = __half22float2(vh[q]), ww = __half22float2(wh[q]);
+        const float2 u = __half22float2(__floats2half2_rn(x.x * inv, x.y * inv));
         rh[q] = __floats2half2_rn(u.x * ww.x, u.y * ww.y);
       }
       *reinterpret_cast<uint4*>(normed + base + i) = result;
     }
   }
+}
+
+// CTAs per row a caller fixed for a buffer (tests force the split path on small worlds); 0: automatic
+std::mutex g_split_lock;
+std::unordered_map<const void*, uint32_t> g_split;
+uint32_t split_of(const void* own) {
+  std::lock_guard<std::mutex> guard(g_split_lock);
+  const auto found = g_split.find(own);
+  return found == g_split.end() ? 0u : found->second;
 }
 
 template <typename... Params, typename... Args>
@@ -207,6 +257,15 @@ extern "C" int mkb_peer_set_poll_limit(void* own, int64_t polls) {
   return MKB_OK;
 }
 
+extern "C" int mkb_peer_set_split(void* own, int split) {
+  using namespace mkb;
+  MKB_REQUIRE(own != nullptr && split >= 0 && split <= kMaxSplit && (split & (split - 1)) == 0, MKB_E_ARGUMENT,
+              "peer_set_split: 0 (automatic) or a power of two up to %d", kMaxSplit);
+  std::lock_guard<std::mutex> guard(g_split_lock);
+  g_split[own] = uint32_t(split);
+  return MKB_OK;
+}
+
 extern "C" int mkb_peer_alloc(int64_t bytes, void** buffer) {
   using namespace mkb;
   MKB_REQUIRE(bytes > 0 && buffer != nullptr, MKB_E_ARGUMENT, "peer_alloc: bad arguments");
@@ -219,6 +278,10 @@ extern "C" int mkb_peer_alloc(int64_t bytes, void** buffer) {
 
 extern "C" int mkb_peer_free(void* buffer) {
   using namespace mkb;
+  {
+    std::lock_guard<std::mutex> guard(g_split_lock);
+    g_split.erase(buffer);
+  }
   const cudaError_t status = cudaFree(buffer);
   if (status != cudaSuccess) return cuda_fail(status, "peer_free");
   return MKB_OK;
@@ -263,8 +326,15 @@ extern "C" int mkb_peer_reduce_add_rmsnorm(const void* partial, void* const* pee
                 reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(normed) |
                 reinterpret_cast<uintptr_t>(reduced)) & 15) == 0,
               MKB_E_ARGUMENT, "peer_reduce_add_rmsnorm: pointers must be 16-byte aligned");
+  // CTAs per row: wide worlds push more bytes than one SM moves quickly (the header may fix the number)
+  const uint32_t wanted = split_of(own);
+  int split = wanted ? int(wanted) : world >= 8 ? 4 : world >= 4 ? 2 : 1;
+  while (split > 1 && (H % (split * 8) != 0 || H / split < 256)) split >>= 1;
+  const int slice = H / split;
+  int threads = (slice / 8 + 31) / 32 * 32;
+  if (threads > kGatherThreads) threads = kGatherThreads;
   const cudaError_t launched = launch_dependent(
-      peer_reduce_add_rmsnorm_kernel, dim3(M), dim3(kGatherThreads), stream, static_cast<const __half*>(partial), peers,
+      peer_reduce_add_rmsnorm_kernel, dim3(M, split), dim3(threads), stream, static_cast<const __half*>(partial), peers,
       own, static_cast<__half*>(residual), static_cast<const __half*>(weight), static_cast<__half*>(normed),
       static_cast<__half*>(reduced), H, world, rank, int64_t(rows) * (H / 4), eps);
   if (launched != cudaSuccess) return cuda_fail(launched, "peer_reduce_add_rmsnorm launch");

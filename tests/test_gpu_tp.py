@@ -308,6 +308,11 @@ class LocalExchange:
 
         _native.check(self.lib.mkb_peer_set_poll_limit(self.buffers[rank], polls), "peer_set_poll_limit")
 
+    def split(self, rank, parts):
+        from mlkit_b200 import _native
+
+        _native.check(self.lib.mkb_peer_set_split(self.buffers[rank], parts), "peer_set_split")
+
     def close(self):
         torch.cuda.synchronize()
         for buffer in self.buffers:
@@ -404,6 +409,57 @@ def test_peer_reduction_wait_runs_out_without_hanging():
     stop.record()
     torch.cuda.synchronize()
     assert start.elapsed_time(stop) < 50 and exchange.status(0) == 1
+    exchange.close()
+
+
+@pytest.mark.parametrize("parts", [2, 4])
+@pytest.mark.parametrize("rows_in", [1, 8])
+def test_peer_reduction_with_a_row_split_over_several_ctas(rows_in, parts):
+    """Wide worlds split a row over several CTAs (each pushes its slice; the slices' sums of squares meet
+    through the rank's own header).  Forced here on two ranks run in turn, eager and from a CUDA graph: sum
+    and residual are bit-equal to the one-CTA result, the norm agrees to the last bits (its sum of squares
+    is added in another order), and a width the split does not divide falls back to fewer CTAs."""
+    torch.manual_seed(40 + rows_in + parts)
+    for width in (8192, 2056):
+        exchange = LocalExchange(2, 8, width)
+        exchange.limit(1, 1000)
+        for rank in (0, 1):
+            exchange.split(rank, parts)
+        weight = (torch.rand(width, device="cuda") + 0.5).half()
+        residual = torch.randn(rows_in, width, device="cuda").half()
+        expected_residual, scratch_residual = residual.clone(), torch.zeros_like(residual)
+        for _ in range(3):
+            partials = [torch.randn(rows_in, width, device="cuda").half() for _ in range(2)]
+            exchange.reduce(1, partials[1], scratch_residual, weight)
+            reduced, normed = exchange.reduce(0, partials[0], residual, weight)
+            total16 = (partials[0].float() + partials[1].float()).half()
+            expected_residual, expected_normed = reference_add_rmsnorm(total16, expected_residual, weight)
+            assert torch.equal(reduced, total16) and torch.equal(residual, expected_residual)
+            assert rel(normed, expected_normed) < 1e-3 and (normed.float() - expected_normed.float()).abs().max() < 0.02
+        assert exchange.status(0) == 0 and exchange.status(1) == 1
+        exchange.close()
+    # one rank alone, replayed from a graph: the per-CTA counters and both parities
+    width = 4096
+    exchange = LocalExchange(1, 8, width)
+    exchange.split(0, parts)
+    weight = (torch.rand(width, device="cuda") + 0.5).half()
+    residual, expected_residual = torch.zeros(rows_in, width, device="cuda").half(), torch.zeros(rows_in, width, device="cuda").half()
+    partial = torch.randn(rows_in, width, device="cuda").half()
+    exchange.reduce(0, partial, residual, weight)
+    expected_residual, _ = reference_add_rmsnorm(partial, expected_residual, weight)
+    graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            reduced, normed = exchange.reduce(0, partial, residual, weight)
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(3):
+        graph.replay()
+        torch.cuda.synchronize()
+        expected_residual, expected_normed = reference_add_rmsnorm(partial, expected_residual, weight)
+        assert torch.equal(reduced, partial) and torch.equal(residual, expected_residual)
+        assert rel(normed, expected_normed) < 1e-3
+    assert exchange.status(0) == 0
     exchange.close()
 
 
