@@ -17,6 +17,7 @@ Sharding happens when the model is built; nothing sharded is ever written to a c
 """
 
 import math
+import os
 from dataclasses import dataclass
 
 import torch
@@ -208,6 +209,9 @@ class PeerExchange:
                 _native.check(library.mkb_peer_alloc(size, ctypes.byref(own)), "peer_alloc")
                 self.own = own.value
                 _native.check(library.mkb_peer_export(self.own, handle), "peer_export")
+                parts = int(os.environ.get("MLKIT_B200_PEER_SPLIT", "0"))   # CTAs per row; 0: from the world size
+                if parts:
+                    _native.check(library.mkb_peer_set_split(self.own, parts), "peer_set_split")
             except Exception as error:  # reported to all ranks below
                 problem = repr(error)
             agreed(problem, "allocating and exporting the buffer")
