@@ -337,8 +337,8 @@ int mkb_peer_status(const void* own, int* status);
  * ranks are separate processes and may be seconds apart).  Synchronous; call it outside captures. */
 int mkb_peer_set_poll_limit(void* own, int64_t polls);
 /* CTAs that share one row of a reduction on this buffer: 0 (default) lets the call choose from the world size
- * and the rows (1 up to three ranks; up to 4 from four ranks on: one SM sustains only a few tens of GB/s of remote
- * stores),
+ * and the rows (up to 4: one SM sustains only a few tens of GB/s of remote stores, so a launch aims at about four
+ * pushing CTAs, more with eight ranks),
  * a power of two up to 8 fixes it.  Host-side state of the library, kept until mkb_peer_free. */
 int mkb_peer_set_split(void* own, int split);
 

@@ -328,9 +328,16 @@ extern "C" int mkb_peer_reduce_add_rmsnorm(const void* partial, void* const* pee
               MKB_E_ARGUMENT, "peer_reduce_add_rmsnorm: pointers must be 16-byte aligned");
   // CTAs per row: wide worlds push more bytes than one SM moves quickly (the header may fix the number)
   const uint32_t wanted = split_of(own);
-  // measured (70B-shaped decode, H = 8192): 4 ranks, one row: 186 / 190 / 194 / 190 tokens/s with 1 / 2 / 4 / 8 CTAs
-  // per row, eight rows: best with one; 8 ranks: four CTAs per row ahead at one row and at eight
-  int split = wanted ? int(wanted) : world >= 8 ? 4 : world >= 4 ? (M <= 2 ? 4 : M <= 4 ? 2 : 1) : 1;
+  // measured (70B-shaped decode, H = 8192, tokens/s with 1 / 2 / 4 / 8 CTAs per row): 2 ranks, one row: 152 / 155 /
+  // 155 / -, eight rows: 1117 / 1119 / 1101 / -; 4 ranks, one row: 186 / 190 / 194 / 190, eight rows best with
+  // one; 8 ranks: four CTAs per row ahead of one at one row (205 against 179) and at eight rows.  So: about four
+  // pushing CTAs per launch, thirty-two when eight ranks make every row a 256 KB push.
+  int split = int(wanted);
+  if (split == 0) {
+    const int budget = world >= 8 ? 32 : world >= 2 ? 4 : 1;   // a single rank pushes nothing over NVLink
+    split = 1;
+    while (split < 4 && 2 * split * M <= budget) split *= 2;
+  }
   while (split > 1 && (H % (split * 8) != 0 || H / split < 256)) split >>= 1;
   const int slice = H / split;
   int threads = (slice / 8 + 31) / 32 * 32;
