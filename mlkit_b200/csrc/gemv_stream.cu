@@ -171,7 +171,9 @@ __host__ __device__ constexpr uint32_t tile_offset(int tile, int row, int vector
   return uint32_t(tile) * (256u * BITS) + uint32_t(row) * (16u * BITS) + uint32_t(vector) * 16u;
 }
 
-template <int BITS, int MODE, int GPT, int KT, int R>
+// ROTATE: the instance that transforms its activations on load; the plain instance carries none of that code
+// (with the rotation a run-time branch of one kernel the plain matvec measured 4-7 % slower)
+template <int BITS, int MODE, int GPT, int KT, int R, bool ROTATE>
 __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const StreamArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
   using V = Visit<BITS, MODE, GPT, KT>;
@@ -261,8 +263,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
 
   // ---- activations: the B fragments of this warp's k-tiles, permuted in registers ----
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  float* rotated = reinterpret_cast<float*>(smem + a.rot_offset);   // [M][K] when the rotation is on
-  if (a.rot_log2) {
+  [[maybe_unused]] float* rotated = reinterpret_cast<float*>(smem + a.rot_offset);   // [M][K] when the rotation is on
+  if constexpr (ROTATE) {
     // nine stages per 512 values in a warp's registers, the rest in shared memory, three stages per pass
     const int front = a.rot_log2 < kWarpBits ? a.rot_log2 : kWarpBits;
     const int chunks_per_row = a.K / kWarpSpan;
@@ -327,7 +329,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
         v[kk][w] = make_uint4(0u, 0u, 0u, 0u);
-        if (has_x && a.rot_log2) {
+        if (ROTATE && has_x) {
           const float* from = rotated + g * a.K + tile0 * 128 + t * 32 + kk * 128 + w * 8;
           const float4 lo = *reinterpret_cast<const float4*>(from), hi = *reinterpret_cast<const float4*>(from + 4);
           const __half2 h0 = __floats2half2_rn(lo.x, lo.y), h1 = __floats2half2_rn(lo.z, lo.w);
@@ -691,7 +693,7 @@ bool plan_stream(int M, int N, int K, int sm_count, int max_smem, int cluster_ca
 
 template <int BITS, int MODE, int GPT, int KT, int R>
 int launch_stream(const StreamArgs& a, const StreamPlan& p, cudaStream_t stream, int* cluster_cap) {
-  auto kernel = gemv_stream_kernel<BITS, MODE, GPT, KT, R>;
+  auto kernel = a.rot_log2 ? gemv_stream_kernel<BITS, MODE, GPT, KT, R, true> : gemv_stream_kernel<BITS, MODE, GPT, KT, R, false>;
   int status = opt_in_shared(kernel);
   if (status != MKB_OK) return status;
   cudaLaunchConfig_t config{};
