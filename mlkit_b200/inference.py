@@ -512,6 +512,7 @@ class CapturedCall:
         self.entries: dict[tuple, dict[str, Any]] = {}
         self.device = next((t.device for t in _module_tensors(function) if t.is_cuda), None)
         self._last: torch.cuda.Event | None = None
+        self._by_identity: dict[tuple[int, ...], dict[str, Any]] = {}
 
     MAXIMUM_PINNED_CAPTURES = 32   # distinct pinned input tensors that get a graph of their own
 
@@ -581,10 +582,27 @@ class CapturedCall:
             self._last.synchronize()
 
     def __call__(self, *inputs: Tensor) -> Any:
+        # the same pinned tensors again (the steady state of a serving loop): no signature to compute, nothing to
+        # copy on the host; the entry keeps those tensors alive, so the identities cannot be reused
+        identity = tuple(map(id, inputs))
+        entry = self._by_identity.get(identity)
+        if entry is not None and all(given is source and given.shape == static.shape
+                                     for given, source, static in zip(inputs, entry["sources"], entry["statics"])):
+            entry["graph"].replay()
+            if entry["to_host"]:
+                self._last.record()
+                if self.synchronize:
+                    self._last.synchronize()
+            return entry["results"][0] if entry["single"] else entry["tuple"]
         signature = self._signature(inputs)
         entry = self.entries.get(signature)
         if entry is None:
             entry = self.entries[signature] = self._capture(inputs, signature)
+            entry["tuple"] = tuple(entry["results"])
+            if self._last is None:
+                self._last = torch.cuda.Event()
+            if inputs and all(source is given for source, given in zip(entry["sources"], inputs)):
+                self._by_identity[identity] = entry      # every input is a pinned tensor read in place
         for static, source, given in zip(entry["statics"], entry["sources"], inputs):
             if source is None:
                 static.copy_(given, non_blocking=True)
@@ -598,8 +616,7 @@ class CapturedCall:
             self._last.record()
             if self.synchronize:
                 self._last.synchronize()
-        results = entry["results"]
-        return results[0] if entry["single"] else tuple(results)
+        return entry["results"][0] if entry["single"] else entry["tuple"]
 
 
 def _module_tensors(function: Any):
