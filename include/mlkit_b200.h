@@ -286,7 +286,9 @@ int mkb_attention_decode(const void* qkv, const int* positions, const void* k_ca
 /* mkb_rope_append and mkb_attention_decode in one launch, for at most 8 query heads per key-value
  * head and head_dim 128: every CTA rotates the new key of its key-value head, appends key and value
  * to the caches at positions[m], rotates its query heads in registers (qkv itself is left
- * unrotated) and attends over positions 0..positions[m]. */
+ * unrotated) and attends over positions 0..positions[m].  `positions` is read before the kernel waits for
+ * its predecessor in the stream (the rotation table is formed meanwhile), so it must not be written by the
+ * kernel launched immediately before this call; the same holds for mkb_attention_decode. */
 int mkb_rope_attention_decode(const void* qkv, const int* positions, void* k_cache, void* v_cache, void* out,
                               int M, int q_heads, int kv_heads, int head_dim, int capacity, float theta,
                               float scale, void* stream);

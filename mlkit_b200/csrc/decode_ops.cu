@@ -319,49 +319,46 @@ __global__ void __launch_bounds__(kGroupThreads) attention_group_kernel(const __
                                                                  const __half* __restrict__ v_cache, __half* __restrict__ out,
                                                                  int q_heads, int kv_heads, int capacity, float scale,
                                                                  float theta, int fuse_rope) {
-  // programmatic dependent launch: let the next kernel in the stream become resident now, then wait
-  // for everything this kernel reads
+  // programmatic dependent launch: let the next kernel in the stream become resident now
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   constexpr int D = 128;
   extern __shared__ __align__(16) uint8_t smem[];
   const int m = blockIdx.x, kv = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int G = q_heads / kv_heads;               // <= 8: rows g of the tiles; rows g + 8 are padding
+  // the positions are an input of the step, not a product of the kernel before this one: they are read,
+  // and the rotation table is formed (powf and a large-argument sincosf: about a microsecond), before
+  // the wait for the kernel that produces the queries, keys and values
   bool in_cache;
   const int length = checked_position(positions[m], capacity, in_cache) + 1;
+  __shared__ float cos_s[D / 2], sin_s[D / 2];
+  if (fuse_rope && threadIdx.x < D / 2) {
+    const float freq = powf(theta, -2.f * float(threadIdx.x) / float(D));
+    sincosf(float(length - 1) * freq, &sin_s[threadIdx.x], &cos_s[threadIdx.x]);
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int row = (q_heads + 2 * kv_heads) * D;
   const __half* keys = k_cache + (int64_t(m) * kv_heads + kv) * capacity * D;
   const __half* values = v_cache + (int64_t(m) * kv_heads + kv) * capacity * D;
   uint8_t* k_tile = smem + warp * 2 * kTileBytes;
   uint8_t* v_tile = k_tile + kTileBytes;
-  __shared__ float cos_s[D / 2], sin_s[D / 2];
   if (fuse_rope) {
     // rotary embedding fused in: this CTA rotates the new key of its head and appends key and value
-    // to the caches itself (nobody else reads that slot), and rotates its query heads in registers
+    // to the caches itself (nobody else reads that slot), and rotates its query heads in registers;
+    // nothing is appended for a position outside the cache
     const int position = length - 1;
-    if (!in_cache) {
-      // nothing is appended for a position outside the cache; the rotation tables are still filled
-      if (threadIdx.x < D / 2) {
-        const float freq = powf(theta, -2.f * float(threadIdx.x) / float(D));
-        sincosf(float(position) * freq, &sin_s[threadIdx.x], &cos_s[threadIdx.x]);
-      }
-    } else if (threadIdx.x < D / 2) {
-      const float freq = powf(theta, -2.f * float(threadIdx.x) / float(D));
-      float sine, cosine;
-      sincosf(float(position) * freq, &sine, &cosine);
-      cos_s[threadIdx.x] = cosine;
-      sin_s[threadIdx.x] = sine;
+    if (in_cache && threadIdx.x < D / 2) {
+      const float cosine = cos_s[threadIdx.x], sine = sin_s[threadIdx.x];   // written by this same thread
       const __half* k = qkv + int64_t(m) * row + int64_t(q_heads + kv) * D;
       const float a = __half2float(k[threadIdx.x]), b = __half2float(k[threadIdx.x + D / 2]);
       __half* slot = const_cast<__half*>(keys) + int64_t(position) * D;
       slot[threadIdx.x] = __float2half_rn(a * cosine - b * sine);
       slot[threadIdx.x + D / 2] = __float2half_rn(b * cosine + a * sine);
-    } else if (threadIdx.x < D / 2 + D) {
+    } else if (in_cache && threadIdx.x < D / 2 + D) {
       const int i = threadIdx.x - D / 2;
       const_cast<__half*>(values)[int64_t(position) * D + i] = qkv[int64_t(m) * row + int64_t(q_heads + kv_heads + kv) * D + i];
     }
-    __threadfence();
+    // the appended row is read back by this CTA only: the barrier orders the stores for its own threads
     __syncthreads();
   }
 
