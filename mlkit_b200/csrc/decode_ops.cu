@@ -31,6 +31,13 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__half* __res
   // programmatic dependent launch: let the next kernel in the stream become resident now (a matvec
   // starts streaming its weights), then wait for everything this kernel reads
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // the norm weights are constants of the model: fetched before the wait, they cost no latency after the sum
+  uint4 scale_of[kNormPieces];
+#pragma unroll
+  for (int piece = 0; piece < kNormPieces; ++piece) {
+    const int i = (piece * kNormThreads + threadIdx.x) * 8;
+    scale_of[piece] = i < H ? __ldg(reinterpret_cast<const uint4*>(weight + i)) : make_uint4(0u, 0u, 0u, 0u);
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ float part_s[kNormThreads / 32];
   const int64_t base = int64_t(blockIdx.x) * H;
@@ -74,9 +81,8 @@ __global__ void __launch_bounds__(kNormThreads) add_rmsnorm_kernel(__half* __res
   for (int piece = 0; piece < kNormPieces; ++piece) {
     const int i = (piece * kNormThreads + threadIdx.x) * 8;
     if (i < H) {
-      const uint4 w = *reinterpret_cast<const uint4*>(weight + i);
       const __half2* vh = reinterpret_cast<const __half2*>(&kept[piece]);
-      const __half2* wh = reinterpret_cast<const __half2*>(&w);
+      const __half2* wh = reinterpret_cast<const __half2*>(&scale_of[piece]);
       uint4 result;
       __half2* rh = reinterpret_cast<__half2*>(&result);
 #pragma unroll

@@ -72,12 +72,19 @@ __global__ void __launch_bounds__(kGatherThreads) peer_reduce_add_rmsnorm_kernel
     const __half* __restrict__ weight, __half* __restrict__ normed, __half* __restrict__ reduced, int H, int world,
     int rank, int64_t slot_units, float eps) {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   __shared__ float part_s[kGatherThreads / 32];
   __shared__ float total_s;
   Header* mine = static_cast<Header*>(own);
   const int m = blockIdx.x, split = gridDim.y, part = blockIdx.y;
   const int slice = H / split, first = part * slice;       // this CTA's elements of the row
+  // the norm weights are constants of the model: fetched before the wait, they cost no latency after the sum
+  uint4 scale_of[kGatherPieces];
+#pragma unroll
+  for (int piece = 0; piece < kGatherPieces; ++piece) {
+    const int i = (piece * kGatherThreads + threadIdx.x) * 8;
+    scale_of[piece] = i < slice ? __ldg(reinterpret_cast<const uint4*>(weight + first + i)) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const uint32_t v = mine->sent[m][part] + 1;   // only this CTA touches sent[m][part]
   const int parity = int(v & 1u);
   const int64_t row_units = int64_t(m) * (H / 4) + first / 4;   // 16-byte units of the slice inside a slot
@@ -200,9 +207,8 @@ __global__ void __launch_bounds__(kGatherThreads) peer_reduce_add_rmsnorm_kernel
   for (int piece = 0; piece < kGatherPieces; ++piece) {
     const int i = (piece * kGatherThreads + threadIdx.x) * 8;
     if (i < slice) {
-      const uint4 w = *reinterpret_cast<const uint4*>(weight + first + i);
       const __half2* vh = reinterpret_cast<const __half2*>(&kept[piece]);
-      const __half2* wh = reinterpret_cast<const __half2*>(&w);
+      const __half2* wh = reinterpret_cast<const __half2*>(&scale_of[piece]);
       uint4 result;
       __half2* rh = reinterpret_cast<__half2*>(&result);
 #pragma unroll
