@@ -84,8 +84,12 @@ __global__ void __launch_bounds__(kGatherThreads) peer_reduce_add_rmsnorm_kernel
     const int i = (piece * kGatherThreads + threadIdx.x) * 8;
     scale_of[piece] = i < slice ? __ldg(reinterpret_cast<const uint4*>(weight + first + i)) : make_uint4(0u, 0u, 0u, 0u);
   }
+  // (nothing of the header is read before the wait: the reduction launched just before this one may be the one
+  // that writes this CTA's counter, and with the status and the poll limit read early the two-GPU decode test
+  // failed)
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  const uint32_t v = mine->sent[m][part] + 1;   // only this CTA touches sent[m][part]
+  const uint32_t first_limit = mine->status != 0 ? 0u : mine->poll_limit;
+  const uint32_t v = mine->sent[m][part] + 1;   // only CTA (m, part) of a reduction touches sent[m][part]
   const int parity = int(v & 1u);
   const int64_t row_units = int64_t(m) * (H / 4) + first / 4;   // 16-byte units of the slice inside a slot
   {
@@ -111,7 +115,7 @@ __global__ void __launch_bounds__(kGatherThreads) peer_reduce_add_rmsnorm_kernel
   }
   // a wait that expired once is not repeated: every later reduction of a broken exchange would otherwise
   // add its own timeout
-  uint32_t limit = mine->status != 0 ? 0u : mine->poll_limit;
+  uint32_t limit = first_limit;
   bool expired = false;
 
   const int64_t base = int64_t(blockIdx.x) * H + first;
