@@ -527,3 +527,20 @@ def test_rotated_packed_linear_fuses_the_rotation_for_few_rows():
     assert calls == [1, 2]             # 2 x 2048 x 4 B = 16 KB is the limit; nothing fused after the later hook
     assert all(torch.equal(a, b) for a, b in zip(fused, separate))
     assert torch.equal(after, separate[0])
+
+
+def test_captured_call_bounds_its_graphs_per_pinned_address():
+    """A pinned input is read in place, so its address keys a graph of its own; a caller that brings a new pinned
+    tensor every time must not grow one graph per call: past the bound such inputs are staged like pageable ones."""
+    linear = torch.nn.Linear(256, 128, bias=False).half().cuda()
+    call = mk.capture(linear)
+    call.MAXIMUM_PINNED_CAPTURES = 4
+    with torch.inference_mode():
+        for trial in range(10):
+            x = torch.randn(2, 256, device="cpu").half().pin_memory()
+            assert torch.equal(call(x), linear(x.cuda()).cpu())
+    assert len(call.entries) == 5          # four graphs keyed by address, then one staged graph for the shape
+    again = torch.randn(2, 256, device="cpu").half().pin_memory()
+    with torch.inference_mode():
+        assert torch.equal(call(again), linear(again.cuda()).cpu()) and torch.equal(call(again), linear(again.cuda()).cpu())
+    assert len(call.entries) == 5
