@@ -199,3 +199,45 @@ def test_library_exports_every_declared_symbol():
     status = _native.library().mkb_gemv_ex(None, None, None, None, None, None, None, 9, 1, 128, 128, 4, 16, 0, 0,
                                            64, 1, 0, 0.0, 0, None)
     assert status == -2 and b"outside 1..8" in _native.library().mkb_last_error()
+
+
+def test_size_queries_need_no_gpu():
+    library = _native.library()
+    assert library.mkb_gemm_workspace_bytes(64, 14336, 4096) > 0
+    assert library.mkb_gemm_workspace_bytes(129, 14336, 4096) == 0      # more rows than one launch takes
+    assert library.mkb_gemm_workspace_bytes(64, 14336, 4100) == 0       # K not a multiple of the group
+    # flagged packets: four bytes of flags per four bytes of data, two parities, behind a fixed header
+    small, large = library.mkb_peer_buffer_bytes(1, 8192, 8), library.mkb_peer_buffer_bytes(8, 8192, 8)
+    assert small > 0 and large - small == 2 * 8 * 7 * 8192 * 4
+    assert library.mkb_peer_buffer_bytes(9, 8192, 8) == 0 and library.mkb_peer_buffer_bytes(8, 8192, 17) == 0
+    assert library.mkb_gemv_static_scratch_bytes() == 8 << 20
+    assert library.mkb_gemv_workspace_bytes(8, 14336, 4096, 4) > 0
+
+
+def test_route_rules_of_the_wrappers():
+    from mlkit_b200 import kernels
+
+    scales = torch.empty(0, dtype=torch.float16)
+    layer = dict(width=4096, group=128, bits=4, dtype=torch.float16, scales=scales, zeros=None, integer_grid=True,
+                 grid_minimum=-8.0, levels=16)
+    assert kernels.gemm_supported(17, **layer) and kernels.gemm_supported(128, **layer)
+    assert not kernels.gemm_supported(129, **layer)
+    assert not kernels.gemm_supported(17, **{**layer, "bits": 3})
+    assert not kernels.gemm_supported(17, **{**layer, "group": 64})
+    assert not kernels.gemm_supported(17, **{**layer, "dtype": torch.bfloat16})
+    assert not kernels.gemm_supported(17, **{**layer, "zeros": scales})
+    assert not kernels.gemm_supported(17, **{**layer, "grid_minimum": 0.0})
+    # profitable against reconstruct + library GEMM: always up to 32 rows, above that for large weights only
+    assert kernels.gemm_supported(32, outputs=1024, **layer)
+    assert not kernels.gemm_supported(64, outputs=1024, **layer)
+    assert kernels.gemm_supported(64, outputs=8192, **layer)
+    # rotation on load: power-of-two widths of at least one warp's span, activations that fit shared memory
+    assert kernels.rotated_matvec_supported(1, 4096, torch.float16)
+    assert kernels.rotated_matvec_supported(4, 4096, torch.float16)
+    assert not kernels.rotated_matvec_supported(4, 4096, torch.float16, profitable=True)
+    assert kernels.rotated_matvec_supported(1, 4096, torch.float16, profitable=True)
+    assert not kernels.rotated_matvec_supported(1, 14336, torch.float16)      # factor width
+    assert not kernels.rotated_matvec_supported(1, 256, torch.float16)
+    assert not kernels.rotated_matvec_supported(8, 4096, torch.float16)       # 128 KB of fp32 activations
+    assert not kernels.rotated_matvec_supported(1, 4096, torch.bfloat16)
+    assert not kernels.rotated_matvec_supported(9, 512, torch.float16)
