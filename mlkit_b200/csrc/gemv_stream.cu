@@ -101,7 +101,7 @@ __device__ __forceinline__ void mma_next(float (&d)[4], uint32_t a0, uint32_t a1
 }
 
 // How codes become tensor-core operands.
-//   RAW   integer grids (lut[c] = min + c) of 2, 4 or 8 bits with one scale per 128 codes: masked bits
+//   RAW   integer grids (lut[c] = min + c) of 2, 3, 4 or 8 bits with one scale per 128 codes: masked bits
 //         used as fp16 subnormals (see the head of this file); the scale multiplies the k-tile sum.
 //   TABLE any table of at most 16 levels with 3- or 4-bit codes and one scale per 64 or 128 codes: a
 //         pair of neighbouring codes indexes a shared-memory table of fp16 pairs (one copy per lane,
@@ -127,10 +127,10 @@ struct Visit {
   static constexpr int SCALE_ROW_BYTES = KT * GPT * 2 < 4 ? 4 : KT * GPT * 2;
   static constexpr int SCALE_OFFSET = KT * TILE_BYTES;
   static constexpr int SLOT_BYTES = KT * TILE_BYTES + 16 * SCALE_ROW_BYTES;
-  [[maybe_unused]] static constexpr int CLASSES = MODE == MODE_RAW ? (BITS == 4 ? 2 : BITS == 2 ? 4 : 1) : 1;
+  [[maybe_unused]] static constexpr int CLASSES = MODE == MODE_RAW ? (BITS == 4 ? 2 : BITS == 2 ? 4 : BITS == 3 ? 8 : 1) : 1;
   [[maybe_unused]] static constexpr int TABLE_ENTRIES = MODE == MODE_TABLE ? (1 << (2 * BITS)) : 0;   // pairs of codes
   static_assert(SEGMENT % 16 == 0 && SLOT_BYTES % 16 == 0, "visit geometry");
-  static_assert(MODE == MODE_TABLE ? (BITS == 3 || BITS == 4) : (BITS == 2 || BITS == 4 || BITS == 8), "codec");
+  static_assert(MODE == MODE_TABLE ? (BITS == 3 || BITS == 4) : (BITS == 2 || BITS == 3 || BITS == 4 || BITS == 8), "codec");
 };
 
 __device__ __forceinline__ uint4 load_shared16(uint32_t address) {
@@ -380,6 +380,15 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
             b[kk][2 * (4 * word + i) + 0] = __byte_perm(r[8 * word + i / 2], r[8 * word + i / 2 + 4], selector);
             b[kk][2 * (4 * word + i) + 1] = __byte_perm(r[8 * word + i / 2 + 2], r[8 * word + i / 2 + 6], selector);
           }
+      } else if constexpr (RAW && BITS == 3) {
+        // step c takes codes (c, c + 16) and (c + 8, c + 24) of the lane's 32: the halves of a lane's 96 bits
+        // repeat each other's bit positions, so one mask keeps a code of each
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint32_t selector = (c & 1) ? 0x7632 : 0x5410;
+          b[kk][2 * c + 0] = __byte_perm(r[c / 2], r[c / 2 + 8], selector);
+          b[kk][2 * c + 1] = __byte_perm(r[c / 2 + 4], r[c / 2 + 12], selector);
+        }
       } else {
 #pragma unroll
         for (int j = 0; j < 16; ++j) b[kk][j] = r[j];   // neighbouring codes pair up: the natural order
@@ -446,6 +455,44 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
           if (step == 0) mma_first(acc[0], a0, a1, a2, a3, b[kk][0], b[kk][1], start[kk][0], start[kk][1], start[kk][2], start[kk][3]);
           else mma_next(acc[0], a0, a1, a2, a3, b[kk][2 * step], b[kk][2 * step + 1]);
         }
+      } else if constexpr (BITS == 3) {
+        // A lane's 32 codes of a row are 12 bytes B0..B11; code c sits at bit 3 c and code c + 16 exactly 48
+        // bits later.  Four registers pair a 16-bit window of the first half with the same window of the
+        // second; in each, and in its copy moved down one byte, whole codes sit at bit offsets 0..7 of both
+        // halves: offset o is the lift 2^o, with an accumulator of its own (eight classes, one step each).
+        const uint32_t at0 = slot_at + tile_offset<3>(kk, g, 0) + t * 12, at1 = slot_at + tile_offset<3>(kk, g + 8, 0) + t * 12;
+        uint32_t q[4], p[4];
+        auto windows = [](uint32_t at, uint32_t (&r)[4]) {
+          const uint32_t w0 = load_shared4(at), w1 = load_shared4(at + 4), w2 = load_shared4(at + 8);
+          const uint32_t u = __funnelshift_r(w0, w1, 16), v = __funnelshift_r(w1, w2, 16);   // B2..B5, B6..B9
+          r[0] = __byte_perm(w0, v, 0x5410);   // B0 B1 | B6 B7:   codes 0 1 2 at offsets 0 3 6, codes 3 4 at 9 12
+          r[1] = __byte_perm(w0, v, 0x6521);   // B1 B2 | B7 B8:   code 5 at 7, codes 6 7 at 10 13
+          r[2] = __byte_perm(u, w2, 0x6521);   // B3 B4 | B9 B10:  codes 8 9 10 at 0 3 6, codes 11 12 at 9 12
+          r[3] = __byte_perm(u, w2, 0x7632);   // B4 B5 | B10 B11: code 13 at 7, codes 14 15 at 10 13
+        };
+        windows(at0, q);
+        windows(at1, p);
+        // class (bit offset) of step c, and where its two pairs of codes come from
+        auto step = [&](auto code, auto offset, uint32_t x0, uint32_t x1, uint32_t y0, uint32_t y1) {
+          constexpr int c = decltype(code)::value, o = decltype(offset)::value;
+          constexpr uint32_t mask = 0x00070007u << o;
+          if constexpr (o == 0)
+            mma_first(acc[o], x0 & mask, x1 & mask, y0 & mask, y1 & mask, b[kk][2 * c], b[kk][2 * c + 1],
+                      start[kk][0], start[kk][1], start[kk][2], start[kk][3]);
+          else
+            mma_first(acc[o], x0 & mask, x1 & mask, y0 & mask, y1 & mask, b[kk][2 * c], b[kk][2 * c + 1], 0.f, 0.f, 0.f, 0.f);
+        };
+        using std::integral_constant;
+        const uint32_t q0 = q[0] >> 8, p0 = p[0] >> 8, q1 = q[1] >> 8, p1 = p[1] >> 8;
+        const uint32_t q2 = q[2] >> 8, p2 = p[2] >> 8, q3 = q[3] >> 8, p3 = p[3] >> 8;
+        step(integral_constant<int, 0>{}, integral_constant<int, 0>{}, q[0], p[0], q[2], p[2]);
+        step(integral_constant<int, 1>{}, integral_constant<int, 3>{}, q[0], p[0], q[2], p[2]);
+        step(integral_constant<int, 2>{}, integral_constant<int, 6>{}, q[0], p[0], q[2], p[2]);
+        step(integral_constant<int, 3>{}, integral_constant<int, 1>{}, q0, p0, q2, p2);
+        step(integral_constant<int, 4>{}, integral_constant<int, 4>{}, q0, p0, q2, p2);
+        step(integral_constant<int, 5>{}, integral_constant<int, 7>{}, q[1], p[1], q[3], p[3]);
+        step(integral_constant<int, 6>{}, integral_constant<int, 2>{}, q1, p1, q3, p3);
+        step(integral_constant<int, 7>{}, integral_constant<int, 5>{}, q1, p1, q3, p3);
       } else {  // BITS == 2: codes of equal position in their byte share a lift of 4^i and an accumulator
         const uint2 lo = load_shared8(slot_at + tile_offset<2>(kk, g, 0) + t * 8), hi = load_shared8(slot_at + tile_offset<2>(kk, g + 8, 0) + t * 8);
         const uint32_t q[2] = {lo.x, lo.y}, p[2] = {hi.x, hi.y};
@@ -469,7 +516,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
       }
       // classes of higher lift were c * 2^-24 times a power of two: recombine exactly (Horner), then one
       // scale per row and k-tile
-      constexpr float down = BITS == 4 ? 0.0625f : 0.25f;
+      constexpr float down = BITS == 4 ? 0.0625f : BITS == 3 ? 0.5f : 0.25f;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         float total = acc[V::CLASSES - 1][q];
@@ -753,6 +800,7 @@ int dispatch_stream(const StreamArgs& a, const StreamPlan& p, cudaStream_t strea
   if (p.mode == MODE_RAW) {
     if (p.bits == 4) return dispatch_shape<4, MODE_RAW, 1>(a, p, stream, cluster_cap);
     if (p.bits == 2) return dispatch_shape<2, MODE_RAW, 1>(a, p, stream, cluster_cap);
+    if (p.bits == 3) return dispatch_shape<3, MODE_RAW, 1>(a, p, stream, cluster_cap);
     return dispatch_shape<8, MODE_RAW, 1>(a, p, stream, cluster_cap);
   }
   if (p.bits == 4) return p.gpt == 1 ? dispatch_shape<4, MODE_TABLE, 1>(a, p, stream, cluster_cap)
@@ -766,7 +814,7 @@ bool codec_of(int group, int bits, int lut_len, const void* zeros, int integer_g
   if (zeros != nullptr || lut_len < 1 || lut_len > (1 << bits)) return false;
   const bool ramp = integer_grid && lut_len == (1 << bits) && grid_minimum == float(int(grid_minimum)) &&
                     grid_minimum >= -512.f && grid_minimum <= 512.f;
-  if (ramp && group == 128 && (bits == 2 || bits == 4 || bits == 8)) {
+  if (ramp && group == 128 && (bits == 2 || bits == 3 || bits == 4 || bits == 8)) {
     p.bits = bits; p.mode = MODE_RAW; p.gpt = 1;
     return true;
   }
