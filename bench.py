@@ -292,7 +292,9 @@ def codec_table(device, peak: float) -> dict:
     codebook = torch.tensor([-1, -0.5, -0.25, 0, 0.25, 0.5, 1.0])
     formats = {
         "int2_g128": (mk.int(2, group=128), 2, 128, 4), "int3_g128": (mk.int(3, group=128), 3, 128, 8),
-        "int4_g128": (mk.int(4, group=128), 4, 128, 16), "int8_g128": (mk.int(8, group=128), 8, 128, 256),
+        "int4_g128": (mk.int(4, group=128), 4, 128, 16), "int5_g128": (mk.int(5, group=128), 5, 128, 32),
+        "int6_g128": (mk.int(6, group=128), 6, 128, 64), "int7_g128": (mk.int(7, group=128), 7, 128, 128),
+        "int8_g128": (mk.int(8, group=128), 8, 128, 256),
         "nf4_g64": (mk.nf4(group=64), 4, 64, 16),
         "codebook3_g64_mse": (mk.scaled(mk.grid.values(codebook, bits=3), group=64, scale="mse"), 3, 64, 7),
     }

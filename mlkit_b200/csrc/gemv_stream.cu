@@ -29,6 +29,7 @@
 #include <mutex>
 #include <tuple>
 #include <type_traits>
+#include <utility>
 
 #include "hadamard_steps.cuh"
 
@@ -101,7 +102,7 @@ __device__ __forceinline__ void mma_next(float (&d)[4], uint32_t a0, uint32_t a1
 }
 
 // How codes become tensor-core operands.
-//   RAW   integer grids (lut[c] = min + c) of 2, 3, 4 or 8 bits with one scale per 128 codes: masked bits
+//   RAW   integer grids (lut[c] = min + c) of 2 to 8 bits with one scale per 128 codes: masked bits
 //         used as fp16 subnormals (see the head of this file); the scale multiplies the k-tile sum.
 //   TABLE any table of at most 16 levels with 3- or 4-bit codes and one scale per 64 or 128 codes: a
 //         pair of neighbouring codes indexes a shared-memory table of fp16 pairs (one copy per lane,
@@ -116,7 +117,7 @@ enum { MODE_RAW = 0, MODE_TABLE = 1 };
 template <int BITS, int MODE, int GPT, int KT>
 struct Visit {
   static constexpr int TILE_ROW_BYTES = 16 * BITS;               // 128 codes of one row
-  static constexpr int LANE_BYTES = 4 * BITS;                    // a lane's 32 codes of one row
+  [[maybe_unused]] static constexpr int LANE_BYTES = 4 * BITS;                    // a lane's 32 codes of one row
   static constexpr int TILE_BYTES = 16 * TILE_ROW_BYTES;         // 16 rows
   static constexpr int SEGMENT = KT * TILE_ROW_BYTES;            // contiguous bytes of one row per visit
   static constexpr int VECTORS_PER_ROW = SEGMENT / 16;           // 16-byte vectors per row segment
@@ -127,10 +128,10 @@ struct Visit {
   static constexpr int SCALE_ROW_BYTES = KT * GPT * 2 < 4 ? 4 : KT * GPT * 2;
   static constexpr int SCALE_OFFSET = KT * TILE_BYTES;
   static constexpr int SLOT_BYTES = KT * TILE_BYTES + 16 * SCALE_ROW_BYTES;
-  [[maybe_unused]] static constexpr int CLASSES = MODE == MODE_RAW ? (BITS == 4 ? 2 : BITS == 2 ? 4 : BITS == 3 ? 8 : 1) : 1;
+  [[maybe_unused]] static constexpr int CLASSES = MODE == MODE_RAW ? (BITS == 4 ? 2 : BITS == 2 ? 4 : BITS == 3 ? 8 : BITS == 8 ? 1 : 11 - BITS) : 1;
   [[maybe_unused]] static constexpr int TABLE_ENTRIES = MODE == MODE_TABLE ? (1 << (2 * BITS)) : 0;   // pairs of codes
   static_assert(SEGMENT % 16 == 0 && SLOT_BYTES % 16 == 0, "visit geometry");
-  static_assert(MODE == MODE_TABLE ? (BITS == 3 || BITS == 4) : (BITS == 2 || BITS == 3 || BITS == 4 || BITS == 8), "codec");
+  static_assert(MODE == MODE_TABLE ? (BITS == 3 || BITS == 4) : (BITS >= 2 && BITS <= 8), "codec");
 };
 
 __device__ __forceinline__ uint4 load_shared16(uint32_t address) {
@@ -169,6 +170,69 @@ __host__ __device__ constexpr uint32_t tile_offset(int tile, int row, int vector
   if (BITS == 4) return uint32_t(tile) * 1024u + uint32_t(row ^ (tile & 1)) * 64u + uint32_t(vector) * 16u;
   if (BITS == 8) return uint32_t(tile) * 2048u + uint32_t(row) * 128u + uint32_t(vector ^ (row & 1)) * 16u;
   return uint32_t(tile) * (256u * BITS) + uint32_t(row) * (16u * BITS) + uint32_t(vector) * 16u;
+}
+
+// Integer grids of 5, 6 or 7 bits.  A lane's 32 codes of a row are 4 B bytes whose halves (16 codes, 2 B
+// bytes) repeat each other's bit positions, so a register that pairs bytes (i, i + 1) of the first half
+// with the same bytes of the second holds code c and code c + 16 at one offset of its two 16-bit lanes.
+// Code c starts at bit (B c) % 8 of byte (B c) / 8; where that leaves it reaching past the ten mantissa
+// bits of an fp16 the register is moved down four bits first.  What remains is the lift 2^offset of the
+// subnormal the mask cuts out: codes of equal offset share an accumulator.
+template <int B>
+struct Spread {
+  __host__ __device__ static constexpr int window(int c) { return (B * c) / 8; }
+  __host__ __device__ static constexpr int shift(int c) { return (B * c) % 8 + B <= 10 ? 0 : 4; }
+  __host__ __device__ static constexpr int offset(int c) { return (B * c) % 8 - shift(c); }
+  static constexpr int LIFTS = 11 - B;   // offsets 0 .. 10 - B
+  // the codes in the order the tensor-core steps take them: by offset, two per step
+  __host__ __device__ static constexpr int code_of(int step, int which) {
+    int n = 0;
+    for (int o = 0; o < LIFTS; ++o)
+      for (int c = 0; c < 16; ++c)
+        if (offset(c) == o) {
+          if (n == 2 * step + which) return c;
+          ++n;
+        }
+    return -1;
+  }
+  __host__ __device__ static constexpr bool opens_class(int step) { return step == 0 || offset(code_of(step, 0)) != offset(code_of(step - 1, 0)); }
+  __host__ __device__ static constexpr bool used(int o) {
+    for (int c = 0; c < 16; ++c)
+      if (offset(c) == o) return true;
+    return false;
+  }
+  __host__ __device__ static constexpr bool paired() {
+    for (int step = 0; step < 8; ++step)
+      if (offset(code_of(step, 0)) != offset(code_of(step, 1))) return false;
+    return true;
+  }
+};
+
+// the register and the byte positions in it that hold bytes (I, I + 1) of a lane's 4 B bytes
+template <int B, int I>
+__device__ __forceinline__ uint32_t piece_register(const uint32_t (&w)[B]) {
+  if constexpr (I % 4 == 3 && I / 4 + 1 < B) return __funnelshift_r(w[I / 4], w[I / 4 + 1], 16);
+  else return w[I / 4];
+}
+template <int B>
+__host__ __device__ constexpr uint32_t piece_bytes(int I) {   // two selector digits: where byte I and byte I + 1 sit
+  if (I % 4 == 3 && I / 4 + 1 < B) return 0x21u;
+  if (I % 4 == 3) return 0x33u;           // the last byte of all: its neighbour does not exist and is not needed
+  return uint32_t(I % 4) | uint32_t(I % 4 + 1) << 4;
+}
+template <int B, int I>
+__device__ __forceinline__ uint32_t paired_window(const uint32_t (&w)[B]) {
+  constexpr uint32_t selector = piece_bytes<B>(I) | (piece_bytes<B>(I + 2 * B) + 0x44u) << 8;
+  return __byte_perm(piece_register<B, I>(w), piece_register<B, I + 2 * B>(w), selector);
+}
+
+template <int... I, typename F>
+__device__ __forceinline__ void static_for_each(std::integer_sequence<int, I...>, F&& f) {
+  (f(std::integral_constant<int, I>{}), ...);
+}
+template <int N, typename F>
+__device__ __forceinline__ void static_for(F&& f) {
+  static_for_each(std::make_integer_sequence<int, N>{}, f);
 }
 
 // ROTATE: the instance that transforms its activations on load; the plain instance carries none of that code
@@ -389,6 +453,13 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
           b[kk][2 * c + 0] = __byte_perm(r[c / 2], r[c / 2 + 8], selector);
           b[kk][2 * c + 1] = __byte_perm(r[c / 2 + 4], r[c / 2 + 12], selector);
         }
+      } else if constexpr (RAW && BITS >= 5 && BITS <= 7) {
+        // step s takes codes (c, c + 16) and (c', c' + 16), c and c' the two codes of the step's offset class
+        static_for<8>([&](auto step) {
+          constexpr int c0 = Spread<BITS>::code_of(decltype(step)::value, 0), c1 = Spread<BITS>::code_of(decltype(step)::value, 1);
+          b[kk][2 * decltype(step)::value + 0] = __byte_perm(r[c0 / 2], r[c0 / 2 + 8], (c0 & 1) ? 0x7632 : 0x5410);
+          b[kk][2 * decltype(step)::value + 1] = __byte_perm(r[c1 / 2], r[c1 / 2 + 8], (c1 & 1) ? 0x7632 : 0x5410);
+        });
       } else {
 #pragma unroll
         for (int j = 0; j < 16; ++j) b[kk][j] = r[j];   // neighbouring codes pair up: the natural order
@@ -493,6 +564,31 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
         step(integral_constant<int, 5>{}, integral_constant<int, 7>{}, q[1], p[1], q[3], p[3]);
         step(integral_constant<int, 6>{}, integral_constant<int, 2>{}, q1, p1, q3, p3);
         step(integral_constant<int, 7>{}, integral_constant<int, 5>{}, q1, p1, q3, p3);
+      } else if constexpr (BITS >= 5 && BITS <= 7) {
+        static_assert(Spread<BITS>::paired(), "every offset class holds an even number of codes");
+        uint32_t q[BITS], p[BITS];
+        const uint32_t at0 = slot_at + tile_offset<BITS>(kk, g, 0) + t * (4 * BITS);
+        const uint32_t at1 = slot_at + tile_offset<BITS>(kk, g + 8, 0) + t * (4 * BITS);
+#pragma unroll
+        for (int i = 0; i < BITS; ++i) {
+          q[i] = load_shared4(at0 + 4 * i);
+          p[i] = load_shared4(at1 + 4 * i);
+        }
+        static_for<8>([&](auto step) {
+          using S = Spread<BITS>;
+          constexpr int s = decltype(step)::value, c0 = S::code_of(s, 0), c1 = S::code_of(s, 1), o = S::offset(c0);
+          constexpr uint32_t mask = (((1u << BITS) - 1u) * 0x00010001u) << o;
+          const uint32_t a0 = (paired_window<BITS, S::window(c0)>(q) >> S::shift(c0)) & mask;
+          const uint32_t a1 = (paired_window<BITS, S::window(c0)>(p) >> S::shift(c0)) & mask;
+          const uint32_t a2 = (paired_window<BITS, S::window(c1)>(q) >> S::shift(c1)) & mask;
+          const uint32_t a3 = (paired_window<BITS, S::window(c1)>(p) >> S::shift(c1)) & mask;
+          if constexpr (s == 0)
+            mma_first(acc[o], a0, a1, a2, a3, b[kk][0], b[kk][1], start[kk][0], start[kk][1], start[kk][2], start[kk][3]);
+          else if constexpr (S::opens_class(s))
+            mma_first(acc[o], a0, a1, a2, a3, b[kk][2 * s], b[kk][2 * s + 1], 0.f, 0.f, 0.f, 0.f);
+          else
+            mma_next(acc[o], a0, a1, a2, a3, b[kk][2 * s], b[kk][2 * s + 1]);
+        });
       } else {  // BITS == 2: codes of equal position in their byte share a lift of 4^i and an accumulator
         const uint2 lo = load_shared8(slot_at + tile_offset<2>(kk, g, 0) + t * 8), hi = load_shared8(slot_at + tile_offset<2>(kk, g + 8, 0) + t * 8);
         const uint32_t q[2] = {lo.x, lo.y}, p[2] = {hi.x, hi.y};
@@ -516,13 +612,25 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) gemv_stream_kernel(const St
       }
       // classes of higher lift were c * 2^-24 times a power of two: recombine exactly (Horner), then one
       // scale per row and k-tile
-      constexpr float down = BITS == 4 ? 0.0625f : BITS == 3 ? 0.5f : 0.25f;
+      if constexpr (BITS >= 5 && BITS <= 7) {   // the offsets in use need not be consecutive
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        float total = acc[V::CLASSES - 1][q];
+        for (int q = 0; q < 4; ++q) {
+          float total = acc[0][q];
+          static_for<V::CLASSES - 1>([&](auto index) {
+            constexpr int o = decltype(index)::value + 1;
+            if constexpr (Spread<BITS>::used(o)) total = fmaf(acc[o][q], 1.f / float(1 << o), total);
+          });
+          y[q] = fmaf(q < 2 ? f0 : f1, total, y[q]);
+        }
+      } else {
+        constexpr float down = BITS == 4 ? 0.0625f : BITS == 3 ? 0.5f : 0.25f;
 #pragma unroll
-        for (int c = V::CLASSES - 2; c >= 0; --c) total = fmaf(total, down, acc[c][q]);
-        y[q] = fmaf(q < 2 ? f0 : f1, total, y[q]);
+        for (int q = 0; q < 4; ++q) {
+          float total = acc[V::CLASSES - 1][q];
+#pragma unroll
+          for (int c = V::CLASSES - 2; c >= 0; --c) total = fmaf(total, down, acc[c][q]);
+          y[q] = fmaf(q < 2 ? f0 : f1, total, y[q]);
+        }
       }
     } else {
       // table codecs: a pair of codes -> fp16 pair from the lane's copy of the table, times the scale of
@@ -801,6 +909,9 @@ int dispatch_stream(const StreamArgs& a, const StreamPlan& p, cudaStream_t strea
     if (p.bits == 4) return dispatch_shape<4, MODE_RAW, 1>(a, p, stream, cluster_cap);
     if (p.bits == 2) return dispatch_shape<2, MODE_RAW, 1>(a, p, stream, cluster_cap);
     if (p.bits == 3) return dispatch_shape<3, MODE_RAW, 1>(a, p, stream, cluster_cap);
+    if (p.bits == 5) return dispatch_shape<5, MODE_RAW, 1>(a, p, stream, cluster_cap);
+    if (p.bits == 6) return dispatch_shape<6, MODE_RAW, 1>(a, p, stream, cluster_cap);
+    if (p.bits == 7) return dispatch_shape<7, MODE_RAW, 1>(a, p, stream, cluster_cap);
     return dispatch_shape<8, MODE_RAW, 1>(a, p, stream, cluster_cap);
   }
   if (p.bits == 4) return p.gpt == 1 ? dispatch_shape<4, MODE_TABLE, 1>(a, p, stream, cluster_cap)
@@ -814,7 +925,7 @@ bool codec_of(int group, int bits, int lut_len, const void* zeros, int integer_g
   if (zeros != nullptr || lut_len < 1 || lut_len > (1 << bits)) return false;
   const bool ramp = integer_grid && lut_len == (1 << bits) && grid_minimum == float(int(grid_minimum)) &&
                     grid_minimum >= -512.f && grid_minimum <= 512.f;
-  if (ramp && group == 128 && (bits == 2 || bits == 3 || bits == 4 || bits == 8)) {
+  if (ramp && group == 128 && bits >= 2 && bits <= 8) {
     p.bits = bits; p.mode = MODE_RAW; p.gpt = 1;
     return true;
   }

@@ -292,7 +292,8 @@ def test_matvec_stream_shapes_bias_ragged_rows_and_splits(rows, width):
 
 
 @pytest.mark.parametrize("kind,bits,group", [("int", 2, 128), ("int", 8, 128), ("int", 3, 128), ("nf4", 4, 64),
-                                             ("nf4", 4, 128), ("codebook3", 3, 64), ("int", 4, 64)])
+                                             ("nf4", 4, 128), ("codebook3", 3, 64), ("int", 4, 64), ("int", 5, 128),
+                                             ("int", 6, 128), ("int", 7, 128)])
 @pytest.mark.parametrize("rows,width", [(300, 1536), (4864, 896), (48, 8192), (1000, 1024)])
 def test_matvec_stream_every_codec_bias_ragged_rows_and_splits(kind, bits, group, rows, width):
     """Every codec of the streaming kernel on shapes with one and two k-tiles per warp, K split over a
