@@ -502,11 +502,17 @@ def reference_arm(args) -> None:
     }))
 
 
+def mk_nf4_levels() -> list:
+    from mlkit_b200.quantization import NF4_VALUES
+
+    return [float(v) for v in NF4_VALUES]
+
+
 def run_case(spec: str, device: torch.device, launches: int) -> None:
     """One layer shape, ``launches`` launches over distinct weight copies (each cold in L2), nothing
     else on the device: the small case a profiler captures.  Prints the mean launch time.
     ``NAME[:ROWS[:KERNEL]]`` with NAME a block linear, ``qkv`` or ``gate_up``; ``gemm:NAME:ROWS`` runs the
-    fused dequantise + GEMM on that shape; ``rht:ROWS:WIDTH`` runs
+    fused dequantise + GEMM on that shape; ``codec:NAME:ROWS`` one codec of the sweep on the gate shape; ``rht:ROWS:WIDTH`` runs
     the activation transform instead; ``tp_layer:WORLD:BATCH`` times the operators of one decoder layer with
     the shard shapes of WORLD ranks."""
     from mlkit_b200 import kernels
@@ -523,6 +529,36 @@ def run_case(spec: str, device: torch.device, launches: int) -> None:
         us = time_transform(device, rows, width, launches)
         print(json.dumps({"case": spec, "launches": launches, "us_per_launch": round(us["median"], 2),
                           "bytes_per_launch": 2 * rows * width * 2 + width}))
+        return
+    if fields[0] == "codec":        # codec:NAME:ROWS -- one codec of the sweep on the gate shape, random codes
+        tables = {"nf4_g64": (4, 64, mk_nf4_levels()), "nf4_g128": (4, 128, mk_nf4_levels()),
+                  "codebook3_g64": (3, 64, [-1, -0.5, -0.25, 0, 0.25, 0.5, 1.0]),
+                  "int3_g128": (3, 128, list(range(-4, 4))), "int7_g128": (7, 128, list(range(-64, 64)))}
+        bits, group, levels = tables[fields[1]]
+        rows = int(fields[2]) if len(fields) > 2 else 1
+        out_rows, width = LLAMA8B["gate"]
+        generator = torch.Generator(device=device).manual_seed(5)
+        packed = [torch.randint(0, 256, (out_rows * width * bits // 8,), dtype=torch.uint8, device=device, generator=generator)
+                  for _ in range(launches)]
+        scales = [(torch.rand(out_rows, width // group, device=device, generator=generator) * 0.01 + 0.001).half()
+                  for _ in range(launches)]
+        values = torch.tensor(levels, dtype=torch.float32, device=device)
+        integer = fields[1].startswith("int")
+        x = torch.randn(rows, width, device=device, generator=generator).half()
+        out = torch.empty(rows, out_rows, device=device, dtype=torch.float16)
+        run = lambda i: kernels.packed_matvec(x, packed[i], scales[i], values, None, None, out, group=group, bits=bits,
+                                              integer_grid=integer, grid_minimum=float(levels[0]) if integer else 0.0)
+        run(0)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(launches):
+            run(i)
+        stop.record()
+        torch.cuda.synchronize()
+        print(json.dumps({"case": spec, "launches": launches,
+                          "us_per_launch_eager": round(start.elapsed_time(stop) * 1e3 / launches, 2),
+                          "bytes_per_launch": matvec_bytes(out_rows, width, rows, bits, group, len(levels))}))
         return
     shapes = dict(LLAMA8B, qkv=(6144, 4096), gate_up=(28672, 4096))
     fused_gemm = fields[0] == "gemm"      # gemm:NAME:ROWS -- the fused dequantise + GEMM on that layer shape
