@@ -117,7 +117,6 @@ enum { MODE_RAW = 0, MODE_TABLE = 1 };
 template <int BITS, int MODE, int GPT, int KT>
 struct Visit {
   static constexpr int TILE_ROW_BYTES = 16 * BITS;               // 128 codes of one row
-  [[maybe_unused]] static constexpr int LANE_BYTES = 4 * BITS;                    // a lane's 32 codes of one row
   static constexpr int TILE_BYTES = 16 * TILE_ROW_BYTES;         // 16 rows
   static constexpr int SEGMENT = KT * TILE_ROW_BYTES;            // contiguous bytes of one row per visit
   static constexpr int VECTORS_PER_ROW = SEGMENT / 16;           // 16-byte vectors per row segment
